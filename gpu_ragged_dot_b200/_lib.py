@@ -1,0 +1,94 @@
+"""ctypes binding of librd_b200.so (the C ABI declared in include/ragged_dot_b200.h).
+
+There is no fallback: if the shared object is missing or does not export a symbol the header
+declares, loading raises.  Build it with ``python -m gpu_ragged_dot_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "librd_b200.so")
+
+RD_OK = 0
+RD_DTYPE_F16 = 0
+RD_DTYPE_BF16 = 1
+
+# Every symbol include/ragged_dot_b200.h declares, with its ctypes signature.
+_c_int = ctypes.c_int
+_c_void_p = ctypes.c_void_p
+_c_size_t = ctypes.c_size_t
+
+
+class TileCfg(ctypes.Structure):
+    """Mirror of ``rd_tile_cfg``."""
+
+    _fields_ = [("tile_n", ctypes.c_int32), ("max_ctas", ctypes.c_int32)]
+
+
+SIGNATURES = {
+    "rd_version": (_c_int, []),
+    "rd_status_string": (ctypes.c_char_p, [_c_int]),
+    "rd_workspace_bytes": (_c_int, [_c_int, _c_int, ctypes.POINTER(_c_size_t)]),
+    "rd_metadata": (
+        _c_int,
+        [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    ),
+    "rd_gmm": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_tgmm": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 5
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_device_status": (_c_int, [_c_void_p, _c_void_p]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class RaggedDotError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, code: int, text: str, where: str):
+        super().__init__(f"{where}: {text} (status {code})")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and bind every declared symbol; raise if anything is missing."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: the CUDA library is not built. "
+                "Run `python -m gpu_ragged_dot_b200.build` (needs nvcc with sm_100a support). "
+                "There is no CPU or PyTorch fallback."
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+        return lib
+
+
+def status_string(code: int) -> str:
+    return load().rd_status_string(code).decode()
+
+
+def check(code: int, where: str) -> None:
+    if code != RD_OK:
+        raise RaggedDotError(code, status_string(code), where)

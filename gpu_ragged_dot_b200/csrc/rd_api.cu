@@ -1,0 +1,341 @@
+// C ABI of the ragged-dot library (declared in include/ragged_dot_b200.h): argument checks,
+// TMA descriptor encoding, tile selection and kernel launches.  No torch / XLA types here;
+// the XLA-FFI and Python layers sit on top of these entry points.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../include/ragged_dot_b200.h"
+#include "rd_gemm.cuh"
+#include "rd_metadata.cuh"
+
+namespace {
+
+using rd::GemmArgs;
+using rd::WorkspaceLayout;
+
+// ------------------------------------------------------------------ driver entry point
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// rank-2 or rank-3 tiled map over a dense row-major 16-bit tensor, 128-byte swizzle,
+// zero fill outside the bounds.  dims / box are innermost first.
+int encode_map(CUtensorMap* map, const void* base, int dtype, int rank, const uint64_t* dims,
+               const uint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return RD_ERR_DRIVER;
+  cuuint64_t gdims[3];
+  cuuint64_t gstrides[2];
+  cuuint32_t gbox[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  uint64_t stride = 2;
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    stride *= dims[i];
+    if (i + 1 < rank) gstrides[i] = stride;
+  }
+  const CUtensorMapDataType dt =
+      dtype == RD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides,
+                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RD_OK : RD_ERR_TENSOR_MAP;
+}
+
+// ------------------------------------------------------------------ device properties
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+bool aligned16(const void* p) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int max_row_tiles(int m, int g) { return (m + rd::kTileM - 1) / rd::kTileM + g; }
+
+struct Workspace {
+  WorkspaceLayout layout;
+  int32_t* base;
+  int32_t* status() const { return base + layout.off_status(); }
+  int32_t* totals() const { return base + layout.off_totals(); }
+  int32_t* group_offsets() const { return base + layout.off_group_offsets(); }
+  int32_t* tile_prefix() const { return base + layout.off_tile_prefix(); }
+  int32_t* tile2group() const { return base + layout.off_tile2group(); }
+  int32_t* tile2idx() const { return base + layout.off_tile2idx(); }
+};
+
+int bind_workspace(void* ws, size_t ws_bytes, int m, int g, Workspace* out) {
+  if (!aligned16(ws)) return RD_ERR_BAD_POINTER;
+  out->layout.g = g;
+  out->layout.max_tiles = max_row_tiles(m, g);
+  if (ws_bytes < static_cast<size_t>(out->layout.total_words()) * sizeof(int32_t))
+    return RD_ERR_WORKSPACE;
+  out->base = static_cast<int32_t*>(ws);
+  return RD_OK;
+}
+
+void launch_internal_metadata(const int32_t* group_sizes, int g, int m, const Workspace& w,
+                              cudaStream_t stream) {
+  rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, stream>>>(
+      group_sizes, g, m, rd::kTileM, w.layout.max_tiles, w.group_offsets(), w.tile2group(),
+      w.tile2idx(), w.totals(), w.tile_prefix(), w.totals() + 1, w.status());
+}
+
+// ------------------------------------------------------------------ tile selection
+// The committed replacement for the reference's run-time tune-jax search: BN by output width
+// and by how many tiles the persistent grid would otherwise get.
+int choose_tile_n(long long row_tiles, int n, int sms) {
+  if (n <= 64) return 64;
+  if (n <= 128) return 128;
+  // Prefer the widest tile unless that leaves the grid under-filled (small / decode shapes).
+  const long long tiles256 = row_tiles * ((n + 255) / 256);
+  if (tiles256 >= 2LL * sms) return 256;
+  const long long tiles128 = row_tiles * ((n + 127) / 128);
+  if (tiles128 >= 2LL * sms) return 128;
+  return tiles256 >= sms ? 256 : (tiles128 >= sms ? 128 : 64);
+}
+
+template <int BN, bool kBKMajor, bool kTgmm>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int ctas,
+                cudaStream_t stream) {
+  constexpr int kStageBytes = rd::stage_bytes<BN, kTgmm>();
+  constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  constexpr int kSmem = kStages * kStageBytes + 1024;
+  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm>;
+  // The attribute is per device; setting it again is cheap, so do it on every call rather
+  // than track which devices have seen it.
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  kernel<<<ctas, rd::kGemmThreads, kSmem, stream>>>(ta, tb, args);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int pick_ctas(const rd_tile_cfg* cfg) {
+  int ctas = sm_count();
+  if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < ctas) ctas = cfg->max_ctas;
+  return ctas;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rd_version(void) { return RD_VERSION; }
+
+const char* rd_status_string(int code) {
+  switch (code) {
+    case RD_OK: return "ok";
+    case RD_ERR_BAD_SHAPE: return "bad shape: sizes must be >= 0 and k, n multiples of 8";
+    case RD_ERR_BAD_DTYPE: return "unsupported dtype: only 16-bit float (f16, bf16) inputs";
+    case RD_ERR_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";
+    case RD_ERR_WORKSPACE: return "workspace too small (see rd_workspace_bytes)";
+    case RD_ERR_BAD_CONFIG: return "unsupported tile configuration";
+    case RD_ERR_TENSOR_MAP: return "driver rejected a TMA tensor map";
+    case RD_ERR_LAUNCH: return "kernel launch failed";
+    case RD_ERR_DRIVER: return "cuTensorMapEncodeTiled entry point not available";
+    case RD_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
+    default: return "unknown status";
+  }
+}
+
+int rd_workspace_bytes(int m, int g, size_t* bytes) {
+  if (m < 0 || g < 0 || bytes == nullptr) return RD_ERR_BAD_SHAPE;
+  WorkspaceLayout l;
+  l.g = g;
+  l.max_tiles = max_row_tiles(m, g);
+  size_t b = static_cast<size_t>(l.total_words()) * sizeof(int32_t);
+  *bytes = (b + 255) & ~static_cast<size_t>(255);
+  return RD_OK;
+}
+
+int rd_metadata(const int32_t* group_sizes, int g, int m, int chunk_m, int32_t* group_offsets,
+                int32_t* row_it2group, int32_t* row_it2it_in_group, int32_t* total_row_its,
+                void* stream) {
+  if (g < 0 || m < 0 || chunk_m <= 0) return RD_ERR_BAD_SHAPE;
+  if (g == 0) {
+    // U = ceil(m / chunk_m) rows of zeros and a zero total.
+    const int u = (m + chunk_m - 1) / chunk_m;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (row_it2group && u) cudaMemsetAsync(row_it2group, 0, sizeof(int32_t) * u, s);
+    if (row_it2it_in_group && u) cudaMemsetAsync(row_it2it_in_group, 0, sizeof(int32_t) * u, s);
+    if (total_row_its) cudaMemsetAsync(total_row_its, 0, sizeof(int32_t), s);
+    return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+  }
+  if (group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  const int u = (m + chunk_m - 1) / chunk_m + g;
+  rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      group_sizes, g, m, chunk_m, u, group_offsets, row_it2group, row_it2it_in_group,
+      total_row_its, nullptr, nullptr, nullptr);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, void* workspace,
+           size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
+           const rd_tile_cfg* cfg, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (m < 0 || k < 0 || n < 0 || g < 0 || (k & 7) || (n & 7)) return RD_ERR_BAD_SHAPE;
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (m == 0 || n == 0) return RD_OK;
+  if (!aligned16(y)) return RD_ERR_BAD_POINTER;
+  if (g == 0 || k == 0) {  // nothing contributes: every row is a zero row
+    cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * 2, stream);
+    return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+  }
+  if (!aligned16(x) || !aligned16(A) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  Workspace w;
+  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  if (rc != RD_OK) return rc;
+
+  const int sms = sm_count();
+  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n((m + rd::kTileM - 1) / rd::kTileM, n, sms);
+  if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {rd::kTileK, rd::kTileM};
+    rc = encode_map(&ta, x, dtype, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+  if (trans_rhs) {  // A[g, n, k]: rows of k, K-major operand, one [BN][64] box per stage
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(g)};
+    const uint32_t box[3] = {rd::kTileK, static_cast<uint32_t>(bn), 1};
+    rc = encode_map(&tb, A, dtype, 3, dims, box);
+  } else {  // A[g, k, n]: rows of n, MN-major operand, [64 k][64 n] boxes
+    const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                              static_cast<uint64_t>(g)};
+    const uint32_t box[3] = {64, rd::kTileK, 1};
+    rc = encode_map(&tb, A, dtype, 3, dims, box);
+  }
+  if (rc != RD_OK) return rc;
+
+  launch_internal_metadata(group_sizes, g, m, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
+  GemmArgs args;
+  args.m = m; args.k = k; args.n = n; args.g = g;
+  args.n_tiles = (n + bn - 1) / bn;
+  args.k_tiles = 0;
+  args.max_m_tiles = w.layout.max_tiles;
+  args.ab_format = dtype;
+  args.group_sizes = group_sizes;
+  args.group_offsets = w.group_offsets();
+  args.tile2group = w.tile2group();
+  args.tile2idx = w.tile2idx();
+  args.tile_prefix = w.tile_prefix();
+  args.totals = w.totals();
+  args.status = w.status();
+  args.out = y;
+
+  const int ctas = pick_ctas(cfg);
+  if (trans_rhs) {
+    if (bn == 256) return launch_gemm<256, true, false>(ta, tb, args, ctas, stream);
+    if (bn == 128) return launch_gemm<128, true, false>(ta, tb, args, ctas, stream);
+    return launch_gemm<64, true, false>(ta, tb, args, ctas, stream);
+  }
+  if (bn == 256) return launch_gemm<256, false, false>(ta, tb, args, ctas, stream);
+  if (bn == 128) return launch_gemm<128, false, false>(ta, tb, args, ctas, stream);
+  return launch_gemm<64, false, false>(ta, tb, args, ctas, stream);
+}
+
+int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+            void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
+            const rd_tile_cfg* cfg, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (m < 0 || k < 0 || n < 0 || g < 0 || (k & 7) || (n & 7)) return RD_ERR_BAD_SHAPE;
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (g == 0 || k == 0 || n == 0) return RD_OK;
+  if (!aligned16(out)) return RD_ERR_BAD_POINTER;
+  if (m == 0) {  // every group is empty
+    cudaMemsetAsync(out, 0, static_cast<size_t>(g) * k * n * 2, stream);
+    return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+  }
+  if (!aligned16(x) || !aligned16(dout) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  Workspace w;
+  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  if (rc != RD_OK) return rc;
+
+  const int sms = sm_count();
+  const long long k_tiles = (k + rd::kTileM - 1) / rd::kTileM;
+  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(k_tiles * g, n, sms);
+  if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {64, rd::kTileK};
+    rc = encode_map(&ta, x, dtype, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {64, rd::kTileK};
+    rc = encode_map(&tb, dout, dtype, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+
+  launch_internal_metadata(group_sizes, g, m, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
+  GemmArgs args;
+  args.m = m; args.k = k; args.n = n; args.g = g;
+  args.n_tiles = (n + bn - 1) / bn;
+  args.k_tiles = static_cast<int>(k_tiles);
+  args.max_m_tiles = w.layout.max_tiles;
+  args.ab_format = dtype;
+  args.group_sizes = group_sizes;
+  args.group_offsets = w.group_offsets();
+  args.tile2group = w.tile2group();
+  args.tile2idx = w.tile2idx();
+  args.tile_prefix = w.tile_prefix();
+  args.totals = w.totals();
+  args.status = w.status();
+  args.out = out;
+
+  const int ctas = pick_ctas(cfg);
+  if (bn == 256) return launch_gemm<256, false, true>(ta, tb, args, ctas, stream);
+  if (bn == 128) return launch_gemm<128, false, true>(ta, tb, args, ctas, stream);
+  return launch_gemm<64, false, true>(ta, tb, args, ctas, stream);
+}
+
+int rd_device_status(const void* workspace, void* stream) {
+  if (workspace == nullptr) return RD_ERR_BAD_POINTER;
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return RD_ERR_LAUNCH;
+  e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return RD_ERR_LAUNCH;
+  return word == 0 ? RD_OK : RD_ERR_DEVICE_WAIT;
+}
+
+}  // extern "C"

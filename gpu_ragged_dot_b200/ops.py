@@ -1,0 +1,361 @@
+"""Host-side mirror of the reference's public interface (gpu_ragged_dot.py:345-454).
+
+Same names (``gmm`` = ``ragged_dot``, ``tgmm`` = ``trans_ragged_dot``), same argument order,
+same defaults and the same custom-VJP wiring, over torch CUDA tensors instead of jax arrays
+(torch supplies device memory and streams; all arithmetic is in librd_b200.so).  The jax
+binding of the same C ABI lives in ``jax_ffi.py``.
+
+Differences from the reference, all deliberate:
+  * ``block_m/block_k/block_n/num_warps/num_stages/chunk_m`` are accepted for drop-in
+    compatibility but are hints only -- tiles come from the committed tile table
+    (``tile_table.py``), which replaces the tune-jax search of tuning.py:49-58.
+  * ``interpret=True`` raises: there is no CPU path.
+  * rows past ``sum(group_sizes)`` are always zero, also when every group is empty (the
+    reference leaves them unwritten in that case, gpu_ragged_dot.py:155-157).
+  * the VJP of ``tgmm`` is the mathematically correct one; the reference's
+    (gpu_ragged_dot.py:431-450) cannot run.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import NamedTuple, Optional
+
+import torch
+
+from . import _lib
+from . import tile_table
+
+__all__ = [
+    "gmm",
+    "tgmm",
+    "ragged_dot",
+    "trans_ragged_dot",
+    "make_group_metadata",
+    "GMMGroupLookupMetadata",
+    "RaggedDotSizes",
+    "BlockSizes",
+]
+
+DEFAULT_BLOCK_M = 64
+DEFAULT_BLOCK_N = 64
+DEFAULT_BLOCK_K = 64
+CHUNK_M = 512
+
+
+class RaggedDotSizes(NamedTuple):
+    m: int
+    k: int
+    n: int
+    g: int
+
+
+class BlockSizes(NamedTuple):
+    m: int
+    k: int
+    n: int
+
+
+class GMMGroupLookupMetadata(NamedTuple):
+    """Same five fields as the reference's tuple (gpu_ragged_dot.py:60-67), as int32 CUDA tensors."""
+
+    group_sizes: torch.Tensor
+    group_offsets: torch.Tensor
+    row_it2group: torch.Tensor
+    row_it2it_in_group: torch.Tensor
+    total_row_its: torch.Tensor
+
+
+_DTYPE_CODE = {torch.float16: _lib.RD_DTYPE_F16, torch.bfloat16: _lib.RD_DTYPE_BF16}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(
+            f"{name} must be a CUDA tensor: ragged_dot runs only on the GPU through librd_b200.so "
+            "(no CPU fallback)"
+        )
+
+
+def _as_i32(group_sizes: torch.Tensor) -> torch.Tensor:
+    _require_cuda(group_sizes, "group_sizes")
+    if group_sizes.dim() != 1:
+        raise AssertionError(f"group_sizes must be 1-D, got {group_sizes.dim()=}")
+    if group_sizes.dtype != torch.int32:
+        group_sizes = group_sizes.to(torch.int32)
+    return group_sizes.contiguous()
+
+
+def _dense16(t: torch.Tensor) -> torch.Tensor:
+    t = t.contiguous()
+    if t.data_ptr() % 16:
+        t = t.clone()
+    return t
+
+
+def _pad_last(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    r = (-t.shape[-1]) % mult
+    return torch.nn.functional.pad(t, (0, r)) if r else t
+
+
+def _pad_last2(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    r1 = (-t.shape[-1]) % mult
+    r2 = (-t.shape[-2]) % mult
+    return torch.nn.functional.pad(t, (0, r1, 0, r2)) if (r1 or r2) else t
+
+
+def _workspace(m: int, g: int, device: torch.device) -> torch.Tensor:
+    lib = _lib.load()
+    nbytes = ctypes.c_size_t(0)
+    _lib.check(lib.rd_workspace_bytes(m, g, ctypes.byref(nbytes)), "rd_workspace_bytes")
+    return torch.empty(max(nbytes.value, 256), dtype=torch.uint8, device=device)
+
+
+def _cfg_ptr(cfg: Optional[_lib.TileCfg]):
+    return ctypes.byref(cfg) if cfg is not None else None
+
+
+def make_group_metadata(group_sizes: torch.Tensor, m: int, chunk_m: int) -> GMMGroupLookupMetadata:
+    """Device-side equivalent of ``_make_gmm_group_metadata`` (gpu_ragged_dot.py:70-90)."""
+    lib = _lib.load()
+    gs = _as_i32(group_sizes)
+    g = gs.numel()
+    u = (m + chunk_m - 1) // chunk_m + g
+    dev = gs.device
+    offsets = torch.empty(g, dtype=torch.int32, device=dev)
+    it2group = torch.empty(u, dtype=torch.int32, device=dev)
+    it2it = torch.empty(u, dtype=torch.int32, device=dev)
+    total = torch.empty((), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.rd_metadata(
+            gs.data_ptr(), g, m, chunk_m, offsets.data_ptr(), it2group.data_ptr(), it2it.data_ptr(),
+            total.data_ptr(), _stream_ptr(dev),
+        )
+    _lib.check(rc, "rd_metadata")
+    return GMMGroupLookupMetadata(gs, offsets, it2group, it2it, total)
+
+
+def gmm_forward(
+    x: torch.Tensor,
+    A: torch.Tensor,
+    group_sizes: torch.Tensor,
+    trans_rhs: bool = False,
+    cfg: Optional[_lib.TileCfg] = None,
+    out: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One call of ``rd_gmm``: y[m,n] = ragged x[m,k] . A[g,k,n] (or A[g,n,k] with trans_rhs)."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    _require_cuda(A, "A")
+    assert A.dim() == 3 and x.dim() == 2, f"but {A.dim()=} {x.dim()=}"
+    gs = _as_i32(group_sizes)
+    assert A.shape[0] == gs.shape[0], f"{A.shape[0]=} != {gs.shape[0]=}"
+    if x.dtype not in _DTYPE_CODE or A.dtype != x.dtype:
+        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {A.dtype}")
+    m, k = x.shape
+    g = A.shape[0]
+    n = A.shape[-1] if not trans_rhs else A.shape[-2]
+    k_rhs = A.shape[-2] if not trans_rhs else A.shape[-1]
+    assert k_rhs == k, f"contraction mismatch: x has k={k}, A has {k_rhs}"
+
+    # TMA needs 16-byte row strides: pad k and n up to multiples of 8 with zeros (exact).
+    xp = _dense16(_pad_last(x))
+    Ap = _dense16(_pad_last2(A))
+    kp = xp.shape[1]
+    np_ = Ap.shape[-1] if not trans_rhs else Ap.shape[-2]
+    padded_n = np_ != n
+    if out is not None and not padded_n:
+        assert out.shape == (m, n) and out.dtype == x.dtype and out.is_contiguous()
+        y = out
+    else:
+        y = torch.empty((m, np_), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else _workspace(m, g, x.device)
+    if cfg is None:
+        cfg = tile_table.lookup("gmm_t" if trans_rhs else "gmm", m, kp, np_, g)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_gmm(
+            xp.data_ptr(), Ap.data_ptr(), gs.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
+            m, kp, np_, g, int(bool(trans_rhs)), _DTYPE_CODE[x.dtype], _cfg_ptr(cfg),
+            _stream_ptr(x.device),
+        )
+    _lib.check(rc, "rd_gmm")
+    if padded_n:
+        y = y[:, :n].contiguous()
+        if out is not None:
+            out.copy_(y)
+            y = out
+    return y
+
+
+def tgmm_forward(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    group_sizes: torch.Tensor,
+    cfg: Optional[_lib.TileCfg] = None,
+    out: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One call of ``rd_tgmm``: out[g,k,n] = x_g^T . y_g over each group's rows."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    _require_cuda(y, "y")
+    assert y.dim() == 2 and x.dim() == 2 and x.shape[0] == y.shape[0]
+    gs = _as_i32(group_sizes)
+    if x.dtype not in _DTYPE_CODE or y.dtype != x.dtype:
+        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {y.dtype}")
+    (m, k), n = x.shape, y.shape[-1]
+    g = gs.numel()
+    xp = _dense16(_pad_last(x))
+    yp = _dense16(_pad_last(y))
+    kp, np_ = xp.shape[1], yp.shape[1]
+    padded = (kp != k) or (np_ != n)
+    if out is not None and not padded:
+        assert out.shape == (g, k, n) and out.dtype == x.dtype and out.is_contiguous()
+        res = out
+    else:
+        res = torch.empty((g, kp, np_), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else _workspace(m, g, x.device)
+    if cfg is None:
+        cfg = tile_table.lookup("tgmm", m, kp, np_, g)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_tgmm(
+            xp.data_ptr(), yp.data_ptr(), gs.data_ptr(), res.data_ptr(), ws.data_ptr(), ws.numel(),
+            m, kp, np_, g, _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+        )
+    _lib.check(rc, "rd_tgmm")
+    if padded:
+        res = res[:, :k, :n].contiguous()
+        if out is not None:
+            out.copy_(res)
+            res = out
+    return res
+
+
+def _check_static_args(x, interpret, compute_dtype, acc_dtype):
+    if interpret:
+        raise NotImplementedError(
+            "interpret=True is not supported: this build has no CPU path (CUDA sm_100a only)"
+        )
+    if compute_dtype is not None and _torch_dtype(compute_dtype) != x.dtype:
+        raise NotImplementedError(
+            f"compute_dtype={compute_dtype} differs from the input dtype {x.dtype}; only None or the "
+            "input dtype is implemented"
+        )
+    if acc_dtype is not None and _torch_dtype(acc_dtype) != torch.float32:
+        raise NotImplementedError(f"acc_dtype={acc_dtype}: only float32 accumulation is implemented")
+
+
+def _torch_dtype(d):
+    if isinstance(d, torch.dtype):
+        return d
+    name = getattr(d, "name", None) or getattr(d, "__name__", None) or str(d)
+    table = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+    if name in table:
+        return table[name]
+    raise NotImplementedError(f"unknown dtype {d!r}")
+
+
+class _GmmFn(torch.autograd.Function):
+    """custom_vjp of gmm: gpu_ragged_dot.py:383-405."""
+
+    @staticmethod
+    def forward(ctx, x, A, group_sizes, trans_rhs):
+        ctx.trans_rhs = trans_rhs
+        ctx.save_for_backward(x, A, group_sizes)  # residuals (x, A, group_sizes), reference :227
+        return gmm_forward(x, A, group_sizes, trans_rhs=trans_rhs)
+
+    @staticmethod
+    def backward(ctx, do):
+        x, A, group_sizes = ctx.saved_tensors
+        do = do.contiguous()
+        dx = dA = None
+        if ctx.needs_input_grad[0]:
+            dx = gmm_forward(do, A, group_sizes, trans_rhs=not ctx.trans_rhs)
+        if ctx.needs_input_grad[1]:
+            dA = (
+                tgmm_forward(x, do, group_sizes)
+                if not ctx.trans_rhs
+                else tgmm_forward(do, x, group_sizes)
+            )
+        return dx, dA, None, None
+
+
+class _TgmmFn(torch.autograd.Function):
+    """VJP of tgmm.  out[g] = x_g^T y_g  =>  dx_g = y_g dout[g]^T,  dy_g = x_g dout[g]."""
+
+    @staticmethod
+    def forward(ctx, x, y, group_sizes):
+        ctx.save_for_backward(x, y, group_sizes)
+        return tgmm_forward(x, y, group_sizes)
+
+    @staticmethod
+    def backward(ctx, do):
+        x, y, group_sizes = ctx.saved_tensors
+        do = do.contiguous()
+        dx = dy = None
+        if ctx.needs_input_grad[0]:
+            dx = gmm_forward(y, do, group_sizes, trans_rhs=True)
+        if ctx.needs_input_grad[1]:
+            dy = gmm_forward(x, do, group_sizes, trans_rhs=False)
+        return dx, dy, None
+
+
+def gmm(
+    x: torch.Tensor,  # [m, k]
+    A: torch.Tensor,  # [g, k, n]
+    group_sizes: torch.Tensor,  # [g]
+    block_m: int = DEFAULT_BLOCK_M,
+    block_k: int = DEFAULT_BLOCK_K,
+    block_n: int = DEFAULT_BLOCK_N,
+    trans_rhs: bool = False,
+    interpret: bool = False,
+    compute_dtype=None,
+    acc_dtype=torch.float32,
+    num_warps: Optional[int] = None,
+    num_stages: Optional[int] = None,
+    chunk_m: int = CHUNK_M,
+) -> torch.Tensor:
+    """Ragged dot corresponding to jax.lax.ragged_dot: (m, k) x (g, k, n) -> (m, n).
+
+    Signature of the reference's ``gmm`` (gpu_ragged_dot.py:362-376)."""
+    del block_m, block_k, block_n, num_warps, num_stages, chunk_m  # hints; the tile table decides
+    _check_static_args(x, interpret, compute_dtype, acc_dtype)
+    return _GmmFn.apply(x, A, group_sizes, bool(trans_rhs))
+
+
+def tgmm(
+    x: torch.Tensor,  # [m, k]
+    y: torch.Tensor,  # [m, n]
+    group_sizes: torch.Tensor,  # [g]
+    block_m: int = DEFAULT_BLOCK_M,
+    block_k: int = DEFAULT_BLOCK_K,
+    block_n: int = DEFAULT_BLOCK_N,
+    interpret: bool = False,
+    compute_dtype=None,
+    acc_dtype=torch.float32,
+    num_warps: Optional[int] = None,
+    num_stages: Optional[int] = None,
+    chunk_m: int = CHUNK_M,
+) -> torch.Tensor:
+    """Transposed ragged dot: (m, k) x (m, n) -> (g, k, n).
+
+    Signature of the reference's ``tgmm`` (gpu_ragged_dot.py:411-424)."""
+    del block_m, block_k, block_n, num_warps, num_stages, chunk_m
+    _check_static_args(x, interpret, compute_dtype, acc_dtype)
+    return _TgmmFn.apply(x, y, group_sizes)
+
+
+ragged_dot = gmm
+trans_ragged_dot = tgmm
+
+
+def device_status(workspace: torch.Tensor) -> int:
+    """Synchronise and return the status the kernels left in ``workspace`` (0 = ok)."""
+    lib = _lib.load()
+    with torch.cuda.device(workspace.device):
+        return lib.rd_device_status(workspace.data_ptr(), _stream_ptr(workspace.device))

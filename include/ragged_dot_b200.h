@@ -1,0 +1,95 @@
+/* ragged_dot_b200.h -- C ABI of the B200 (sm_100a) ragged-dot library.
+ *
+ * Every entry point is stream-ordered and asynchronous: it validates its arguments on the
+ * host, enqueues kernels on `stream` and returns.  Nothing here allocates or frees device
+ * memory, synchronises the device or copies group_sizes to the host (group_sizes is a
+ * run-time device value, as in the reference where the metadata is computed inside the jit,
+ * gpu_ragged_dot.py:203).  All buffers, the workspace included, are owned by the caller.
+ *
+ * Return value: RD_OK (0) when the work was enqueued, otherwise one of the RD_ERR_* codes;
+ * rd_status_string() gives the text.  Nothing throws, exits or traps.  Conditions only the
+ * device can see (a bounded wait that expired) are recorded in the workspace and read back
+ * with rd_device_status().
+ *
+ * Shapes follow the reference's signature (gpu_ragged_dot.py:362-376, README.md:52-67):
+ *   x            [m, k]      row-major, 16-bit float
+ *   A            [g, k, n]   (trans_rhs == 0)  or  [g, n, k]  (trans_rhs != 0)
+ *   group_sizes  [g]         int32, sum <= m; rows past the sum are written as zeros
+ *   y            [m, n]
+ * k and n must be multiples of 8 and every pointer 16-byte aligned (TMA strides); the Python
+ * host layer pads other shapes before calling.
+ */
+#ifndef RAGGED_DOT_B200_H_
+#define RAGGED_DOT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RD_VERSION 1
+
+enum rd_error {
+  RD_OK = 0,
+  RD_ERR_BAD_SHAPE = 1,       /* negative size, or k / n not a multiple of 8 */
+  RD_ERR_BAD_DTYPE = 2,       /* dtype is not RD_DTYPE_F16 / RD_DTYPE_BF16 */
+  RD_ERR_BAD_POINTER = 3,     /* null or not 16-byte aligned */
+  RD_ERR_WORKSPACE = 4,       /* workspace smaller than rd_workspace_bytes() */
+  RD_ERR_BAD_CONFIG = 5,      /* rd_tile_cfg names a tile the kernels do not have */
+  RD_ERR_TENSOR_MAP = 6,      /* the driver rejected a TMA descriptor */
+  RD_ERR_LAUNCH = 7,          /* cudaGetLastError() after a launch */
+  RD_ERR_DRIVER = 8,          /* driver entry point for tensor-map encoding not found */
+  RD_ERR_DEVICE_WAIT = 9      /* device status: a bounded wait inside a kernel expired */
+};
+
+enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
+
+/* Tile choice for one call; replaces the reference's block_m/block_k/block_n + tune-jax
+ * search (tuning.py:49-58).  Pass NULL to let the library choose.
+ *   tile_n   : output columns per CTA tile, one of 64, 128, 256 (tile_m is always 128,
+ *              the contraction step always 64).
+ *   max_ctas : cap on the persistent grid (0 = one CTA per SM). */
+typedef struct rd_tile_cfg {
+  int32_t tile_n;
+  int32_t max_ctas;
+} rd_tile_cfg;
+
+int rd_version(void);
+const char* rd_status_string(int code);
+
+/* Bytes of workspace rd_gmm / rd_tgmm need for a problem with m rows and g groups. */
+int rd_workspace_bytes(int m, int g, size_t* bytes);
+
+/* Group metadata: replaces _make_gmm_group_metadata (gpu_ragged_dot.py:70-90).  Writes the
+ * reference's arrays for chunk size `chunk_m`, all int32 and all on the device:
+ *   group_offsets[g], row_it2group[U], row_it2it_in_group[U], total_row_its[1],
+ *   U = ceil(m / chunk_m) + g; entries past total_row_its are 0.  Any output may be NULL. */
+int rd_metadata(const int32_t* group_sizes, int g, int m, int chunk_m, int32_t* group_offsets,
+                int32_t* row_it2group, int32_t* row_it2it_in_group, int32_t* total_row_its,
+                void* stream);
+
+/* Forward grouped GEMM; replaces _gpu_gmm_fwd + _gpu_gmm_kernel (gpu_ragged_dot.py:93-228).
+ * With trans_rhs it is also the dlhs half of the backward pass (gpu_ragged_dot.py:400).
+ * k is x's second dimension (the contraction), n the output's. */
+int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, void* workspace,
+           size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
+           const rd_tile_cfg* cfg, void* stream);
+
+/* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
+ * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass
+ * (gpu_ragged_dot.py:401).  Empty groups produce zero blocks. */
+int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+            void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
+            const rd_tile_cfg* cfg, void* stream);
+
+/* Synchronises `stream`, reads the device status word of `workspace` and returns RD_OK or
+ * RD_ERR_DEVICE_WAIT.  For tests and debugging; the hot path never calls it. */
+int rd_device_status(const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RAGGED_DOT_B200_H_ */

@@ -1,0 +1,307 @@
+"""GPU parity tests: the CUDA path (through the C ABI, via the Python host layer) against the
+CPU oracle on the same seeded inputs.
+
+Tolerances: elementwise |a-b| <= 2e-2 + 2e-2*|b| for bf16 inputs with fp32 accumulation, and
+the reference's own relative-L2 gates (tests.py:127,144,168,183): 5e-3 per row for gmm and its
+gradients, 2e-3 per group for tgmm.  Group metadata must match bit for bit.
+"""
+
+import itertools
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_ragged_dot_b200 as rd
+from gpu_ragged_dot_b200 import _lib, ops, workloads
+from oracle import ragged_dot_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 2e-2
+EPS_ROWS_BF16 = 5e-3
+EPS_GROUPS_BF16 = 2e-3
+DEV = "cuda:0"
+
+
+def _assert_close(got, want, what):
+    ok, worst = oracle.allclose_report(got, want, RTOL, ATOL)
+    assert ok, f"{what}: elementwise rtol/atol 2e-2 violated, worst ratio {worst:.3f}"
+
+
+def _inputs(seed, m, k, n, g, dtype=torch.bfloat16, random_inputs=True):
+    if random_inputs:
+        x = oracle.reference_normal(seed * 7 + 1, (m, k), dtype)
+        A = oracle.reference_normal(seed * 7 + 2, (g, k, n), dtype)
+        dout = oracle.reference_normal(seed * 7 + 3, (m, n), dtype)
+    else:
+        x, A, dout = (torch.ones(s, dtype=dtype) for s in ((m, k), (g, k, n), (m, n)))
+    return x, A, dout
+
+
+def _to_dev(*ts):
+    return tuple(t.to(DEV) for t in ts)
+
+
+# ------------------------------------------------------------------ metadata (bit exact)
+META_CASES = [
+    ([5, 0, 12, 3, 0, 0, 9, 1], 32, 8),
+    ([0, 0, 0, 0], 16, 8),
+    ([128], 128, 128),
+    ([127, 1, 128, 129, 0, 255], 640, 128),
+    ([512, 0, 0, 512], 1024, 512),
+    ([3] * 300, 1024, 8),
+]
+
+
+@pytest.mark.parametrize("gs,m,chunk", META_CASES)
+def test_metadata_bit_exact(gs, m, chunk):
+    want = oracle.make_group_metadata(gs, m, chunk)
+    got = rd.make_group_metadata(torch.tensor(gs, dtype=torch.int32, device=DEV), m, chunk)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.group_offsets.cpu().numpy(), want.group_offsets)
+    assert np.array_equal(got.row_it2group.cpu().numpy(), want.row_it2group)
+    assert np.array_equal(got.row_it2it_in_group.cpu().numpy(), want.row_it2it_in_group)
+    assert int(got.total_row_its.cpu()) == int(want.total_row_its)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+@pytest.mark.parametrize("g,m,chunk", [(8, 8192, 128), (256, 32768, 128), (64, 256, 128), (2500, 40000, 64)])
+def test_metadata_random_bit_exact(seed, g, m, chunk):
+    rng = np.random.default_rng(seed)
+    gs = rng.multinomial(int(m * 0.9), rng.dirichlet(0.3 * np.ones(g))).astype(np.int32)
+    want = oracle.make_group_metadata(gs, m, chunk)
+    got = rd.make_group_metadata(torch.from_numpy(gs).to(DEV), m, chunk)
+    assert np.array_equal(got.group_offsets.cpu().numpy(), want.group_offsets)
+    assert np.array_equal(got.row_it2group.cpu().numpy(), want.row_it2group)
+    assert np.array_equal(got.row_it2it_in_group.cpu().numpy(), want.row_it2it_in_group)
+    assert int(got.total_row_its.cpu()) == int(want.total_row_its)
+
+
+# ------------------------------------------------------------------ forward
+def _check_gmm(x, A, gs, trans_rhs=False, cfg=None, what="gmm"):
+    gs_t = torch.as_tensor(gs, dtype=torch.int32)
+    want = oracle.ragged_dot(x, A, gs_t, trans_rhs=trans_rhs)
+    xd, Ad, gd = _to_dev(x, A, gs_t)
+    m, g = x.shape[0], A.shape[0]
+    ws = ops._workspace(m, g, xd.device)
+    got = ops.gmm_forward(xd, Ad, gd, trans_rhs=trans_rhs, cfg=cfg, workspace=ws)
+    assert ops.device_status(ws) == 0, "device reported an expired wait"
+    got = got.cpu()
+    total = int(min(int(np.sum(np.maximum(np.asarray(gs), 0))), m))
+    _assert_close(got, want, what)
+    err = oracle.rel_l2_err(got, want, axis=-1, mask=torch.arange(m) < total)
+    assert float(err.max()) < EPS_ROWS_BF16, f"{what}: rel-L2 per row {float(err.max()):.2e}"
+    if total < m:
+        assert not bool(got[total:].float().abs().max() > 0), f"{what}: rows past sum(group_sizes) not zero"
+    return got
+
+
+def _check_tgmm(x, dout, gs, cfg=None, what="tgmm"):
+    gs_t = torch.as_tensor(gs, dtype=torch.int32)
+    want = oracle.trans_ragged_dot(x, dout, gs_t)
+    xd, dd, gd = _to_dev(x, dout, gs_t)
+    m, g = x.shape[0], gs_t.numel()
+    ws = ops._workspace(m, g, xd.device)
+    got = ops.tgmm_forward(xd, dd, gd, cfg=cfg, workspace=ws)
+    assert ops.device_status(ws) == 0, "device reported an expired wait"
+    got = got.cpu()
+    _assert_close(got, want, what)
+    err = oracle.rel_l2_err(got, want, axis=(-1, -2), mask=gs_t != 0)
+    assert float(err.max()) < EPS_GROUPS_BF16, f"{what}: rel-L2 per group {float(err.max()):.2e}"
+    empty = (gs_t == 0).nonzero().flatten().tolist()
+    for gi in empty:
+        assert not bool(got[gi].float().abs().max() > 0), f"{what}: empty group {gi} not zero"
+    return got
+
+
+def test_small_config_forward_backward():
+    s = workloads.SMALL
+    gs = workloads.group_sizes_small(0)
+    assert gs.sum() == s.m and (gs == 0).any()
+    rng_x = oracle.reference_normal(101, (s.m, s.k), torch.bfloat16)
+    A = (oracle.reference_normal(102, (s.g, s.k, s.n), torch.float32) / s.k ** 0.5).to(torch.bfloat16)
+    dout = oracle.reference_normal(103, (s.m, s.n), torch.bfloat16)
+    _check_gmm(rng_x, A, gs, what="small fwd")
+    _check_gmm(dout, A, gs, trans_rhs=True, what="small dlhs")
+    _check_tgmm(rng_x, dout, gs, what="small drhs")
+
+
+def _reference_grid(samples, seed=1234):
+    grid = dict(
+        m=[128, 256, 171], k=[256, 512, 58], n=[64, 128, 77], g=[8, 16],
+        fill_in=[1.0, 0.7, 0.5], seed=[0, 1], random_inputs=[True, False],
+    )
+    keys = list(grid)
+    prod = list(itertools.product(*grid.values()))
+    random.Random(seed).shuffle(prod)
+    return [dict(zip(keys, v)) for v in prod[:samples]]
+
+
+GRID = _reference_grid(24)
+
+
+@pytest.mark.parametrize("case", GRID, ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_reference_grid_forward(case):
+    m, k, n, g = case["m"], case["k"], case["n"], case["g"]
+    x, A, _ = _inputs(case["seed"], m, k, n, g, random_inputs=case["random_inputs"])
+    target_m = max(min(round(m * case["fill_in"]), m), 0)
+    gs = oracle.reference_group_sizes(case["seed"] + 17, g, target_m)
+    _check_gmm(x, A, gs, what="grid fwd")
+
+
+@pytest.mark.parametrize("case", GRID[:12], ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_reference_grid_trans_rhs(case):
+    m, k, n, g = case["m"], case["k"], case["n"], case["g"]
+    x, A, _ = _inputs(case["seed"], m, k, n, g, random_inputs=case["random_inputs"])
+    target_m = max(min(round(m * case["fill_in"]), m), 0)
+    gs = oracle.reference_group_sizes(case["seed"] + 17, g, target_m)
+    _check_gmm(x, A.transpose(1, 2).contiguous(), gs, trans_rhs=True, what="grid fwd trans_rhs")
+
+
+@pytest.mark.parametrize("case", GRID[:16], ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_reference_grid_trans_ragged_dot(case):
+    m, k, n, g = case["m"], case["k"], case["n"], case["g"]
+    x, _, dout = _inputs(case["seed"], m, k, n, g, random_inputs=case["random_inputs"])
+    target_m = max(min(round(m * case["fill_in"]), m), 0)
+    gs = oracle.reference_group_sizes(case["seed"] + 17, g, target_m)
+    _check_tgmm(x, dout, gs, what="grid tgmm")
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("trans_rhs", [False, True])
+def test_every_tile_width(tile_n, trans_rhs):
+    m, k, n, g = 700, 320, 520, 5
+    x, A, dout = _inputs(3, m, k, n, g)
+    gs = [130, 0, 257, 1, 300]
+    cfg = _lib.TileCfg(tile_n, 0)
+    Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
+    _check_gmm(x, Aa, gs, trans_rhs=trans_rhs, cfg=cfg, what=f"tile_n={tile_n}")
+    if not trans_rhs:
+        _check_tgmm(x, dout, gs, cfg=cfg, what=f"tgmm tile_n={tile_n}")
+
+
+def test_group_boundaries_every_residue():
+    """Group sizes 1..40 and 120..136: every boundary residue around the 64-row reduction
+    step and the 128-row tile."""
+    sizes = list(range(1, 41)) + list(range(120, 137))
+    m, k, n = sum(sizes) + 5, 128, 64
+    x, A, dout = _inputs(5, m, k, n, len(sizes))
+    _check_gmm(x, A, sizes, what="residues fwd")
+    _check_tgmm(x, dout, sizes, what="residues tgmm")
+
+
+def test_all_groups_empty():
+    m, k, n, g = 200, 64, 72, 4
+    x, A, dout = _inputs(7, m, k, n, g)
+    got = _check_gmm(x, A, [0, 0, 0, 0], what="all-empty fwd")
+    assert float(got.float().abs().max()) == 0.0
+    got = _check_tgmm(x, dout, [0, 0, 0, 0], what="all-empty tgmm")
+    assert float(got.float().abs().max()) == 0.0
+
+
+def test_single_giant_group():
+    m, k, n, g = 1500, 256, 264, 3
+    x, A, dout = _inputs(9, m, k, n, g)
+    _check_gmm(x, A, [0, 1500, 0], what="giant fwd")
+    _check_tgmm(x, dout, [0, 1500, 0], what="giant tgmm")
+
+
+def test_nan_rows_outside_groups_do_not_leak():
+    """Rows past sum(group_sizes) may hold anything (here NaN): they must not reach any output."""
+    m, k, n, g = 300, 128, 128, 3
+    x, A, dout = _inputs(11, m, k, n, g)
+    gs = [70, 50, 33]
+    x[153:] = float("nan")
+    dout[153:] = float("nan")
+    got = _check_gmm(x, A, gs, what="nan-tail fwd")
+    assert torch.isfinite(got.float()).all()
+    got = _check_tgmm(x, dout, gs, what="nan-tail tgmm")
+    assert torch.isfinite(got.float()).all()
+
+
+def test_float16_inputs():
+    m, k, n, g = 256, 128, 192, 4
+    x, A, dout = _inputs(13, m, k, n, g, dtype=torch.float16)
+    A = (A.float() / k ** 0.5).to(torch.float16)
+    _check_gmm(x, A, [64, 100, 0, 92], what="fp16 fwd")
+    _check_tgmm(x, (dout.float() / 8).to(torch.float16), [64, 100, 0, 92], what="fp16 tgmm")
+
+
+# ------------------------------------------------------------------ custom VJP wiring
+@pytest.mark.parametrize("trans_rhs", [False, True])
+def test_vjp_matches_oracle(trans_rhs):
+    m, k, n, g = 384, 256, 192, 6
+    x, A, dout = _inputs(21, m, k, n, g)
+    A = (A.float() / k ** 0.5).to(torch.bfloat16)
+    gs = torch.tensor([100, 0, 37, 128, 60, 40], dtype=torch.int32)
+    Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
+    dx_ref, dA_ref = oracle.ragged_dot_vjp(x, Aa, gs, dout, trans_rhs=trans_rhs)
+    xd, Ad, dd, gd = _to_dev(x, Aa, dout, gs)
+    xd.requires_grad_(True)
+    Ad.requires_grad_(True)
+    y = rd.ragged_dot(xd, Ad, gd, block_m=32, block_k=32, block_n=32, trans_rhs=trans_rhs)
+    y.backward(dd)
+    total = int(gs.sum())
+    _assert_close(y.detach().cpu(), oracle.ragged_dot(x, Aa, gs, trans_rhs=trans_rhs), "vjp fwd")
+    _assert_close(xd.grad.cpu(), dx_ref, "dlhs")
+    _assert_close(Ad.grad.cpu(), dA_ref, "drhs")
+    e = oracle.rel_l2_err(xd.grad.cpu(), dx_ref, axis=-1, mask=torch.arange(m) < total)
+    assert float(e.max()) < EPS_ROWS_BF16
+    e = oracle.rel_l2_err(Ad.grad.cpu(), dA_ref, axis=(-1, -2), mask=gs != 0)
+    assert float(e.max()) < EPS_ROWS_BF16
+
+
+def test_tgmm_vjp_matches_oracle():
+    m, k, n, g = 256, 128, 64, 4
+    x, _, y = _inputs(23, m, k, n, g)
+    gs = torch.tensor([60, 0, 100, 96], dtype=torch.int32)
+    dA = oracle.reference_normal(99, (g, k, n), torch.bfloat16)
+    dx_ref = oracle.ragged_dot(y, dA, gs, trans_rhs=True)
+    dy_ref = oracle.ragged_dot(x, dA, gs, trans_rhs=False)
+    xd, yd, gd, dAd = _to_dev(x, y, gs, dA)
+    xd.requires_grad_(True)
+    yd.requires_grad_(True)
+    out = rd.trans_ragged_dot(xd, yd, gd)
+    out.backward(dAd)
+    _assert_close(xd.grad.cpu(), dx_ref, "tgmm dx")
+    _assert_close(yd.grad.cpu(), dy_ref, "tgmm dy")
+
+
+def test_interpret_and_dtype_arguments_raise():
+    x = torch.zeros(8, 8, dtype=torch.bfloat16, device=DEV)
+    A = torch.zeros(1, 8, 8, dtype=torch.bfloat16, device=DEV)
+    gs = torch.tensor([8], dtype=torch.int32, device=DEV)
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, interpret=True)
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, acc_dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        rd.gmm(x.cpu(), A, gs)
+
+
+# ------------------------------------------------------------------ full-size properties
+def test_mixtral_shape_properties():
+    """At the benchmark size the oracle is too slow for a full comparison: check a sample of
+    rows against it, linearity in x, and the zero tail."""
+    s = workloads.MIXTRAL
+    gs_np = workloads.group_sizes_mixtral_ragged(0)
+    gs_np[-1] -= 200  # leave a tail of unowned rows
+    x, A, _ = workloads.make_inputs(s, DEV, seed=0, with_dout=False)
+    gs = torch.from_numpy(gs_np).to(DEV)
+    y = ops.gmm_forward(x, A, gs)
+    y2 = ops.gmm_forward(x * 2, A, gs)
+    torch.cuda.synchronize()
+    total = int(gs_np.sum())
+    assert float(y[total:].float().abs().max()) == 0.0
+    # exact linearity under scaling by a power of two
+    assert torch.equal((y.float() * 2).to(torch.bfloat16), y2)
+    # sampled rows against the oracle
+    rng = np.random.default_rng(0)
+    rows = np.sort(rng.choice(total, size=64, replace=False))
+    offs = np.concatenate([[0], np.cumsum(gs_np)])
+    for r in rows:
+        gi = int(np.searchsorted(offs, r, side="right") - 1)
+        want = (x[r].float().cpu() @ A[gi].float().cpu()).to(torch.bfloat16)
+        _assert_close(y[r].cpu(), want, f"mixtral row {r}")
