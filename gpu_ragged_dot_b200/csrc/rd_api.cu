@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include <mutex>
 
@@ -59,7 +60,16 @@ int encode_map(CUtensorMap* map, const void* base, int dtype, int rank, const ui
   CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides,
                   gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? RD_OK : RD_ERR_TENSOR_MAP;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "ragged_dot_b200: cuTensorMapEncodeTiled failed (CUresult %d): base=%p rank=%d "
+            "dims={%llu,%llu,%llu} box={%u,%u,%u}\n",
+            static_cast<int>(r), base, rank, (unsigned long long)gdims[0],
+            (unsigned long long)gdims[1], (unsigned long long)(rank > 2 ? gdims[2] : 0), gbox[0],
+            gbox[1], rank > 2 ? gbox[2] : 0u);
+    return RD_ERR_TENSOR_MAP;
+  }
+  return RD_OK;
 }
 
 // ------------------------------------------------------------------ device properties
@@ -218,6 +228,13 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
   int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n((m + rd::kTileM - 1) / rd::kTileM, n, sms);
   if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
 
+  // Launch the metadata kernel before encoding the tensor maps: besides being the first step
+  // of the call, a runtime launch binds the device's primary context to the calling thread,
+  // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
+  // arrive here without one).
+  launch_internal_metadata(group_sizes, g, m, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
@@ -237,9 +254,6 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
     rc = encode_map(&tb, A, dtype, 3, dims, box);
   }
   if (rc != RD_OK) return rc;
-
-  launch_internal_metadata(group_sizes, g, m, w, stream);
-  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   GemmArgs args;
   args.m = m; args.k = k; args.n = n; args.g = g;
@@ -289,6 +303,13 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(k_tiles * g, n, sms);
   if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
 
+  // Launch the metadata kernel before encoding the tensor maps: besides being the first step
+  // of the call, a runtime launch binds the device's primary context to the calling thread,
+  // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
+  // arrive here without one).
+  launch_internal_metadata(group_sizes, g, m, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
@@ -302,9 +323,6 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
     rc = encode_map(&tb, dout, dtype, 2, dims, box);
     if (rc != RD_OK) return rc;
   }
-
-  launch_internal_metadata(group_sizes, g, m, w, stream);
-  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   GemmArgs args;
   args.m = m; args.k = k; args.n = n; args.g = g;
