@@ -1,0 +1,483 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged-dot hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--only fwd|dlhs|drhs] [--no-e2e] [--no-cpu-baseline]
+
+One JSON line on stdout (rank 0).  N = 1: one step is ragged_dot forward + its full backward
+(dlhs through the transposed grouped GEMM, drhs through tgmm) on the Mixtral-8x7B-shaped
+workload, m=8192, k=4096, n=14336, g=8, bf16 with fp32 accumulation; `value` counts useful
+flops, 2*m*k*n per GEMM.  N > 1 (torchrun): the expert-parallel workload -- per GPU 8192
+tokens x top-4 routing over 64 experts sharded 64/N per GPU, NCCL all-to-all of the rows, then
+the local ragged_dot.
+
+`--impl reference` times the CPU oracle (oracle/ragged_dot_oracle.py, the restatement of the
+reference semantics; jax is not installed, so jax.lax.ragged_dot on XLA-CPU cannot run) on a
+bounded sample of the same workload with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel on this workload, from
+# the ncu captures summarised in profiles/ragged_gemm_mixtral_m8192_k4096_n14336_g8.md.
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = {"fwd": 1.038238e9 + 229.12128e6, "dlhs": 1.501015e9 + 68.167168e6,
+                                 "drhs": 1.002836e9 + 887.103488e6}
+
+METRIC = "ragged_dot fwd+bwd TFLOP/s (2*m*k*n useful flops per GEMM)"
+UNIT = "TFLOP/s"
+
+
+# ---------------------------------------------------------------------------- helpers
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {
+            "bf16_tflops": float(p["bf16_tflops"]),
+            "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+            "hbm_gbs": float(p["hbm_gbs"]),
+            "source": "measured",
+        }
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index = index
+        self.period = period_s
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+            return self
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def _run(self):
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ---------------------------------------------------------------------------- reference arm (CPU)
+def cpu_oracle_sample(shape, rows, threads, seed=0):
+    """Inputs for a CPU run on the first `rows` rows of the workload (group sizes scaled)."""
+    from gpu_ragged_dot_b200 import workloads
+
+    gs_full = workloads.group_sizes_mixtral_ragged(seed).astype(np.int64)
+    gs = (gs_full * rows) // shape.m
+    gs[-1] += rows - gs.sum()
+    x = workloads.normal_tensor((rows, shape.k), 1.0, 11, "cpu")
+    A = workloads.normal_tensor((shape.g, shape.k, shape.n), shape.k ** -0.5, 12, "cpu")
+    dout = workloads.normal_tensor((rows, shape.n), 1.0, 13, "cpu")
+    return x, A, dout, torch.from_numpy(gs.astype(np.int32))
+
+
+def cpu_oracle_step(x, A, dout, gs, only=None):
+    from oracle import ragged_dot_oracle as oracle
+
+    if only in (None, "fwd"):
+        oracle.ragged_dot(x, A, gs, native_16bit=True)
+    if only in (None, "dlhs"):
+        oracle.ragged_dot(dout, A, gs, trans_rhs=True, native_16bit=True)
+    if only in (None, "drhs"):
+        oracle.trans_ragged_dot(x, dout, gs, native_16bit=True)
+
+
+def run_reference(args):
+    from gpu_ragged_dot_b200 import workloads
+
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    shape = workloads.MIXTRAL
+    threads = torch.get_num_threads()
+    gemms = 3 if args.only is None else 1
+    # Calibrate on 128 rows, then size the per-step sample so warmup+steps stay near 2 minutes.
+    x, A, dout, gs = cpu_oracle_sample(shape, 128, threads)
+    t0 = time.perf_counter()
+    cpu_oracle_step(x, A, dout, gs, args.only)
+    t_probe = time.perf_counter() - t0
+    budget = 120.0 / max(args.steps + args.warmup, 1)
+    rows = int(min(shape.m, max(128, 128 * budget / max(t_probe, 1e-3))))
+    rows = max(128, (rows // 128) * 128)
+    x, A, dout, gs = cpu_oracle_sample(shape, rows, threads)
+    for _ in range(args.warmup):
+        cpu_oracle_step(x, A, dout, gs, args.only)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_step(x, A, dout, gs, args.only)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    flops = 2.0 * rows * shape.k * shape.n * gemms
+    value = flops / dt / 1e12
+    sample = (f"rows 0..{rows - 1} of {shape.m} (group sizes scaled), all {shape.g} experts' weights, "
+              f"{'fwd+dlhs+drhs' if args.only is None else args.only} per step; torch CPU bf16 matmul (oneDNN, fp32 accumulate) per group")
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": dt * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": shape.name + "_fwd_bwd", "m": shape.m, "k": shape.k, "n": shape.n,
+                   "g": shape.g, "reference": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------- our arm, N = 1
+def run_single(args):
+    from gpu_ragged_dot_b200 import _lib, ops, workloads
+    import gpu_ragged_dot_b200 as rd
+
+    _lib.load()  # fail loudly if the CUDA library is missing
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = workloads.MIXTRAL
+    peaks = measured_peaks()
+    kernels = ["fwd", "dlhs", "drhs"] if args.only is None else [args.only]
+    # Allocate only what the selected kernels touch (keeps profiler captures small).
+    x, A, dout = workloads.make_inputs(shape, dev, seed=0, with_dout=kernels != ["fwd"])
+    if kernels == ["dlhs"]:
+        x = None
+    if kernels == ["drhs"]:
+        A = None
+    gs_fwd = torch.from_numpy(workloads.group_sizes_mixtral(0)).to(dev)
+    gs_bwd = torch.from_numpy(workloads.group_sizes_mixtral_ragged(0)).to(dev)
+    y = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev) if "fwd" in kernels else None
+    dx = torch.empty((shape.m, shape.k), dtype=torch.bfloat16, device=dev) if "dlhs" in kernels else None
+    dA = (torch.empty((shape.g, shape.k, shape.n), dtype=torch.bfloat16, device=dev)
+          if "drhs" in kernels else None)
+    ws = ops._workspace(shape.m, shape.g, dev)
+
+    def launch(name):
+        if name == "fwd":
+            ops.gmm_forward(x, A, gs_fwd, out=y, workspace=ws)
+        elif name == "dlhs":
+            ops.gmm_forward(dout, A, gs_bwd, trans_rhs=True, out=dx, workspace=ws)
+        else:
+            ops.tgmm_forward(x, dout, gs_bwd, out=dA, workspace=ws)
+
+    for _ in range(max(args.warmup, 3)):
+        for name in kernels:
+            launch(name)
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream(dev)
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(kernels) + 1)] for _ in range(args.steps)]
+    sampler = ClockSampler(physical_gpu_index(0)).start()
+    torch.cuda.synchronize()
+    for s in range(args.steps):
+        marks[s][0].record(stream)
+        for i, name in enumerate(kernels):
+            launch(name)
+            marks[s][i + 1].record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    status = ops.device_status(ws)
+    if status != 0:
+        raise RuntimeError(f"device status {status} after the timed region")
+
+    total_ms = marks[0][0].elapsed_time(marks[-1][-1])
+    ms_per_step = total_ms / args.steps
+    per_kernel_ms = {
+        name: sum(marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(args.steps)) / args.steps
+        for i, name in enumerate(kernels)
+    }
+    gemm_flops = 2.0 * shape.m * shape.k * shape.n
+    value = gemm_flops * len(kernels) / (ms_per_step * 1e-3) / 1e12
+
+    # roofline of the dominant (slowest) kernel; every GEMM here is tensor-bound (AI ~ 775 flop/B)
+    dom = max(per_kernel_ms, key=per_kernel_ms.get)
+    per_kernel = {}
+    for name, ms in per_kernel_ms.items():
+        tf = gemm_flops / (ms * 1e-3) / 1e12
+        per_kernel[name] = {"ms": ms, "tflops": tf, "frac_of_measured_burst": tf / peaks["bf16_tflops"],
+                            "frac_of_measured_sustained": tf / peaks["bf16_tflops_sustained"]}
+    traffic = DRAM_TRAFFIC_BYTES_PER_LAUNCH
+    roofline = {
+        "bound": "tensor",
+        "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
+                   "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
+        "achieved": per_kernel[dom]["tflops"],
+        "peak": peaks["bf16_tflops"],
+        "peak_source": f"{peaks['source']} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
+        "unit": "TFLOP/s",
+        "frac": per_kernel[dom]["tflops"] / peaks["bf16_tflops"],
+        "frac_of_sustained": per_kernel[dom]["tflops"] / peaks["bf16_tflops_sustained"],
+        "traffic": traffic.get(dom),
+        "algorithmic_flops_per_launch": gemm_flops,
+        "algorithmic_bytes_per_launch": 2.0 * (shape.m * shape.k + shape.g * shape.k * shape.n + shape.m * shape.n),
+        "per_kernel": per_kernel,
+    }
+
+    line = {
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": shape.name + ("_fwd_bwd" if args.only is None else "_" + args.only),
+            "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
+            "group_sizes": "fwd: multinomial(Dirichlet(2)); bwd: same, each group at a random offset mod 128",
+            "l2": "inputs larger than L2 (weights 940 MB per GEMM)",
+            "timing": "CUDA events on the launch stream; per-kernel events inside the timed region",
+        },
+        "clocks": clocks,
+        "gpu_launches": 2 * len(kernels) * args.steps,
+        "roofline": roofline,
+    }
+
+    if not args.no_e2e and args.only is None:
+        line["e2e"] = run_e2e(args, shape, dev, rd, x, A, dout, gs_fwd, kernels)
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = run_cpu_baseline(shape, kernels)
+    print(json.dumps(line), flush=True)
+
+
+def run_e2e(args, shape, dev, rd, x, A, dout, gs, kernels):
+    """Same step through the public API with host buffers: pinned H2D of x, A, group_sizes and
+    dout, ragged_dot + backward on the device, D2H of y, dlhs and drhs -- all inside the timed
+    region."""
+    full = len(kernels) == 3
+    hx, hA, hd = (t.cpu().pin_memory() for t in (x, A, dout))
+    hgs = gs.cpu().pin_memory()
+    hy = torch.empty((shape.m, shape.n), dtype=torch.bfloat16).pin_memory()
+    hdx = torch.empty_like(hx).pin_memory()
+    hdA = torch.empty_like(hA).pin_memory()
+    steps = max(2, min(args.steps, 5))
+
+    def step():
+        dx_ = hx.to(dev, non_blocking=True)
+        dA_ = hA.to(dev, non_blocking=True)
+        dg_ = hgs.to(dev, non_blocking=True)
+        if full:
+            dd_ = hd.to(dev, non_blocking=True)
+            dx_.requires_grad_(True)
+            dA_.requires_grad_(True)
+        yv = rd.ragged_dot(dx_, dA_, dg_)
+        if full:
+            yv.backward(dd_)
+            hdx.copy_(dx_.grad, non_blocking=True)
+            hdA.copy_(dA_.grad, non_blocking=True)
+        hy.copy_(yv.detach(), non_blocking=True)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = lambda t: t.numel() * t.element_size()
+    h2d = nbytes(hx) + nbytes(hA) + nbytes(hgs) + (nbytes(hd) if full else 0)
+    d2h = nbytes(hy) + ((nbytes(hdx) + nbytes(hdA)) if full else 0)
+    flops = 2.0 * shape.m * shape.k * shape.n * (3 if full else 1)
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "gpu_ragged_dot_b200.ragged_dot + autograd backward, pinned host buffers"}
+
+
+def run_cpu_baseline(shape, kernels):
+    threads = torch.get_num_threads()
+    rows = 4096
+    x, A, dout, gs = cpu_oracle_sample(shape, rows, threads)
+    only = None if len(kernels) == 3 else kernels[0]
+    cpu_oracle_step(x[:128], A, dout[:128], torch.tensor([16] * shape.g, dtype=torch.int32), only)  # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 3 and time.perf_counter() - t0 < 20.0:
+        cpu_oracle_step(x, A, dout, gs, only)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    flops = 2.0 * rows * shape.k * shape.n * len(kernels)
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+            "host_cpus": os.cpu_count(),
+            "sample": f"rows 0..{rows - 1} of {shape.m} (group sizes scaled 1/{shape.m // rows}), all {shape.g} "
+                      f"experts' weights, {'+'.join(kernels)} x{reps}; oracle = torch CPU bf16 matmul (oneDNN, fp32 accumulate) per group"}
+
+
+# ---------------------------------------------------------------------------- our arm, N > 1
+def run_expert_parallel(args):
+    import torch.distributed as dist
+    from gpu_ragged_dot_b200 import _lib, ep, workloads
+
+    _lib.load()
+    rank, world, local = dist_env()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    shape = workloads.EP_PREFILL
+    tokens, top_k, experts = 8192, 4, shape.g
+    layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank)
+    x_tokens = workloads.normal_tensor((tokens, shape.k), 1.0, 1000 + rank, dev)
+    routing = torch.from_numpy(workloads.topk_routing(tokens, experts, top_k, seed=3000 + rank)).to(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(x_tokens, routing)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local)).start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    layer.reset_timers()
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward(x_tokens, routing, timed=True)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    parts = layer.timers_ms(args.steps)
+    t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"]], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, gemm_ms, a2a_ms, permute_ms = t.tolist()
+    rows_global = tokens * top_k * world
+    flops = 2.0 * rows_global * shape.k * shape.n
+    peaks = measured_peaks()
+    if rank == 0:
+        gemm_tf = 2.0 * tokens * top_k * shape.k * shape.n / (gemm_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"expert_parallel_fwd_{shape.name}_w{world}", "tokens_per_gpu": tokens,
+                       "top_k": top_k, "experts": experts, "experts_per_gpu": experts // world,
+                       "k": shape.k, "n": shape.n, "collective": "NCCL all-to-all (rows) + all-to-all (counts)",
+                       "l2": "inputs larger than L2 (268 MB of rows per GPU)"},
+            "clocks": clocks,
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "ragged_gemm_kernel<gmm> (local experts)",
+                         "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": gemm_tf / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"]},
+            "breakdown_ms": {"permute_gather": permute_ms, "all_to_all": a2a_ms, "local_ragged_dot": gemm_ms},
+            "all_to_all_GBps_per_gpu": (tokens * top_k * shape.k * 2 * (world - 1) / world) / (a2a_ms * 1e-3) / 1e9,
+            "e2e": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, choices=["fwd", "dlhs", "drhs"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU oracle)")
+    _, world, _ = dist_env()
+    if world > 1 or args.gpus > 1:
+        run_expert_parallel(args)
+    else:
+        run_single(args)
+
+
+if __name__ == "__main__":
+    main()
