@@ -305,3 +305,41 @@ def test_mixtral_shape_properties():
         gi = int(np.searchsorted(offs, r, side="right") - 1)
         want = (x[r].float().cpu() @ A[gi].float().cpu()).to(torch.bfloat16)
         _assert_close(y[r].cpu(), want, f"mixtral row {r}")
+
+
+# ------------------------------------------------------------------ against the reference's own outputs
+from tests import golden_io  # noqa: E402
+
+GOLDEN = golden_io.gemm_cases()
+
+
+@pytest.mark.parametrize("case", GOLDEN, ids=lambda c: c["name"])
+def test_cuda_matches_reference_golden(case):
+    """The CUDA path against outputs produced by the reference's own kernels
+    (tests/golden/make_golden.py)."""
+    gs = case["group_sizes"]
+    x, A, dout, gd = _to_dev(case["x"], case["A"], case["dout"], gs)
+    At = A.transpose(1, 2).contiguous()
+    pairs = [
+        ("y", ops.gmm_forward(x, A, gd), case["y"]),
+        ("y_trans_rhs", ops.gmm_forward(x, At, gd, trans_rhs=True), case["y_trans_rhs"]),
+        ("tgmm", ops.tgmm_forward(x, dout, gd), case["tgmm"]),
+        ("dlhs", ops.gmm_forward(dout, A, gd, trans_rhs=True), case["dlhs"]),
+        ("drhs", ops.tgmm_forward(x, dout, gd), case["drhs"]),
+        ("dlhs_trans_rhs", ops.gmm_forward(dout, At, gd, trans_rhs=False), case["dlhs_trans_rhs"]),
+        ("drhs_trans_rhs", ops.tgmm_forward(dout, x, gd), case["drhs_trans_rhs"]),
+    ]
+    for name, got, want in pairs:
+        assert bool(torch.isfinite(want.float()).all())
+        _assert_close(got.cpu(), want, f"{case['name']}:{name}")
+
+
+@pytest.mark.parametrize("case", golden_io.metadata_cases(),
+                         ids=lambda c: f"gs{len(c['group_sizes'])}_m{c['m_chunk'][0]}_c{c['m_chunk'][1]}")
+def test_cuda_metadata_matches_reference_golden(case):
+    m, chunk = (int(v) for v in case["m_chunk"])
+    got = rd.make_group_metadata(torch.from_numpy(case["group_sizes"]).to(DEV), m, chunk)
+    assert np.array_equal(got.group_offsets.cpu().numpy(), case["group_offsets"])
+    assert np.array_equal(got.row_it2group.cpu().numpy(), case["row_it2group"])
+    assert np.array_equal(got.row_it2it_in_group.cpu().numpy(), case["row_it2it_in_group"])
+    assert int(got.total_row_its.cpu()) == int(case["total_row_its"])

@@ -1,0 +1,81 @@
+"""Host-side logic that needs no GPU: workload generators, tile table, static-argument
+handling and the refusal to run on CPU tensors."""
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_ragged_dot_b200 as rd
+from gpu_ragged_dot_b200 import ops, tile_table, workloads
+
+
+def test_group_size_generators():
+    gs = workloads.group_sizes_small(0)
+    assert gs.sum() == 512 and gs.size == 8 and (gs == 0).any() and gs.dtype == np.int32
+    gs = workloads.group_sizes_mixtral(0)
+    assert gs.sum() == 8192 and gs.size == 8 and gs.min() > 0
+    r = workloads.group_sizes_mixtral_ragged(0)
+    assert r.sum() == 8192 and (r[:-1] % 128 != 0).all()
+    d = workloads.group_sizes_deepseek(0)
+    assert d.sum() == 32768 and d.size == 256
+    assert 0.05 < (d == 0).mean() < 0.45 and d.max() > 5 * d.mean()
+    # same seed, same sizes
+    assert np.array_equal(workloads.group_sizes_deepseek(0), d)
+
+
+def test_topk_routing_is_distinct_and_uniform():
+    r = workloads.topk_routing(512, 64, 4, seed=1)
+    assert r.shape == (512, 4) and r.min() >= 0 and r.max() < 64
+    assert all(len(set(row)) == 4 for row in r.tolist())
+    gs = workloads.group_sizes_from_routing(r, 64)
+    assert gs.sum() == 2048 and gs.size == 64
+
+
+def test_normal_tensor_is_seeded():
+    a = workloads.normal_tensor((64, 32), 0.5, 3, "cpu")
+    b = workloads.normal_tensor((64, 32), 0.5, 3, "cpu")
+    assert torch.equal(a, b) and a.dtype == torch.bfloat16
+    assert 0.4 < float(a.float().std()) < 0.6
+
+
+def test_tile_table_lookup(tmp_path, monkeypatch):
+    assert tile_table.lookup("gmm", 1, 8, 8, 1) is None or True  # default table loads
+    p = tmp_path / "t.json"
+    p.write_text('{"entries": [{"op": "gmm", "k": 4096, "n": 1536, "g": 64, "m_max": 512, "tile_n": 128}]}')
+    monkeypatch.setenv("RD_TILE_TABLE", str(p))
+    monkeypatch.setattr(tile_table, "_entries", None)
+    hit = tile_table.lookup("gmm", 256, 4096, 1536, 64)
+    assert hit is not None and hit.tile_n == 128 and hit.max_ctas == 0
+    assert tile_table.lookup("gmm", 1024, 4096, 1536, 64) is None
+    assert tile_table.lookup("tgmm", 256, 4096, 1536, 64) is None
+    monkeypatch.setattr(tile_table, "_entries", None)
+
+
+def test_reference_signature_is_kept():
+    import inspect
+
+    sig = inspect.signature(rd.gmm)
+    assert list(sig.parameters) == [
+        "x", "A", "group_sizes", "block_m", "block_k", "block_n", "trans_rhs", "interpret",
+        "compute_dtype", "acc_dtype", "num_warps", "num_stages", "chunk_m"]
+    assert sig.parameters["block_m"].default == 64 and sig.parameters["chunk_m"].default == 512
+    sig = inspect.signature(rd.tgmm)
+    assert list(sig.parameters) == [
+        "x", "y", "group_sizes", "block_m", "block_k", "block_n", "interpret", "compute_dtype",
+        "acc_dtype", "num_warps", "num_stages", "chunk_m"]
+    assert rd.ragged_dot is rd.gmm and rd.trans_ragged_dot is rd.tgmm
+
+
+def test_cpu_tensors_are_refused():
+    x = torch.zeros(8, 8, dtype=torch.bfloat16)
+    A = torch.zeros(1, 8, 8, dtype=torch.bfloat16)
+    gs = torch.tensor([8], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.gmm(x, A, gs)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.tgmm(x, x, gs)
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, interpret=True)
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, compute_dtype=torch.float32)
+    assert ops._torch_dtype("float32") is torch.float32
