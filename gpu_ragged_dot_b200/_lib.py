@@ -50,6 +50,10 @@ SIGNATURES = {
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
     "rd_device_status": (_c_int, [_c_void_p, _c_void_p]),
+    "rd_gmm_static_scratch": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 6 + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
 }
 
 _lock = threading.Lock()

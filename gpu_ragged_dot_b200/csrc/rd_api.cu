@@ -172,6 +172,10 @@ const char* rd_status_string(int code) {
     case RD_ERR_LAUNCH: return "kernel launch failed";
     case RD_ERR_DRIVER: return "cuTensorMapEncodeTiled entry point not available";
     case RD_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
+    case RD_ERR_TOO_LARGE:
+      return "problem too large for the built-in scratch of rd_gmm_static_scratch "
+             "(needs 4*g + 2*ceil(m/128) + 9 <= 16384 words); use rd_gmm with a workspace";
+    case RD_ERR_SCRATCH_SETUP: return "could not resolve the address of the built-in scratch array";
     default: return "unknown status";
   }
 }
@@ -357,3 +361,68 @@ int rd_device_status(const void* workspace, void* stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+//
+// Some hosts of this library can neither hand over a workspace nor create one: an operator slot
+// whose argument list is frozen to "inputs and outputs" (a legacy custom-call interface, a
+// plugin ABI defined by someone else), running inside a framework that has reserved the whole
+// device for its own allocator -- there a cudaMalloc from inside the call may fail, and where it
+// succeeds it synchronises the device and stalls every stream.  For them rd_gmm_static_scratch
+// keeps the group-metadata scratch in a fixed array inside this library's device image.
+//
+// The array costs kStaticScratchBytes (64 KiB) on every GPU that loads the library, until the
+// process exits.  It is one array per device, shared by every call: it still holds whatever the
+// previous call left there, so the header words the kernels accumulate into are cleared at the
+// start of each call, and two calls that overlap on the GPU (different streams, no ordering
+// between them) race on it -- serialise them, or use rd_gmm with separate workspaces.
+namespace {
+
+constexpr size_t kStaticScratchWords = 16384;
+constexpr size_t kStaticScratchBytes = kStaticScratchWords * sizeof(int32_t);
+
+static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchWords];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use has to be asked for, per device, with that device current.
+int static_scratch_address(int32_t** out) {
+  static std::mutex mu;
+  static int32_t* per_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RD_ERR_SCRATCH_SETUP;
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "ragged_dot_b200: cudaGetSymbolAddress(scratch) failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return RD_ERR_SCRATCH_SETUP;
+    }
+    per_device[dev] = static_cast<int32_t*>(ptr);
+  }
+  *out = per_device[dev];
+  return RD_OK;
+}
+
+}  // namespace
+
+extern "C" int rd_gmm_static_scratch(const void* x, const void* A, const int32_t* group_sizes,
+                                     void* y, int m, int k, int n, int g, int trans_rhs, int dtype,
+                                     const rd_tile_cfg* cfg, void* stream) {
+  if (m < 0 || g < 0) return RD_ERR_BAD_SHAPE;
+  WorkspaceLayout layout;
+  layout.g = g;
+  layout.max_tiles = max_row_tiles(m, g);
+  if (static_cast<size_t>(layout.total_words()) > kStaticScratchWords) return RD_ERR_TOO_LARGE;
+  int32_t* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != RD_OK) return rc;
+  // The array keeps the last call's contents: start this call's status and totals from zero.
+  if (cudaMemsetAsync(scratch, 0, 8 * sizeof(int32_t), static_cast<cudaStream_t>(stream)) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  return rd_gmm(x, A, group_sizes, y, scratch, kStaticScratchBytes, m, k, n, g, trans_rhs, dtype, cfg,
+                stream);
+}
+

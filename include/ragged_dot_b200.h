@@ -41,7 +41,9 @@ enum rd_error {
   RD_ERR_TENSOR_MAP = 6,      /* the driver rejected a TMA descriptor */
   RD_ERR_LAUNCH = 7,          /* cudaGetLastError() after a launch */
   RD_ERR_DRIVER = 8,          /* driver entry point for tensor-map encoding not found */
-  RD_ERR_DEVICE_WAIT = 9      /* device status: a bounded wait inside a kernel expired */
+  RD_ERR_DEVICE_WAIT = 9,     /* device status: a bounded wait inside a kernel expired */
+  RD_ERR_TOO_LARGE = 10,      /* rd_gmm_static_scratch: problem exceeds the built-in scratch */
+  RD_ERR_SCRATCH_SETUP = 11   /* rd_gmm_static_scratch: scratch address could not be resolved */
 };
 
 enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
@@ -83,6 +85,26 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
 int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
             void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
             const rd_tile_cfg* cfg, void* stream);
+
+/* rd_gmm for callers that cannot supply a workspace and cannot allocate one.  It has no
+ * counterpart in the reference (there XLA allocates every buffer).  Meant for an operator slot
+ * whose argument list is fixed to inputs and outputs, inside a framework that owns all device
+ * memory: a cudaMalloc made from inside such a call can fail, and when it works it synchronises
+ * the whole device.  This entry point allocates and frees nothing; the group-metadata scratch
+ * lives in a 64 KiB array built into the library's device image (held on every GPU that loads
+ * the library until the process exits).
+ *   Limit: 4*g + 2*ceil(m/128) + 9 <= 16384 (e.g. g = 256 with m up to 980,000 rows);
+ *          beyond it the call returns RD_ERR_TOO_LARGE and does nothing.
+ *   First call on each device resolves the array's device address (cudaGetSymbolAddress, with
+ *          that device current); make that first call outside any stream capture.
+ *   The array is shared by all calls on a device and keeps the previous call's contents; the
+ *          words that must start at zero are cleared on `stream` at the start of every call.
+ *          Calls that can overlap on the GPU race on it: keep them on one stream or order them.
+ * Arguments and results otherwise exactly as rd_gmm; the device status is not readable through
+ * rd_device_status (there is no caller-visible workspace). */
+int rd_gmm_static_scratch(const void* x, const void* A, const int32_t* group_sizes, void* y, int m,
+                          int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
+                          void* stream);
 
 /* Synchronises `stream`, reads the device status word of `workspace` and returns RD_OK or
  * RD_ERR_DEVICE_WAIT.  For tests and debugging; the hot path never calls it. */
