@@ -49,6 +49,13 @@ SIGNATURES = {
         + [_c_int] * 5
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
+    "rd_gmm_indexed": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_gather_rows": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]),
     "rd_device_status": (_c_int, [_c_void_p, _c_void_p]),
     "rd_gmm_static_scratch": (
         _c_int,

@@ -11,6 +11,7 @@
 #include "../../include/ragged_dot_b200.h"
 #include "rd_gemm.cuh"
 #include "rd_metadata.cuh"
+#include "rd_rows.cuh"
 
 namespace {
 
@@ -211,15 +212,19 @@ int rd_metadata(const int32_t* group_sizes, int g, int m, int chunk_m, int32_t* 
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
-int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, void* workspace,
-           size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
-           const rd_tile_cfg* cfg, void* stream_v) {
+// Shared body of rd_gmm / rd_gmm_indexed.  `num_weights` is A's leading dimension;
+// `group_to_weight` (device, [g]) is null when group i uses A[i].
+static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
+                    const int32_t* group_to_weight, int num_weights, void* y, void* workspace,
+                    size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
+                    const rd_tile_cfg* cfg, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (m < 0 || k < 0 || n < 0 || g < 0 || (k & 7) || (n & 7)) return RD_ERR_BAD_SHAPE;
+  if (m < 0 || k < 0 || n < 0 || g < 0 || num_weights < 0 || (k & 7) || (n & 7))
+    return RD_ERR_BAD_SHAPE;
   if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
   if (m == 0 || n == 0) return RD_OK;
   if (!aligned16(y)) return RD_ERR_BAD_POINTER;
-  if (g == 0 || k == 0) {  // nothing contributes: every row is a zero row
+  if (g == 0 || k == 0 || num_weights == 0) {  // nothing contributes: every row is a zero row
     cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * 2, stream);
     return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
   }
@@ -248,12 +253,12 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
   }
   if (trans_rhs) {  // A[g, n, k]: rows of k, K-major operand, one [BN][64] box per stage
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                              static_cast<uint64_t>(g)};
+                              static_cast<uint64_t>(num_weights)};
     const uint32_t box[3] = {rd::kTileK, static_cast<uint32_t>(bn), 1};
     rc = encode_map(&tb, A, dtype, 3, dims, box);
   } else {  // A[g, k, n]: rows of n, MN-major operand, [64 k][64 n] boxes
     const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
-                              static_cast<uint64_t>(g)};
+                              static_cast<uint64_t>(num_weights)};
     const uint32_t box[3] = {64, rd::kTileK, 1};
     rc = encode_map(&tb, A, dtype, 3, dims, box);
   }
@@ -271,6 +276,7 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
   args.tile2idx = w.tile2idx();
   args.tile_prefix = w.tile_prefix();
   args.totals = w.totals();
+  args.group_to_weight = group_to_weight;
   args.status = w.status();
   args.out = y;
 
@@ -283,6 +289,37 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
   if (bn == 256) return launch_gemm<256, false, false>(ta, tb, args, ctas, stream);
   if (bn == 128) return launch_gemm<128, false, false>(ta, tb, args, ctas, stream);
   return launch_gemm<64, false, false>(ta, tb, args, ctas, stream);
+}
+
+int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, void* workspace,
+           size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
+           const rd_tile_cfg* cfg, void* stream) {
+  return gmm_impl(x, A, group_sizes, nullptr, g, y, workspace, workspace_bytes, m, k, n, g, trans_rhs,
+                  dtype, cfg, stream);
+}
+
+int rd_gmm_indexed(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                   const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                   int m, int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
+                   void* stream) {
+  if (g > 0 && group_to_weight == nullptr) return RD_ERR_BAD_POINTER;
+  return gmm_impl(x, A, group_sizes, group_to_weight, num_weights, y, workspace, workspace_bytes, m, k,
+                  n, g, trans_rhs, dtype, cfg, stream);
+}
+
+int rd_gather_rows(const void* src, const int32_t* row_index, void* dst, int rows_out, int rows_in,
+                   int row_bytes, void* stream) {
+  if (rows_out < 0 || rows_in < 0 || row_bytes < 0 || (row_bytes & 15)) return RD_ERR_BAD_SHAPE;
+  if (rows_out == 0 || row_bytes == 0) return RD_OK;
+  if (!aligned16(src) || !aligned16(dst) || row_index == nullptr) return RD_ERR_BAD_POINTER;
+  const int warps_per_block = rd::kGatherThreads / 32;
+  int blocks = (rows_out + warps_per_block - 1) / warps_per_block;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  rd::gather_rows_kernel<<<blocks, rd::kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), row_index, static_cast<uint4*>(dst), rows_out, rows_in,
+      row_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
 int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
@@ -340,6 +377,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.tile2idx = w.tile2idx();
   args.tile_prefix = w.tile_prefix();
   args.totals = w.totals();
+  args.group_to_weight = nullptr;
   args.status = w.status();
   args.out = out;
 

@@ -49,12 +49,14 @@ struct GemmArgs {
   const int32_t* tile2idx;
   const int32_t* tile_prefix;
   const int32_t* totals;  // {live row tiles, min(sum(group_sizes), m)}
+  const int32_t* group_to_weight;  // gmm: weight matrix used by each group, or null (identity)
   int32_t* status;
   void* out;
 };
 
 struct TileCoord {
-  int group;   // expert index
+  int group;   // group index
+  int weight;  // gmm: index of the weight matrix this group multiplies by
   int row0;    // gmm: first row of x / y;  tgmm: first row of the group
   int rows;    // gmm: valid rows in this tile (<=128);  tgmm: rows of the group (contraction)
   int n0;      // first output column
@@ -77,6 +79,7 @@ __device__ __forceinline__ TileCoord decode_gmm_tile(const GemmArgs& p, int tile
   const int mi = local - nt * tiles_g;
   TileCoord t;
   t.group = gi;
+  t.weight = p.group_to_weight ? p.group_to_weight[gi] : gi;
   t.row0 = p.group_offsets[gi] + mi * kTileM;
   t.rows = imin(kTileM, imax(p.group_sizes[gi], 0) - mi * kTileM);
   t.rows = imin(t.rows, p.m - t.row0);  // never touch rows past m
@@ -94,6 +97,7 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile(const GemmArgs& p, int til
   const int nt = rem - kt * p.n_tiles;
   TileCoord t;
   t.group = gi;
+  t.weight = gi;
   t.row0 = p.group_offsets[gi];
   t.rows = imax(imin(imax(p.group_sizes[gi], 0), p.m - t.row0), 0);
   t.n0 = nt;
@@ -207,11 +211,11 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else {
             tma_load_2d(sa, &tmap_a, full, kb * kTileK, t.row0);
             if (kBKMajor) {
-              tma_load_3d(sb, &tmap_b, full, kb * kTileK, n0, t.group);
+              tma_load_3d(sb, &tmap_b, full, kb * kTileK, n0, t.weight);
             } else {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
-                tma_load_3d(sb + j * kBoxBytes, &tmap_b, full, n0 + j * 64, kb * kTileK, t.group);
+                tma_load_3d(sb + j * kBoxBytes, &tmap_b, full, n0 + j * 64, kb * kTileK, t.weight);
             }
           }
         }

@@ -1,0 +1,122 @@
+"""Expert-parallel ragged_dot: experts sharded g/W per GPU, token rows exchanged with an NCCL
+all-to-all, then the local ragged_dot.  One process per GPU (torch.distributed).
+
+The reference has no multi-device code; this is the sharding its hot path admits: groups are
+independent GEMMs, so the only exchange is rows travelling to the rank that owns their expert.
+
+Per step, on each rank (T tokens, top_k routing, E experts, El = E / W per rank):
+  1. plan      sort the T*top_k (token, expert) pairs by expert; per-expert counts; exchange the
+               counts (all-to-all of int32 [W, El]); read the 2*W split sizes on the host.
+  2. permute   gather the token rows into expert order (rd_gather_rows).
+  3. exchange  all_to_all_single of the rows (split sizes from the plan).  Rows land in this
+               GPU's own memory, ordered (source rank, local expert).
+  4. compute   rd_gmm_indexed over the W*El received segments; segment (s, e) multiplies by
+               local expert e's weights.  No re-sort after the exchange.
+
+`plan_dispatch` and `exchange_rows` use only torch + torch.distributed and run on any backend
+(the CPU tests drive them over gloo); `ExpertParallelRaggedDot` adds the CUDA steps.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    token_index: torch.Tensor       # [T*top_k] source token of every sorted row (int32)
+    send_splits: List[int]          # rows this rank sends to each rank
+    recv_splits: List[int]          # rows this rank receives from each rank
+    segment_sizes: torch.Tensor     # [W*El] int32: rows of (source rank s, local expert e), s-major
+    segment_to_expert: torch.Tensor  # [W*El] int32: local expert of each segment
+    rows_received: int
+
+
+def plan_dispatch(routing: torch.Tensor, num_experts: int, group: Optional[dist.ProcessGroup] = None) -> DispatchPlan:
+    """routing: [T, top_k] expert ids.  Expert e lives on rank e // (num_experts // world)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    assert num_experts % world == 0, "experts must divide evenly over ranks"
+    local = num_experts // world
+    top_k = routing.shape[1]
+    flat = routing.reshape(-1).to(torch.int64)
+    _, order = torch.sort(flat, stable=True)
+    token_index = (order // top_k).to(torch.int32)
+    counts = torch.bincount(flat, minlength=num_experts).to(torch.int32)  # [E]
+    if world > 1:
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=group)  # [W, El]: from each source rank
+    else:
+        recv_counts = counts
+    both = torch.stack([counts.view(world, local).sum(1), recv_counts.view(world, local).sum(1)]).cpu()
+    send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+    seg2e = torch.arange(local, dtype=torch.int32, device=routing.device).repeat(world)
+    return DispatchPlan(token_index, send_splits, recv_splits, recv_counts.contiguous(), seg2e,
+                        int(sum(recv_splits)))
+
+
+def exchange_rows(rows_sorted: torch.Tensor, plan: DispatchPlan, group: Optional[dist.ProcessGroup] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """all-to-all of expert-sorted rows; returns [rows_received, k] ordered (source, expert)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if out is None:
+        out = torch.empty((plan.rows_received, rows_sorted.shape[1]), dtype=rows_sorted.dtype,
+                          device=rows_sorted.device)
+    if world == 1:
+        out.copy_(rows_sorted)
+        return out
+    dist.all_to_all_single(out, rows_sorted, output_split_sizes=plan.recv_splits,
+                           input_split_sizes=plan.send_splits, group=group)
+    return out
+
+
+class ExpertParallelRaggedDot:
+    """Holds this rank's experts' weights and runs the four steps above on its GPU."""
+
+    def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
+                 dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None):
+        from . import workloads
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert num_experts % self.world == 0
+        self.num_experts, self.local_experts = num_experts, num_experts // self.world
+        self.k, self.n, self.device = k, n, device
+        self.weights = workloads.normal_tensor((self.local_experts, k, n), k ** -0.5, seed, device, dtype)
+        self._events = []
+
+    def reset_timers(self):
+        self._events = []
+
+    def timers_ms(self, steps: int):
+        torch.cuda.synchronize(self.device)
+        tot = {"permute": 0.0, "a2a": 0.0, "gemm": 0.0}
+        for e in self._events:
+            tot["permute"] += e[0].elapsed_time(e[1])
+            tot["a2a"] += e[1].elapsed_time(e[2])
+            tot["gemm"] += e[2].elapsed_time(e[3])
+        return {k: v / max(steps, 1) for k, v in tot.items()}
+
+    def forward(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
+        """Returns (y [rows_received, n], plan).  y's rows are ordered (source rank, local expert)."""
+        from . import ops
+
+        plan = plan_dispatch(routing, self.num_experts, self.group)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
+        if timed:
+            ev[0].record()
+        rows_sorted = ops.gather_rows(x_tokens, plan.token_index)
+        if timed:
+            ev[1].record()
+        received = exchange_rows(rows_sorted, plan, self.group)
+        if timed:
+            ev[2].record()
+        y = ops.gmm_forward(received, self.weights, plan.segment_sizes, group_to_weight=plan.segment_to_expert)
+        if timed:
+            ev[3].record()
+            self._events.append(ev)
+        return y, plan

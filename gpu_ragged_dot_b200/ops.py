@@ -147,18 +147,26 @@ def gmm_forward(
     cfg: Optional[_lib.TileCfg] = None,
     out: Optional[torch.Tensor] = None,
     workspace: Optional[torch.Tensor] = None,
+    group_to_weight: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """One call of ``rd_gmm``: y[m,n] = ragged x[m,k] . A[g,k,n] (or A[g,n,k] with trans_rhs)."""
+    """One call of ``rd_gmm``: y[m,n] = ragged x[m,k] . A[g,k,n] (or A[g,n,k] with trans_rhs).
+
+    With ``group_to_weight`` (int32 [g], values in [0, A.shape[0])) it is ``rd_gmm_indexed``:
+    group i multiplies by A[group_to_weight[i]] and g may differ from A.shape[0]."""
     lib = _lib.load()
     _require_cuda(x, "x")
     _require_cuda(A, "A")
     assert A.dim() == 3 and x.dim() == 2, f"but {A.dim()=} {x.dim()=}"
     gs = _as_i32(group_sizes)
-    assert A.shape[0] == gs.shape[0], f"{A.shape[0]=} != {gs.shape[0]=}"
+    if group_to_weight is None:
+        assert A.shape[0] == gs.shape[0], f"{A.shape[0]=} != {gs.shape[0]=}"
+    else:
+        group_to_weight = _as_i32(group_to_weight)
+        assert group_to_weight.shape == gs.shape
     if x.dtype not in _DTYPE_CODE or A.dtype != x.dtype:
         raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {A.dtype}")
     m, k = x.shape
-    g = A.shape[0]
+    g = gs.shape[0]
     n = A.shape[-1] if not trans_rhs else A.shape[-2]
     k_rhs = A.shape[-2] if not trans_rhs else A.shape[-1]
     assert k_rhs == k, f"contraction mismatch: x has k={k}, A has {k_rhs}"
@@ -178,11 +186,18 @@ def gmm_forward(
     if cfg is None:
         cfg = tile_table.lookup("gmm_t" if trans_rhs else "gmm", m, kp, np_, g)
     with torch.cuda.device(x.device):
-        rc = lib.rd_gmm(
-            xp.data_ptr(), Ap.data_ptr(), gs.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
-            m, kp, np_, g, int(bool(trans_rhs)), _DTYPE_CODE[x.dtype], _cfg_ptr(cfg),
-            _stream_ptr(x.device),
-        )
+        if group_to_weight is None:
+            rc = lib.rd_gmm(
+                xp.data_ptr(), Ap.data_ptr(), gs.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
+                m, kp, np_, g, int(bool(trans_rhs)), _DTYPE_CODE[x.dtype], _cfg_ptr(cfg),
+                _stream_ptr(x.device),
+            )
+        else:
+            rc = lib.rd_gmm_indexed(
+                xp.data_ptr(), Ap.data_ptr(), Ap.shape[0], gs.data_ptr(), group_to_weight.data_ptr(),
+                y.data_ptr(), ws.data_ptr(), ws.numel(), m, kp, np_, g, int(bool(trans_rhs)),
+                _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+            )
     _lib.check(rc, "rd_gmm")
     if padded_n:
         y = y[:, :n].contiguous()
@@ -190,6 +205,23 @@ def gmm_forward(
             out.copy_(y)
             y = out
     return y
+
+
+def gather_rows(src: torch.Tensor, row_index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dst[i] = src[row_index[i]] through ``rd_gather_rows`` (rows must be a multiple of 16 bytes)."""
+    lib = _lib.load()
+    _require_cuda(src, "src")
+    idx = _as_i32(row_index)
+    src = _dense16(src)
+    assert src.dim() == 2
+    rows_out, row_bytes = idx.numel(), src.shape[1] * src.element_size()
+    dst = out if out is not None else torch.empty((rows_out, src.shape[1]), dtype=src.dtype, device=src.device)
+    assert dst.is_contiguous() and dst.shape == (rows_out, src.shape[1]) and dst.dtype == src.dtype
+    with torch.cuda.device(src.device):
+        rc = lib.rd_gather_rows(src.data_ptr(), idx.data_ptr(), dst.data_ptr(), rows_out, src.shape[0],
+                                row_bytes, _stream_ptr(src.device))
+    _lib.check(rc, "rd_gather_rows")
+    return dst
 
 
 def tgmm_forward(

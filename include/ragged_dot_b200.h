@@ -79,6 +79,23 @@ int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, vo
            size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
            const rd_tile_cfg* cfg, void* stream);
 
+/* rd_gmm with an indirection on the weights: group i multiplies by A[group_to_weight[i]], A is
+ * [num_weights, k, n] (or [num_weights, n, k]).  No counterpart in the reference; it serves the
+ * expert-parallel path, where the rows received from W source ranks form W * (experts per rank)
+ * consecutive segments that share the local experts' weights, so no re-sort is needed after
+ * the all-to-all.  group_to_weight is an int32 device array of g entries in [0, num_weights). */
+int rd_gmm_indexed(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                   const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                   int m, int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
+                   void* stream);
+
+/* dst[i, :] = src[row_index[i], :] for rows of row_bytes (a multiple of 16) bytes: the permute
+ * that precedes ragged_dot in an MoE layer (rows replicated per routed expert, sorted by
+ * expert).  The reference leaves this step to its caller.  An index outside [0, rows_in)
+ * yields a zero row. */
+int rd_gather_rows(const void* src, const int32_t* row_index, void* dst, int rows_out, int rows_in,
+                   int row_bytes, void* stream);
+
 /* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
  * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass
  * (gpu_ragged_dot.py:401).  Empty groups produce zero blocks. */

@@ -343,3 +343,44 @@ def test_cuda_metadata_matches_reference_golden(case):
     assert np.array_equal(got.row_it2group.cpu().numpy(), case["row_it2group"])
     assert np.array_equal(got.row_it2it_in_group.cpu().numpy(), case["row_it2it_in_group"])
     assert int(got.total_row_its.cpu()) == int(case["total_row_its"])
+
+
+# ------------------------------------------------------------------ expert-parallel building blocks
+def test_gather_rows_bit_exact():
+    src = oracle.reference_normal(31, (300, 136), torch.bfloat16)
+    idx = torch.tensor(np.random.default_rng(0).integers(0, 300, size=777), dtype=torch.int32)
+    got = ops.gather_rows(src.to(DEV), idx.to(DEV)).cpu()
+    assert torch.equal(got.view(torch.int16), src[idx.long()].view(torch.int16))
+    idx[5] = -1
+    idx[6] = 300
+    got = ops.gather_rows(src.to(DEV), idx.to(DEV)).cpu()
+    assert float(got[5].float().abs().max()) == 0.0 and float(got[6].float().abs().max()) == 0.0
+
+
+def test_gmm_indexed_shares_weights_between_segments():
+    m, k, n, experts = 640, 128, 136, 3
+    x, A, _ = _inputs(41, m, k, n, experts)
+    seg_sizes = [100, 0, 60, 130, 90, 1, 0, 200, 30]  # 3 sources x 3 experts, source-major
+    seg2e = [0, 1, 2] * 3
+    want = oracle.ragged_dot(x, A[torch.tensor(seg2e)], torch.tensor(seg_sizes))
+    got = ops.gmm_forward(x.to(DEV), A.to(DEV), torch.tensor(seg_sizes, dtype=torch.int32, device=DEV),
+                          group_to_weight=torch.tensor(seg2e, dtype=torch.int32, device=DEV)).cpu()
+    _assert_close(got, want, "gmm_indexed")
+    assert float(got[sum(seg_sizes):].float().abs().max()) == 0.0
+
+
+def test_expert_parallel_single_rank_matches_oracle():
+    from gpu_ragged_dot_b200 import ep
+
+    E, k, n, T, top_k = 16, 128, 72, 300, 4
+    layer = ep.ExpertParallelRaggedDot(E, k, n, torch.device(DEV), seed=5)
+    x = workloads.normal_tensor((T, k), 1.0, 77, DEV)
+    routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=9)).to(DEV)
+    y, plan = layer.forward(x, routing)
+    flat = routing.reshape(-1).cpu()
+    order = torch.sort(flat, stable=True).indices
+    rows = x.cpu()[(order // top_k)]
+    gs = torch.bincount(flat, minlength=E).to(torch.int32)
+    assert plan.segment_sizes.cpu().tolist() == gs.tolist()
+    want = oracle.ragged_dot(rows, layer.weights.cpu(), gs)
+    _assert_close(y.cpu(), want, "ep single rank")
