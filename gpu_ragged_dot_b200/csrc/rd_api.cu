@@ -100,6 +100,9 @@ struct Workspace {
   int32_t* tile_prefix() const { return base + layout.off_tile_prefix(); }
   int32_t* tile2group() const { return base + layout.off_tile2group(); }
   int32_t* tile2idx() const { return base + layout.off_tile2idx(); }
+  rd::TileRecord* tile_rec() const {
+    return reinterpret_cast<rd::TileRecord*>(base + layout.off_tile_rec());
+  }
 };
 
 int bind_workspace(void* ws, size_t ws_bytes, int m, int g, Workspace* out) {
@@ -112,41 +115,76 @@ int bind_workspace(void* ws, size_t ws_bytes, int m, int g, Workspace* out) {
   return RD_OK;
 }
 
-void launch_internal_metadata(const int32_t* group_sizes, int g, int m, const Workspace& w,
-                              cudaStream_t stream) {
+void launch_internal_metadata(const int32_t* group_sizes, const int32_t* group_to_weight, int g,
+                              int m, int tile_m, const Workspace& w, cudaStream_t stream) {
   rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, stream>>>(
-      group_sizes, g, m, rd::kTileM, w.layout.max_tiles, w.group_offsets(), w.tile2group(),
-      w.tile2idx(), w.totals(), w.tile_prefix(), w.totals() + 1, w.status());
+      group_sizes, g, m, tile_m, w.layout.max_tiles, w.group_offsets(), w.tile2group(),
+      w.tile2idx(), w.totals(), w.tile_prefix(), w.totals() + 1, w.status(), w.tile_rec(),
+      group_to_weight);
 }
 
 // ------------------------------------------------------------------ tile selection
-// The committed replacement for the reference's run-time tune-jax search: BN by output width
-// and by how many tiles the persistent grid would otherwise get.
-int choose_tile_n(long long row_tiles, int n, int sms) {
+// The committed replacement for the reference's run-time tune-jax search.  Measured on B200
+// (profiles/): the 256-wide tile wins at every benchmark shape, compute-bound or
+// bandwidth-bound (decode m=256: 93 % of copy bandwidth at 256, 67 % at 128, 39 % at 64), so
+// narrower tiles are only used when n itself is narrow.
+int choose_tile_n(long long /*row_tiles*/, int n, int /*sms*/) {
   if (n <= 64) return 64;
   if (n <= 128) return 128;
-  // Prefer the widest tile unless that leaves the grid under-filled (small / decode shapes).
-  const long long tiles256 = row_tiles * ((n + 255) / 256);
-  if (tiles256 >= 2LL * sms) return 256;
-  const long long tiles128 = row_tiles * ((n + 127) / 128);
-  if (tiles128 >= 2LL * sms) return 128;
-  return tiles256 >= sms ? 256 : (tiles128 >= sms ? 128 : 64);
+  return 256;
 }
 
-template <int BN, bool kBKMajor, bool kTgmm>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int ctas,
-                cudaStream_t stream) {
-  constexpr int kStageBytes = rd::stage_bytes<BN, kTgmm>();
-  constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  constexpr int kSmem = kStages * kStageBytes + 1024;
-  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm>;
+template <int BN, bool kBKMajor, bool kTgmm, int kCtas>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                const GemmArgs& args, int ctas, cudaStream_t stream) {
+  constexpr int kStageBytes = rd::stage_bytes<BN, kCtas>();
+  constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
+  constexpr int kSmem = kStages * kStageBytes + rd::kOutStagingBytes + 1024;
+  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm, kCtas>;
   // The attribute is per device; setting it again is cheap, so do it on every call rather
   // than track which devices have seen it.
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
       cudaSuccess)
     return RD_ERR_LAUNCH;
-  kernel<<<ctas, rd::kGemmThreads, kSmem, stream>>>(ta, tb, args);
+  cudaLaunchConfig_t lc = {};
+  lc.blockDim = dim3(rd::kGemmThreads, 1, 1);
+  lc.dynamicSmemBytes = kSmem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  lc.attrs = attr;
+  lc.numAttrs = 0;
+  if (kCtas == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.numAttrs = 1;
+    // A persistent grid must be fully co-resident: ask how many CTA pairs fit at once.
+    lc.gridDim = dim3(2, 1, 1);
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &lc) != cudaSuccess || clusters <= 0)
+      return RD_ERR_LAUNCH;
+    int pairs = ctas / 2;
+    if (pairs > clusters) pairs = clusters;
+    if (pairs < 1) pairs = 1;
+    lc.gridDim = dim3(2 * pairs, 1, 1);
+  } else {
+    lc.gridDim = dim3(ctas, 1, 1);
+  }
+  if (cudaLaunchKernelEx(&lc, kernel, ta, tb, tout, args) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return RD_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+// CTA pairs (256 x 256 tiles, B operand split between the two CTAs) pay off where the
+// 256-row granularity wastes nothing: tgmm, whose tile rows are the dense k axis.  For gmm the
+// tile rows are a group's ragged token rows and the wider tile wastes more than the pair
+// saves at the benchmark group sizes, so gmm pairs only on request (rd_tile_cfg.cta_group).
+bool choose_pair(bool tgmm, long long tiles256, int bn, int sms) {
+  if (!tgmm || bn != 256) return false;
+  return tiles256 >= 2LL * (sms / 2);
 }
 
 int pick_ctas(const rd_tile_cfg* cfg) {
@@ -175,7 +213,7 @@ const char* rd_status_string(int code) {
     case RD_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
     case RD_ERR_TOO_LARGE:
       return "problem too large for the built-in scratch of rd_gmm_static_scratch "
-             "(needs 4*g + 2*ceil(m/128) + 9 <= 16384 words); use rd_gmm with a workspace";
+             "(needs 12*g + 10*ceil(m/128) + 16 <= 16384 words); use rd_gmm with a workspace";
     case RD_ERR_SCRATCH_SETUP: return "could not resolve the address of the built-in scratch array";
     default: return "unknown status";
   }
@@ -208,7 +246,7 @@ int rd_metadata(const int32_t* group_sizes, int g, int m, int chunk_m, int32_t* 
   const int u = (m + chunk_m - 1) / chunk_m + g;
   rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       group_sizes, g, m, chunk_m, u, group_offsets, row_it2group, row_it2it_in_group,
-      total_row_its, nullptr, nullptr, nullptr);
+      total_row_its, nullptr, nullptr, nullptr, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -236,12 +274,15 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   const int sms = sm_count();
   int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n((m + rd::kTileM - 1) / rd::kTileM, n, sms);
   if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+  int cta_group = cfg ? cfg->cta_group : 0;
+  if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
+  if (cta_group == 0) cta_group = choose_pair(false, 0, bn, sms) ? 2 : 1;
 
   // Launch the metadata kernel before encoding the tensor maps: besides being the first step
   // of the call, a runtime launch binds the device's primary context to the calling thread,
   // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
   // arrive here without one).
-  launch_internal_metadata(group_sizes, g, m, w, stream);
+  launch_internal_metadata(group_sizes, group_to_weight, g, m, rd::kTileM * cta_group, w, stream);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   CUtensorMap ta, tb;
@@ -254,7 +295,7 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   if (trans_rhs) {  // A[g, n, k]: rows of k, K-major operand, one [BN][64] box per stage
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
                               static_cast<uint64_t>(num_weights)};
-    const uint32_t box[3] = {rd::kTileK, static_cast<uint32_t>(bn), 1};
+    const uint32_t box[3] = {rd::kTileK, static_cast<uint32_t>(bn / cta_group), 1};
     rc = encode_map(&tb, A, dtype, 3, dims, box);
   } else {  // A[g, k, n]: rows of n, MN-major operand, [64 k][64 n] boxes
     const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
@@ -263,6 +304,13 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
     rc = encode_map(&tb, A, dtype, 3, dims, box);
   }
   if (rc != RD_OK) return rc;
+  CUtensorMap tout;
+  {  // y[m, n] written as [32 rows][64 cols] boxes
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {64, 32};
+    rc = encode_map(&tout, y, dtype, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
 
   GemmArgs args;
   args.m = m; args.k = k; args.n = n; args.g = g;
@@ -272,23 +320,22 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.ab_format = dtype;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
-  args.tile2group = w.tile2group();
-  args.tile2idx = w.tile2idx();
-  args.tile_prefix = w.tile_prefix();
+  args.tile_rec = w.tile_rec();
   args.totals = w.totals();
-  args.group_to_weight = group_to_weight;
   args.status = w.status();
   args.out = y;
 
   const int ctas = pick_ctas(cfg);
   if (trans_rhs) {
-    if (bn == 256) return launch_gemm<256, true, false>(ta, tb, args, ctas, stream);
-    if (bn == 128) return launch_gemm<128, true, false>(ta, tb, args, ctas, stream);
-    return launch_gemm<64, true, false>(ta, tb, args, ctas, stream);
+    if (cta_group == 2) return launch_gemm<256, true, false, 2>(ta, tb, tout, args, ctas, stream);
+    if (bn == 256) return launch_gemm<256, true, false, 1>(ta, tb, tout, args, ctas, stream);
+    if (bn == 128) return launch_gemm<128, true, false, 1>(ta, tb, tout, args, ctas, stream);
+    return launch_gemm<64, true, false, 1>(ta, tb, tout, args, ctas, stream);
   }
-  if (bn == 256) return launch_gemm<256, false, false>(ta, tb, args, ctas, stream);
-  if (bn == 128) return launch_gemm<128, false, false>(ta, tb, args, ctas, stream);
-  return launch_gemm<64, false, false>(ta, tb, args, ctas, stream);
+  if (cta_group == 2) return launch_gemm<256, false, false, 2>(ta, tb, tout, args, ctas, stream);
+  if (bn == 256) return launch_gemm<256, false, false, 1>(ta, tb, tout, args, ctas, stream);
+  if (bn == 128) return launch_gemm<128, false, false, 1>(ta, tb, tout, args, ctas, stream);
+  return launch_gemm<64, false, false, 1>(ta, tb, tout, args, ctas, stream);
 }
 
 int rd_gmm(const void* x, const void* A, const int32_t* group_sizes, void* y, void* workspace,
@@ -340,15 +387,22 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   if (rc != RD_OK) return rc;
 
   const int sms = sm_count();
-  const long long k_tiles = (k + rd::kTileM - 1) / rd::kTileM;
-  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(k_tiles * g, n, sms);
+  int bn = cfg && cfg->tile_n
+               ? cfg->tile_n
+               : choose_tile_n(static_cast<long long>((k + rd::kTileM - 1) / rd::kTileM) * g, n, sms);
   if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+  int cta_group = cfg ? cfg->cta_group : 0;
+  if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
+  if (cta_group == 0)
+    cta_group =
+        choose_pair(true, static_cast<long long>((k + 255) / 256) * g * ((n + 255) / 256), bn, sms) ? 2 : 1;
+  const long long k_tiles = (k + rd::kTileM * cta_group - 1) / (rd::kTileM * cta_group);
 
   // Launch the metadata kernel before encoding the tensor maps: besides being the first step
   // of the call, a runtime launch binds the device's primary context to the calling thread,
   // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
   // arrive here without one).
-  launch_internal_metadata(group_sizes, g, m, w, stream);
+  launch_internal_metadata(group_sizes, nullptr, g, m, rd::kTileM, w, stream);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   CUtensorMap ta, tb;
@@ -365,6 +419,15 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
     if (rc != RD_OK) return rc;
   }
 
+  CUtensorMap tout;
+  {  // out[g, k, n] written as [32 rows][64 cols] boxes of one group
+    const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                              static_cast<uint64_t>(g)};
+    const uint32_t box[3] = {64, 32, 1};
+    rc = encode_map(&tout, out, dtype, 3, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+
   GemmArgs args;
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
@@ -373,18 +436,16 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.ab_format = dtype;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
-  args.tile2group = w.tile2group();
-  args.tile2idx = w.tile2idx();
-  args.tile_prefix = w.tile_prefix();
+  args.tile_rec = w.tile_rec();
   args.totals = w.totals();
-  args.group_to_weight = nullptr;
   args.status = w.status();
   args.out = out;
 
   const int ctas = pick_ctas(cfg);
-  if (bn == 256) return launch_gemm<256, false, true>(ta, tb, args, ctas, stream);
-  if (bn == 128) return launch_gemm<128, false, true>(ta, tb, args, ctas, stream);
-  return launch_gemm<64, false, true>(ta, tb, args, ctas, stream);
+  if (cta_group == 2) return launch_gemm<256, false, true, 2>(ta, tb, tout, args, ctas, stream);
+  if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);
+  if (bn == 128) return launch_gemm<128, false, true, 1>(ta, tb, tout, args, ctas, stream);
+  return launch_gemm<64, false, true, 1>(ta, tb, tout, args, ctas, stream);
 }
 
 int rd_device_status(const void* workspace, void* stream) {

@@ -6,9 +6,24 @@
 //
 // One persistent, warp-specialised CTA per SM:
 //   warp 0      TMA producer   -- cp.async.bulk.tensor tiles into a kStages-deep smem ring
-//   warp 1      MMA issuer     -- tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators
-//   warps 2..5  epilogue       -- tcgen05.ld, fp32 -> bf16/fp16, row/column-masked 16-byte stores
+//   warp 1      MMA issuer     -- tcgen05.mma (K=16) into one of two TMEM accumulators
+//   warps 2..5  epilogue       -- tcgen05.ld, fp32 -> bf16/fp16, staged through swizzled smem and
+//                                 written with TMA stores ([32 rows][64 cols] boxes, clipped at the
+//                                 tensor's edges); a gmm slab that crosses the end of its group
+//                                 is written with row-masked 16-byte stores instead
 // The two TMEM accumulators let the epilogue of tile t overlap the main loop of tile t+1.
+//
+// kCtas == 1: each CTA owns a 128 x BN output tile (tcgen05.mma.cta_group::1, M=128).
+// kCtas == 2: two CTAs of a cluster own a 256 x BN tile (cta_group::2, M=256).  Each CTA loads
+//             its own 128 rows of the A operand and HALF of the B operand's BN columns; the
+//             leader CTA (cluster rank 0) issues the MMAs, which read B from both CTAs' shared
+//             memory.  Per SM this cuts the shared-memory fill per flop by a third, which is
+//             what bounds the 1-CTA kernel.  Every CTA loads only its own tiles (nothing is
+//             broadcast); the peer's loads count their bytes on the LEADER's "full" barrier
+//             (cta_group::2 TMA form), so the leader sees one barrier per stage, and
+//             tcgen05.commit frees the stage in both CTAs.  The one stage per tgmm tile whose
+//             tail rows must be cleared goes through a slower hand-shake (peer clears its
+//             rows, then arrives on the leader's peer_ready barrier).
 //
 // Operand layouts (all 128-byte-swizzled, written by TMA, read through UMMA descriptors):
 //   K-major  operand tile [rows][64 k]  : one box, 8-row groups 1024 B apart
@@ -22,15 +37,18 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "rd_metadata.cuh"
 #include "rd_ptx.cuh"
 
 namespace rd {
 
-constexpr int kTileM = 128;  // UMMA M per CTA == output rows per tile
+constexpr int kTileM = 128;  // UMMA M per CTA == output rows per CTA tile
 constexpr int kTileK = 64;   // elements per 128-byte swizzle row == contraction depth per stage
 constexpr int kUmmaK = 16;   // contraction depth of one tcgen05.mma for 16-bit inputs
 constexpr int kBoxBytes = 64 * 128;  // one [64 rows][128 B] TMA box
 constexpr int kGemmThreads = 192;
+constexpr int kOutBoxBytes = 32 * 128;                  // one [32 rows][64 cols] output box
+constexpr int kOutStagingBytes = 4 * 2 * kOutBoxBytes;  // 4 epilogue warps x 2 buffers
 
 enum DeviceStatus : int32_t {
   kStatusOk = 0,
@@ -40,27 +58,25 @@ enum DeviceStatus : int32_t {
 struct GemmArgs {
   int m, k, n, g;   // gmm: x[m,k] . W[g] -> y[m,n]      tgmm: x[m,k], dout[m,n] -> out[g,k,n]
   int n_tiles;      // ceil(n / BN)
-  int k_tiles;      // tgmm: ceil(k / 128) tiles of the output's k axis; gmm: unused
+  int k_tiles;      // tgmm: tiles along the output's k axis (128 * kCtas rows each); gmm: unused
   int max_m_tiles;  // static upper bound on live row tiles (gmm)
   int ab_format;    // 0 = fp16, 1 = bf16
   const int32_t* group_sizes;
   const int32_t* group_offsets;
-  const int32_t* tile2group;
-  const int32_t* tile2idx;
-  const int32_t* tile_prefix;
-  const int32_t* totals;  // {live row tiles, min(sum(group_sizes), m)}
-  const int32_t* group_to_weight;  // gmm: weight matrix used by each group, or null (identity)
+  const TileRecord* tile_rec;  // gmm: one record per live row tile (of 128 * kCtas rows)
+  const int32_t* totals;       // {live row tiles, min(sum(group_sizes), m)}
   int32_t* status;
   void* out;
 };
 
+// Coordinates of one CTA's share of a tile.
 struct TileCoord {
   int group;   // group index
   int weight;  // gmm: index of the weight matrix this group multiplies by
-  int row0;    // gmm: first row of x / y;  tgmm: first row of the group
-  int rows;    // gmm: valid rows in this tile (<=128);  tgmm: rows of the group (contraction)
-  int n0;      // first output column
-  int k0;      // tgmm: first row of out[group] covered by this tile
+  int row0;    // gmm: first row of x / y for this CTA;  tgmm: first row of the group
+  int rows;    // gmm: valid rows for this CTA (<=128, may be <= 0);  tgmm: rows of the group
+  int n0;      // first output column of the tile
+  int k0;      // tgmm: first row of out[group] written by this CTA
 };
 
 __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
@@ -68,28 +84,30 @@ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
 
 // gmm tile order: group-major; inside a group the n-tiles are outer and the group's row
 // tiles inner, so CTAs running concurrently share one [k, BN] weight panel through L2 and an
-// expert's weights stream from HBM once.
-__device__ __forceinline__ TileCoord decode_gmm_tile(const GemmArgs& p, int tile) {
+// expert's weights stream from HBM once.  One 32-byte record load per tile, no dependent loads.
+template <int BN, int kCtas>
+__device__ __forceinline__ TileCoord decode_gmm_tile(const GemmArgs& p, int tile, int cta_rank) {
+  constexpr int kRows = kTileM * kCtas;
   const int mt = tile / p.n_tiles;
-  const int gi = p.tile2group[mt];
-  const int base = p.tile_prefix[gi];
-  const int tiles_g = p.tile_prefix[gi + 1] - base;
-  const int local = tile - base * p.n_tiles;
-  const int nt = local / tiles_g;
-  const int mi = local - nt * tiles_g;
+  const int4* rp = reinterpret_cast<const int4*>(p.tile_rec + mt);
+  const int4 a = rp[0];  // group, weight, group_offset, group_size
+  const int4 b = rp[1];  // tile_base, tiles, idx, pad
+  const int local = tile - b.x * p.n_tiles;
+  const int nt = local / b.y;
+  const int mi = local - nt * b.y;
   TileCoord t;
-  t.group = gi;
-  t.weight = p.group_to_weight ? p.group_to_weight[gi] : gi;
-  t.row0 = p.group_offsets[gi] + mi * kTileM;
-  t.rows = imin(kTileM, imax(p.group_sizes[gi], 0) - mi * kTileM);
+  t.group = a.x;
+  t.weight = a.y;
+  t.row0 = a.z + mi * kRows + cta_rank * kTileM;
+  t.rows = imin(kTileM, a.w - mi * kRows - cta_rank * kTileM);
   t.rows = imin(t.rows, p.m - t.row0);  // never touch rows past m
-  t.n0 = 0;
+  t.n0 = nt * BN;
   t.k0 = 0;
-  t.n0 = nt;  // caller scales by BN
   return t;
 }
 
-__device__ __forceinline__ TileCoord decode_tgmm_tile(const GemmArgs& p, int tile) {
+template <int BN, int kCtas>
+__device__ __forceinline__ TileCoord decode_tgmm_tile(const GemmArgs& p, int tile, int cta_rank) {
   const int per_group = p.k_tiles * p.n_tiles;
   const int gi = tile / per_group;
   const int rem = tile - gi * per_group;
@@ -100,8 +118,8 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile(const GemmArgs& p, int til
   t.weight = gi;
   t.row0 = p.group_offsets[gi];
   t.rows = imax(imin(imax(p.group_sizes[gi], 0), p.m - t.row0), 0);
-  t.n0 = nt;
-  t.k0 = kt * kTileM;
+  t.n0 = nt * BN;
+  t.k0 = (kt * kCtas + cta_rank) * kTileM;
   return t;
 }
 
@@ -114,61 +132,111 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int ab_format) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BN, bool kTgmm>
+// tgmm: does the group's last 64-row stage need rows cleared before its MMAs (rows past the end
+// of the group that fall inside the last 16-deep MMA issued)?
+__device__ __forceinline__ bool tail_needs_clearing(int group_rows) {
+  const int live = group_rows % kTileK;
+  return live != 0 && (live % kUmmaK) != 0;
+}
+
+// Zero rows [live, end of the last 16-deep MMA) of every [64 rows][128 B] box of one stage and
+// make the writes visible to the tensor core (async proxy).  Whole warp.
+template <int kBoxes>
+__device__ __forceinline__ void clear_tail_rows(uint32_t stage_addr, int live, int lane) {
+  const int n_mma = (live + kUmmaK - 1) / kUmmaK;
+  const int dead = n_mma * kUmmaK - live;
+  if (dead <= 0) return;
+  const int chunks = kBoxes * dead * 8;  // 16-byte chunks
+  for (int c = lane; c < chunks; c += 32) {
+    const int box = c / (dead * 8);
+    const int rem = c - box * (dead * 8);
+    const uint32_t addr = stage_addr + box * kBoxBytes + (live * 128) + rem * 16;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+  }
+  fence_proxy_async_smem();
+}
+
+// TMA load whose bytes are counted on this CTA's own barrier, or (remote_bar) on a barrier of
+// the other CTA of the pair.
+__device__ __forceinline__ void load_2d(bool remote_bar, uint32_t dst, const CUtensorMap* map,
+                                        uint32_t bar, int c0, int c1) {
+  if (remote_bar) {
+    tma_load_2d_pair(dst, map, bar, c0, c1);
+  } else {
+    tma_load_2d(dst, map, bar, c0, c1);
+  }
+}
+__device__ __forceinline__ void load_3d(bool remote_bar, uint32_t dst, const CUtensorMap* map,
+                                        uint32_t bar, int c0, int c1, int c2) {
+  if (remote_bar) {
+    tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+  } else {
+    tma_load_3d(dst, map, bar, c0, c1, c2);
+  }
+}
+
+template <int BN, int kCtas>
 constexpr int stage_bytes() {
-  return kTileM * kTileK * 2 + BN * kTileK * 2;
+  return kTileM * kTileK * 2 + (BN / kCtas) * kTileK * 2;
 }
 
 // kTgmm == false : gmm.   A operand = x tile, K-major.  B operand = W tile, K-major when
 //                  kBKMajor (trans_rhs: W[g] is [n,k]) else MN-major (W[g] is [k,n]).
 // kTgmm == true  : tgmm.  A operand = x^T tile (MN-major), B operand = dout tile (MN-major);
 //                  kBKMajor must be false.
-template <int BN, bool kBKMajor, int kStages, bool kTgmm>
+template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                   const __grid_constant__ CUtensorMap tmap_b, const GemmArgs p) {
+                   const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
+  static_assert(kCtas == 1 || (kCtas == 2 && BN >= 128), "a CTA pair needs BN >= 128");
+  constexpr bool kPair = kCtas == 2;
+  constexpr int kBCols = BN / kCtas;  // B-operand columns this CTA loads
   constexpr uint32_t kABytes = kTileM * kTileK * 2;
-  constexpr uint32_t kBBytes = BN * kTileK * 2;
+  constexpr uint32_t kBBytes = kBCols * kTileK * 2;
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;  // two fp32 accumulators of BN columns
-  constexpr uint32_t kIdesc =
-      0;  // built at run time (ab_format is a run-time value); see make_idesc_f16 below
 
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];
-  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_full[kStages];        // TMA data of this CTA landed
+  __shared__ __align__(8) uint64_t bar_empty[kStages];       // MMAs reading the stage retired
+  __shared__ __align__(8) uint64_t bar_peer_ready[kStages];  // leader only: peer's stage is ready
   __shared__ __align__(8) uint64_t bar_acc_full[2];
-  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];  // leader only when paired
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  (void)kIdesc;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int cta_rank = kPair ? static_cast<int>(cluster_cta_rank()) : 0;
+  const bool leader = cta_rank == 0;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_out);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_peer_ready[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_acc_full[a]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[a]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&bar_acc_empty[a]), 4 * kCtas);  // one arrival per epilogue warp
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(&tmem_slot), kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<kCtas>(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish<kCtas>();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (kPair) cluster_sync();  // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abort_ptr = &abort_flag;
@@ -179,6 +247,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     num_tiles = imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
   }
+  const int tile_start = static_cast<int>(blockIdx.x) / kCtas;
+  const int tile_step = static_cast<int>(gridDim.x) / kCtas;
   const int k_blocks_gmm = (p.k + kTileK - 1) / kTileK;
 
   if (warp == 0) {
@@ -186,9 +256,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord t = kTgmm ? decode_tgmm_tile(p, tile) : decode_gmm_tile(p, tile);
-        const int n0 = t.n0 * BN;
+      for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
+                                  : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
+        const int nb = t.n0 + cta_rank * kBCols;  // first B column this CTA loads
         const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages;
@@ -197,25 +268,37 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bar_full[s]);
+          uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t sa = stage_base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
-          mbar_arrive_expect_tx(full, kStageBytes);
+          // In a pair the peer's bytes are counted on the leader's barrier, except for a stage
+          // whose tail rows the peer has to clear first (it then needs to see its own data land).
+          const bool local_stage = !kPair || (kTgmm && kb == kb_count - 1 && tail_needs_clearing(t.rows));
+          bool remote_bar = false;
+          if (leader) {
+            mbar_arrive_expect_tx(full, local_stage ? kStageBytes : 2 * kStageBytes);
+          } else if (local_stage) {
+            mbar_arrive_expect_tx(full, kStageBytes);
+          } else {
+            full = map_to_cta(full, 0);
+            remote_bar = true;
+          }
           if (kTgmm) {
             const int r = t.row0 + kb * kTileK;
-            tma_load_2d(sa, &tmap_a, full, t.k0, r);
-            tma_load_2d(sa + kBoxBytes, &tmap_a, full, t.k0 + 64, r);
+            load_2d(remote_bar, sa, &tmap_a, full, t.k0, r);
+            load_2d(remote_bar, sa + kBoxBytes, &tmap_a, full, t.k0 + 64, r);
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * kBoxBytes, &tmap_b, full, n0 + j * 64, r);
+            for (int j = 0; j < kBCols / 64; ++j)
+              load_2d(remote_bar, sb + j * kBoxBytes, &tmap_b, full, nb + j * 64, r);
           } else {
-            tma_load_2d(sa, &tmap_a, full, kb * kTileK, t.row0);
+            load_2d(remote_bar, sa, &tmap_a, full, kb * kTileK, t.row0);
             if (kBKMajor) {
-              tma_load_3d(sb, &tmap_b, full, kb * kTileK, n0, t.weight);
+              load_3d(remote_bar, sb, &tmap_b, full, kb * kTileK, nb, t.weight);
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_3d(sb + j * kBoxBytes, &tmap_b, full, n0 + j * 64, kb * kTileK, t.weight);
+              for (int j = 0; j < kBCols / 64; ++j)
+                load_3d(remote_bar, sb + j * kBoxBytes, &tmap_b, full, nb + j * 64, kb * kTileK,
+                        t.weight);
             }
           }
         }
@@ -223,16 +306,45 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM, BN);
+    // In a pair only the leader issues MMAs.  The peer's warp 1 has nothing to do except for
+    // the tgmm stages whose tail rows it must clear in its own shared memory.
+    const uint32_t idesc =
+        make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
     uint32_t it = 0;
     uint32_t local_tile = 0;
+    uint32_t tail_parity = 0;  // bit s: parity of the next tail hand-shake on stage s
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const TileCoord t = kTgmm ? decode_tgmm_tile(p, tile) : decode_gmm_tile(p, tile);
+    for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+      const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
+                                : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
       const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+
+      if (kPair && !leader) {
+        // ---- peer CTA: only the tail stage of a tgmm tile needs this warp
+        if (tail_stage) {
+          const uint32_t s = (it + kb_count - 1) % kStages;
+          const uint32_t par = (tail_parity >> s) & 1u;
+          tail_parity ^= 1u << s;
+          if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = stage_base + s * kStageBytes;
+          const int live = t.rows - (kb_count - 1) * kTileK;
+          clear_tail_rows<(kABytes + kBBytes) / kBoxBytes>(sa, live, lane);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(&bar_peer_ready[s]), 0);
+          __syncwarp();
+        }
+        it += kb_count;
+        continue;
+      }
+
+      // ---- single CTA, or the leader of a pair
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
-      if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
+      if (!mbar_wait<kPair>(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
         ok = false;
         break;
       }
@@ -241,58 +353,71 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int kb = 0; kb < kb_count; ++kb, ++it) {
         const uint32_t s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
-        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_ptr)) {
+        if (!mbar_wait<kPair>(smem_u32(&bar_full[s]), ph, abort_ptr)) {
           ok = false;
           break;
         }
         const uint32_t sa = stage_base + s * kStageBytes;
         const uint32_t sb = sa + kABytes;
-        if (kTgmm) {
-          // Rows past the end of the group belong to the next group (or to nobody): clear
-          // them in every box of this stage so they add nothing to the reduction.
-          const int live = t.rows - kb * kTileK;
-          if (live < kTileK) {
-            constexpr int kBoxes = (kABytes + kBBytes) / kBoxBytes;
-            const int dead = kTileK - live;
-            const int chunks = kBoxes * dead * 8;  // 16-byte chunks
-            for (int c = lane; c < chunks; c += 32) {
-              const int box = c / (dead * 8);
-              const int rem = c - box * (dead * 8);
-              const uint32_t addr = sa + box * kBoxBytes + (live * 128) + rem * 16;
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u)
-                           : "memory");
-            }
-            fence_proxy_async_smem();
-          }
+        // Contraction depth that is really there in this stage: the group's last rows (tgmm)
+        // or the last columns of k (gmm).  Whole 16-deep MMAs past it are skipped.
+        const int live = kTgmm ? t.rows - kb * kTileK : p.k - kb * kTileK;
+        const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
+        if (kTgmm && tail_stage && kb == kb_count - 1) {
+          // Rows past the end of the group belong to the next group (or to nobody): clear them,
+          // up to the end of the last MMA that is issued, in every box of this stage, so they
+          // add nothing to the reduction.  (In gmm the columns past k are zero-filled by TMA.)
+          clear_tail_rows<(kABytes + kBBytes) / kBoxBytes>(sa, live, lane);
           __syncwarp();
+          if (kPair) {  // ... and wait until the peer has done the same with its half
+            const uint32_t par = (tail_parity >> s) & 1u;
+            tail_parity ^= 1u << s;
+            if (!mbar_wait<true>(smem_u32(&bar_peer_ready[s]), par, abort_ptr)) {
+              ok = false;
+              break;
+            }
+          }
         }
         tc_fence_after_sync();
         if (lane == 0) {
 #pragma unroll
           for (int kk = 0; kk < kTileK / kUmmaK; ++kk) {
-            uint64_t adesc, bdesc;
-            if (kTgmm) {
-              adesc = make_smem_desc(sa + kk * 2048, kBoxBytes, 1024);
-            } else {
-              adesc = make_smem_desc(sa + kk * 32, 16, 1024);
+            if (kk < n_mma) {
+              uint64_t adesc, bdesc;
+              if (kTgmm) {
+                adesc = make_smem_desc(sa + kk * 2048, kBoxBytes, 1024);
+              } else {
+                adesc = make_smem_desc(sa + kk * 32, 16, 1024);
+              }
+              if (kBKMajor) {
+                bdesc = make_smem_desc(sb + kk * 32, 16, 1024);
+              } else {
+                bdesc = make_smem_desc(sb + kk * 2048, kBoxBytes, 1024);
+              }
+              umma_f16<kCtas>(tmem_d, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
-            if (kBKMajor) {
-              bdesc = make_smem_desc(sb + kk * 32, 16, 1024);
-            } else {
-              bdesc = make_smem_desc(sb + kk * 2048, kBoxBytes, 1024);
-            }
-            umma_f16<1>(tmem_d, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&bar_empty[s]));  // frees the smem stage when these MMAs retire
+          // Frees the smem stage (in both CTAs of a pair) when these MMAs retire.
+          if (kPair) {
+            umma_commit_pair(smem_u32(&bar_empty[s]), 0x3);
+          } else {
+            umma_commit(smem_u32(&bar_empty[s]));
+          }
         }
         __syncwarp();
       }
       if (!ok) break;
       if (lane == 0) {
+        const uint32_t bar = smem_u32(&bar_acc_full[acc]);
         if (kb_count > 0) {
-          umma_commit(smem_u32(&bar_acc_full[acc]));
-        } else {
-          mbar_arrive(smem_u32(&bar_acc_full[acc]));  // empty group: nothing to wait for
+          if (kPair) {
+            umma_commit_pair(bar, 0x3);
+          } else {
+            umma_commit(bar);
+          }
+        } else {  // empty group: nothing to wait for
+          mbar_arrive(bar);
+          if (kPair) mbar_arrive_cluster(bar, 1);
         }
       }
       __syncwarp();
@@ -301,71 +426,130 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const int r_in_tile = quarter * 32 + lane;
+    const uint32_t staging = stage_base + kStages * kStageBytes + (warp - 2) * 2 * kOutBoxBytes;
     uint32_t local_tile = 0;
+    uint32_t boxes_stored = 0;
     bool ok = true;
     uint16_t* out16 = reinterpret_cast<uint16_t*>(p.out);
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const TileCoord t = kTgmm ? decode_tgmm_tile(p, tile) : decode_gmm_tile(p, tile);
-      const int n0 = t.n0 * BN;
+    for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+      const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
+                                : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
+      const int n0 = t.n0;
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
-      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_ph, abort_ptr)) {
+      if (!mbar_wait<kPair>(smem_u32(&bar_acc_full[acc]), acc_ph, abort_ptr)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
 
-      bool row_ok;
-      size_t row_off;  // element offset of this thread's output row
-      bool warp_has_rows;
+      bool row_ok;         // this thread's output row exists
+      size_t row_off;      // element offset of this thread's output row
+      bool warp_has_rows;  // any row of this warp's 32-row slab exists
+      bool slab_by_tma;    // the whole slab may be written as one box per 64 columns
       bool zero_only = false;
+      int out_row0;        // first output row of the slab (TMA coordinate)
       if (kTgmm) {
         const int kr = t.k0 + r_in_tile;
+        out_row0 = t.k0 + quarter * 32;
         row_ok = kr < p.k;
-        warp_has_rows = (t.k0 + quarter * 32) < p.k;
+        warp_has_rows = out_row0 < p.k;
+        slab_by_tma = true;  // rows >= k are outside the map and dropped by the store
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
         zero_only = t.rows <= 0;
       } else {
+        out_row0 = t.row0 + quarter * 32;
         row_ok = r_in_tile < t.rows;
         warp_has_rows = quarter * 32 < t.rows;
+        slab_by_tma = quarter * 32 + 32 <= t.rows;  // else the box would overwrite the next group
         row_off = static_cast<size_t>(t.row0 + r_in_tile) * static_cast<size_t>(p.n);
       }
 
-      if (warp_has_rows) {
+      const int n_chunks = warp_has_rows ? imin(BN / 64, (p.n - n0 + 63) / 64) : 0;
+      const uint32_t acc_empty_bar = smem_u32(&bar_acc_empty[acc]);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= p.n) break;
-          uint32_t v[32];
-          if (!zero_only) {
-            const uint32_t taddr =
-                tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16);
-            tmem_ld_32x32(taddr, v);
-            tmem_ld_wait();
-          } else {
+      for (int c = 0; c < n_chunks; ++c) {
+        const int col = n0 + c * 64;
+        uint32_t v[64];
+        if (!zero_only) {
+          const uint32_t taddr =
+              tmem_base + acc * BN + c * 64 + (static_cast<uint32_t>(quarter * 32) << 16);
+          tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          for (int j = 0; j < 64; ++j) v[j] = 0u;
+        }
+        if (c == n_chunks - 1) {
+          // Everything this warp needs from the accumulator is in registers: hand it back.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if (kPair) {
+              mbar_arrive_cluster(acc_empty_bar, 0);
+            } else {
+              mbar_arrive(acc_empty_bar);
+            }
           }
-          if (row_ok) {
-            uint16_t* dst = out16 + row_off + col;
+        }
+        uint4 o[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (col + q * 8 < p.n) {  // n is a multiple of 8: a chunk is all in or all out
-                uint4 o;
-                o.x = pack2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), p.ab_format);
-                o.y = pack2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), p.ab_format);
-                o.z = pack2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), p.ab_format);
-                o.w = pack2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), p.ab_format);
-                *reinterpret_cast<uint4*>(dst + q * 8) = o;
-              }
+        for (int q = 0; q < 8; ++q) {
+          o[q].x = pack2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), p.ab_format);
+          o[q].y = pack2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), p.ab_format);
+          o[q].z = pack2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), p.ab_format);
+          o[q].w = pack2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), p.ab_format);
+        }
+        if (slab_by_tma) {
+          const uint32_t buf = staging + (boxes_stored & 1u) * kOutBoxBytes;
+          // The box stored two boxes ago used this buffer: wait until TMA has read it out.
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+          const uint32_t row_addr = buf + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t a = row_addr + (((q ^ (lane & 7)) & 7) << 4);  // 128-byte swizzle
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[q].x),
+                         "r"(o[q].y), "r"(o[q].z), "r"(o[q].w)
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (kTgmm) {
+              tma_store_3d(&tmap_out, buf, col, out_row0, t.group);
+            } else {
+              tma_store_2d(&tmap_out, buf, col, out_row0);
+            }
+            bulk_commit_group();
+          }
+          ++boxes_stored;
+        } else if (row_ok) {
+          uint16_t* dst = out16 + row_off + col;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col + q * 8 < p.n) {  // n is a multiple of 8: a chunk is all in or all out
+              *reinterpret_cast<uint4*>(dst + q * 8) = o[q];
             }
           }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+      if (n_chunks == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (kPair) {
+            mbar_arrive_cluster(acc_empty_bar, 0);
+          } else {
+            mbar_arrive(acc_empty_bar);
+          }
+        }
+      }
     }
+    // All boxes must have left shared memory (and reached global memory) before the CTA goes.
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
 
     if (!kTgmm) {
       // Rows past sum(group_sizes) belong to no group: jax.lax.ragged_dot defines them as 0
@@ -390,9 +574,11 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  // Neither CTA of a pair may leave while the other can still reach its barriers or smem.
+  if (kPair) cluster_sync();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<kCtas>(tmem_base, kTmemCols);
   }
 }
 

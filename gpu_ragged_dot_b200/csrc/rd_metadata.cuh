@@ -21,7 +21,21 @@ struct WorkspaceLayout {
   __host__ __device__ int off_tile_prefix() const { return 8 + g; }            // [g + 1]
   __host__ __device__ int off_tile2group() const { return 8 + 2 * g + 1; }     // [U]
   __host__ __device__ int off_tile2idx() const { return 8 + 2 * g + 1 + max_tiles; }  // [U]
-  __host__ __device__ int total_words() const { return 8 + 2 * g + 1 + 2 * max_tiles; }
+  // [U] records of 8 words, 32-byte aligned: everything a GEMM CTA needs to place a row tile
+  __host__ __device__ int off_tile_rec() const { return (8 + 2 * g + 1 + 2 * max_tiles + 7) & ~7; }
+  __host__ __device__ int total_words() const { return off_tile_rec() + 8 * max_tiles; }
+};
+
+// One record per live row tile (any tile of a group carries the group's facts).
+struct __align__(16) TileRecord {
+  int32_t group;         // group id
+  int32_t weight;        // weight matrix the group multiplies by (group_to_weight or identity)
+  int32_t group_offset;  // first row of the group
+  int32_t group_size;    // rows of the group (clamped to >= 0)
+  int32_t tile_base;     // number of row tiles in all earlier groups
+  int32_t tiles;         // row tiles of this group
+  int32_t idx;           // this tile's index inside the group
+  int32_t pad;
 };
 
 constexpr int kMetaThreads = 1024;
@@ -43,12 +57,15 @@ __device__ __forceinline__ int warp_inclusive_scan(int v, int lane) {
 //   tile_prefix[g+1]   exclusive prefix sum of tiles per group (extra)
 //   row_total[1]       min(sum(group_sizes), m) (extra)
 //   status[1]          device status word, reset to 0 here at the start of every call (extra)
+//   tile_rec[U]        one TileRecord per live row tile; needs tile_prefix and group_offsets (extra)
 __global__ void __launch_bounds__(kMetaThreads, 1)
 group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int tile_m,
-                      int max_tiles, int32_t* __restrict__ group_offsets,
+                      int max_tiles, int32_t* group_offsets,
                       int32_t* __restrict__ tile2group, int32_t* __restrict__ tile2idx,
                       int32_t* __restrict__ total_tiles, int32_t* tile_prefix,
-                      int32_t* __restrict__ row_total, int32_t* __restrict__ status) {
+                      int32_t* __restrict__ row_total, int32_t* __restrict__ status,
+                      TileRecord* __restrict__ tile_rec,
+                      const int32_t* __restrict__ group_to_weight) {
   __shared__ int warp_rows[32];
   __shared__ int warp_tiles[32];
   __shared__ int carry_rows;
@@ -110,7 +127,7 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
     if (total_tiles) total_tiles[0] = all_tiles;
     if (row_total) row_total[0] = carry_rows < m ? carry_rows : m;
   }
-  if (tile2group == nullptr && tile2idx == nullptr) return;
+  if (tile2group == nullptr && tile2idx == nullptr && tile_rec == nullptr) return;
 
   // Pass 2: every row tile finds its group by binary search over the per-group tile prefix
   // (recomputed from group_sizes when the caller did not ask for tile_prefix).
@@ -143,6 +160,19 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
     }
     if (tile2group) tile2group[u] = gi;
     if (tile2idx) tile2idx[u] = idx;
+    if (tile_rec && tile_prefix && group_offsets && u < live_tiles) {
+      TileRecord r;
+      int rows = group_sizes[gi];
+      r.group = gi;
+      r.weight = group_to_weight ? group_to_weight[gi] : gi;
+      r.group_offset = group_offsets[gi];
+      r.group_size = rows < 0 ? 0 : rows;
+      r.tile_base = tile_prefix[gi];
+      r.tiles = tile_prefix[gi + 1] - r.tile_base;
+      r.idx = idx;
+      r.pad = 0;
+      tile_rec[u] = r;
+    }
   }
 }
 

@@ -50,12 +50,15 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
 
 /* Tile choice for one call; replaces the reference's block_m/block_k/block_n + tune-jax
  * search (tuning.py:49-58).  Pass NULL to let the library choose.
- *   tile_n   : output columns per CTA tile, one of 64, 128, 256 (tile_m is always 128,
- *              the contraction step always 64).
- *   max_ctas : cap on the persistent grid (0 = one CTA per SM). */
+ *   tile_n    : output columns per tile, one of 64, 128, 256; 0 = library's choice
+ *               (the contraction step is always 64).
+ *   max_ctas  : cap on the persistent grid (0 = one CTA per SM).
+ *   cta_group : 1 = one CTA per 128-row tile; 2 = a pair of CTAs per 256-row tile
+ *               (tile_n must be 256); 0 = library's choice. */
 typedef struct rd_tile_cfg {
   int32_t tile_n;
   int32_t max_ctas;
+  int32_t cta_group;
 } rd_tile_cfg;
 
 int rd_version(void);
@@ -110,7 +113,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
  * the whole device.  This entry point allocates and frees nothing; the group-metadata scratch
  * lives in a 64 KiB array built into the library's device image (held on every GPU that loads
  * the library until the process exits).
- *   Limit: 4*g + 2*ceil(m/128) + 9 <= 16384 (e.g. g = 256 with m up to 980,000 rows);
+ *   Limit: 12*g + 10*ceil(m/128) + 16 <= 16384 words (e.g. g = 256 with m up to 170,000 rows);
  *          beyond it the call returns RD_ERR_TOO_LARGE and does nothing.
  *   First call on each device resolves the array's device address (cudaGetSymbolAddress, with
  *          that device current); make that first call outside any stream capture.

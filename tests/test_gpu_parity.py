@@ -169,17 +169,33 @@ def test_reference_grid_trans_ragged_dot(case):
     _check_tgmm(x, dout, gs, what="grid tgmm")
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("tile_n,cta_group", [(64, 1), (128, 1), (256, 1), (256, 2)])
 @pytest.mark.parametrize("trans_rhs", [False, True])
-def test_every_tile_width(tile_n, trans_rhs):
+def test_every_tile_shape(tile_n, cta_group, trans_rhs):
+    """Every kernel instantiation, forced through rd_tile_cfg: tile widths 64/128/256 on one CTA
+    and the 256x256 tile on a CTA pair."""
     m, k, n, g = 700, 320, 520, 5
     x, A, dout = _inputs(3, m, k, n, g)
     gs = [130, 0, 257, 1, 300]
-    cfg = _lib.TileCfg(tile_n, 0)
+    cfg = _lib.TileCfg(tile_n, 0, cta_group)
     Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
-    _check_gmm(x, Aa, gs, trans_rhs=trans_rhs, cfg=cfg, what=f"tile_n={tile_n}")
+    _check_gmm(x, Aa, gs, trans_rhs=trans_rhs, cfg=cfg, what=f"tile_n={tile_n} ctas={cta_group}")
     if not trans_rhs:
-        _check_tgmm(x, dout, gs, cfg=cfg, what=f"tgmm tile_n={tile_n}")
+        _check_tgmm(x, dout, gs, cfg=cfg, what=f"tgmm tile_n={tile_n} ctas={cta_group}")
+
+
+@pytest.mark.parametrize("trans_rhs", [False, True])
+def test_cta_pair_ragged_boundaries(trans_rhs):
+    """CTA-pair tiles (256 rows) against groups that end inside the first or the second CTA's
+    half, empty groups, and k / n that are not multiples of the tile."""
+    sizes = [1, 127, 128, 129, 255, 256, 257, 0, 300, 64, 0, 513]
+    m, k, n = sum(sizes) + 40, 200, 392
+    x, A, dout = _inputs(6, m, k, n, len(sizes))
+    cfg = _lib.TileCfg(256, 0, 2)
+    Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
+    _check_gmm(x, Aa, sizes, trans_rhs=trans_rhs, cfg=cfg, what="pair ragged gmm")
+    if not trans_rhs:
+        _check_tgmm(x, dout, sizes, cfg=cfg, what="pair ragged tgmm")
 
 
 def test_group_boundaries_every_residue():
