@@ -324,9 +324,74 @@ def run_single(args):
 
     if not args.no_e2e and args.only is None:
         line["e2e"] = run_e2e(args, shape, dev, rd, x, A, dout, gs_fwd, kernels)
+    if args.only is None and not args.no_other_workloads:
+        del x, A, dout, y, dx, dA
+        torch.cuda.empty_cache()
+        line["other_workloads"] = run_other_workloads(dev, peaks)
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = run_cpu_baseline(shape, kernels)
     print(json.dumps(line), flush=True)
+
+
+def _time_ms(fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_other_workloads(dev, peaks):
+    """Short device-resident measurements of the bandwidth-bound configurations (not part of the
+    headline `value`): the decode shape (m=256 over 64 experts) and the DeepSeek-V3 shape."""
+    from gpu_ragged_dot_b200 import ops, workloads
+
+    out = {}
+    hbm = peaks["hbm_gbs"]
+
+    def entry(ms, flops, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "algorithmic_GBps": gbs,
+                "frac_of_measured_hbm": gbs / hbm}
+
+    # decode: 64 tokens x top-4 over 64 experts -> m = 256, weights 805 MB (larger than L2)
+    s = workloads.EP_DECODE
+    gs_np = workloads.group_sizes_from_routing(workloads.topk_routing(64, 64, 4, seed=5), 64)
+    gplus = int((gs_np > 0).sum())
+    x, A, _ = workloads.make_inputs(s, dev, with_dout=False)
+    gs = torch.from_numpy(gs_np).to(dev)
+    ws = ops._workspace(s.m, s.g, dev)
+    y = torch.empty((s.m, s.n), dtype=torch.bfloat16, device=dev)
+    ms = _time_ms(lambda: ops.gmm_forward(x, A, gs, out=y, workspace=ws), 30)
+    out[s.name + "_fwd"] = entry(ms, 2.0 * s.m * s.k * s.n, 2.0 * (s.m * s.k + gplus * s.k * s.n + s.m * s.n))
+    out[s.name + "_fwd"]["nonempty_groups"] = gplus
+    del x, A, y
+    torch.cuda.empty_cache()
+
+    # DeepSeek-V3 shaped: heavy-tailed groups, ~20 % empty
+    s = workloads.DEEPSEEK_V3
+    gs_np = workloads.group_sizes_deepseek(0)
+    gplus = int((gs_np > 0).sum())
+    x, A, dout = workloads.make_inputs(s, dev)
+    gs = torch.from_numpy(gs_np).to(dev)
+    ws = ops._workspace(s.m, s.g, dev)
+    y = torch.empty((s.m, s.n), dtype=torch.bfloat16, device=dev)
+    dx = torch.empty((s.m, s.k), dtype=torch.bfloat16, device=dev)
+    dA = torch.empty_like(A)
+    fl = 2.0 * s.m * s.k * s.n
+    b_gmm = 2.0 * (s.m * s.k + gplus * s.k * s.n + s.m * s.n)
+    b_tgmm = 2.0 * (s.m * s.k + s.m * s.n + s.g * s.k * s.n)
+    out[s.name + "_fwd"] = entry(_time_ms(lambda: ops.gmm_forward(x, A, gs, out=y, workspace=ws), 8), fl, b_gmm)
+    out[s.name + "_dlhs"] = entry(
+        _time_ms(lambda: ops.gmm_forward(dout, A, gs, trans_rhs=True, out=dx, workspace=ws), 8), fl, b_gmm)
+    out[s.name + "_drhs"] = entry(_time_ms(lambda: ops.tgmm_forward(x, dout, gs, out=dA, workspace=ws), 8), fl, b_tgmm)
+    out[s.name + "_fwd"]["nonempty_groups"] = gplus
+    return out
 
 
 def run_e2e(args, shape, dev, rd, x, A, dout, gs, kernels):
@@ -466,6 +531,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["fwd", "dlhs", "drhs"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -525,3 +525,11 @@ extern "C" int rd_gmm_static_scratch(const void* x, const void* A, const int32_t
                 stream);
 }
 
+#ifdef RD_TRACE
+// Debug builds only: copy CTA 0's timeline stamps (8192 x u64) to the host.
+extern "C" int rd_debug_trace(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_rd_trace, sizeof(unsigned long long) * 8192) == cudaSuccess
+             ? RD_OK
+             : RD_ERR_LAUNCH;
+}
+#endif

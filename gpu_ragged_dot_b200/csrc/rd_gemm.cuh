@@ -40,6 +40,22 @@
 #include "rd_metadata.cuh"
 #include "rd_ptx.cuh"
 
+// Optional timeline instrumentation (build with -DRD_TRACE): CTA 0 records globaltimer stamps
+// of its pipeline events into a device array read back by rd_debug_trace().
+#ifdef RD_TRACE
+__device__ unsigned long long g_rd_trace[8192];
+#define RD_TRACE_EVENT(role, idx, ev)                                                         \
+  do {                                                                                        \
+    if (blockIdx.x == 0 && (idx) < 64) {                                                      \
+      g_rd_trace[(((role) * 64 + (idx)) * 8 + (ev))] = rd::global_timer_ns();                 \
+    }                                                                                         \
+  } while (0)
+#else
+#define RD_TRACE_EVENT(role, idx, ev) \
+  do {                                \
+  } while (0)
+#endif
+
 namespace rd {
 
 constexpr int kTileM = 128;  // UMMA M per CTA == output rows per CTA tile
@@ -261,6 +277,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                   : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
         const int nb = t.n0 + cta_rank * kBCols;  // first B column this CTA loads
         const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 0);
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -268,6 +285,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
+          if (kb == 0) RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 1);
+          if (kb == kb_count - 1) RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 2);
           uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t sa = stage_base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
@@ -344,10 +363,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // ---- single CTA, or the leader of a pair
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
+      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 0);
       if (!mbar_wait<kPair>(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
         ok = false;
         break;
       }
+      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 1);
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       for (int kb = 0; kb < kb_count; ++kb, ++it) {
@@ -357,6 +378,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = false;
           break;
         }
+        if (lane == 0 && kb == 0) RD_TRACE_EVENT(1, local_tile, 2);
+        if (lane == 0 && kb == kb_count - 1) RD_TRACE_EVENT(1, local_tile, 3);
         const uint32_t sa = stage_base + s * kStageBytes;
         const uint32_t sb = sa + kABytes;
         // Contraction depth that is really there in this stage: the group's last rows (tgmm)
@@ -407,6 +430,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
       }
       if (!ok) break;
+      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 4);
       if (lane == 0) {
         const uint32_t bar = smem_u32(&bar_acc_full[acc]);
         if (kb_count > 0) {
@@ -437,10 +461,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = t.n0;
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
+      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 0);
       if (!mbar_wait<kPair>(smem_u32(&bar_acc_full[acc]), acc_ph, abort_ptr)) {
         ok = false;
         break;
       }
+      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 1);
       tc_fence_after_sync();
 
       bool row_ok;         // this thread's output row exists
@@ -535,6 +561,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 2);
       if (n_chunks == 0) {
         tc_fence_before_sync();
         __syncwarp();
