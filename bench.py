@@ -219,7 +219,8 @@ def run_single(args):
     _lib.load()  # fail loudly if the CUDA library is missing
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    shape = workloads.MIXTRAL
+    shape = {"mixtral": workloads.MIXTRAL, "decode": workloads.EP_DECODE,
+             "deepseek": workloads.DEEPSEEK_V3}[args.workload]
     peaks = measured_peaks()
     kernels = ["fwd", "dlhs", "drhs"] if args.only is None else [args.only]
     # Allocate only what the selected kernels touch (keeps profiler captures small).
@@ -228,8 +229,14 @@ def run_single(args):
         x = None
     if kernels == ["drhs"]:
         A = None
-    gs_fwd = torch.from_numpy(workloads.group_sizes_mixtral(0)).to(dev)
-    gs_bwd = torch.from_numpy(workloads.group_sizes_mixtral_ragged(0)).to(dev)
+    if args.workload == "mixtral":
+        gs_fwd_np, gs_bwd_np = workloads.group_sizes_mixtral(0), workloads.group_sizes_mixtral_ragged(0)
+    elif args.workload == "decode":
+        gs_fwd_np = gs_bwd_np = workloads.group_sizes_from_routing(workloads.topk_routing(64, 64, 4, seed=5), 64)
+    else:
+        gs_fwd_np = gs_bwd_np = workloads.group_sizes_deepseek(0)
+    gs_fwd = torch.from_numpy(gs_fwd_np).to(dev)
+    gs_bwd = torch.from_numpy(gs_bwd_np).to(dev)
     y = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev) if "fwd" in kernels else None
     dx = torch.empty((shape.m, shape.k), dtype=torch.bfloat16, device=dev) if "dlhs" in kernels else None
     dA = (torch.empty((shape.g, shape.k, shape.n), dtype=torch.bfloat16, device=dev)
@@ -280,22 +287,45 @@ def run_single(args):
         tf = gemm_flops / (ms * 1e-3) / 1e12
         per_kernel[name] = {"ms": ms, "tflops": tf, "frac_of_measured_burst": tf / peaks["bf16_tflops"],
                             "frac_of_measured_sustained": tf / peaks["bf16_tflops_sustained"]}
-    traffic = DRAM_TRAFFIC_BYTES_PER_LAUNCH
-    roofline = {
-        "bound": "tensor",
-        "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
-                   "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
-        "achieved": per_kernel[dom]["tflops"],
-        "peak": peaks["bf16_tflops"],
-        "peak_source": f"{peaks['source']} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
-        "unit": "TFLOP/s",
-        "frac": per_kernel[dom]["tflops"] / peaks["bf16_tflops"],
-        "frac_of_sustained": per_kernel[dom]["tflops"] / peaks["bf16_tflops_sustained"],
-        "traffic": traffic.get(dom),
-        "algorithmic_flops_per_launch": gemm_flops,
-        "algorithmic_bytes_per_launch": 2.0 * (shape.m * shape.k + shape.g * shape.k * shape.n + shape.m * shape.n),
-        "per_kernel": per_kernel,
+    traffic = DRAM_TRAFFIC_BYTES_PER_LAUNCH if args.workload == "mixtral" else {}
+    gplus_f, gplus_b = int((gs_fwd_np > 0).sum()), int((gs_bwd_np > 0).sum())
+    alg_bytes = {
+        "fwd": 2.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
+        "dlhs": 2.0 * (shape.m * shape.n + gplus_b * shape.k * shape.n + shape.m * shape.k),
+        "drhs": 2.0 * (shape.m * shape.k + shape.m * shape.n + shape.g * shape.k * shape.n),
     }
+    for name, ms in per_kernel_ms.items():
+        gbs = alg_bytes[name] / (ms * 1e-3) / 1e9
+        per_kernel[name]["algorithmic_GBps"] = gbs
+        per_kernel[name]["frac_of_measured_hbm"] = gbs / peaks["hbm_gbs"]
+    hbm_bound = alg_bytes[dom] / (peaks["hbm_gbs"] * 1e9) > gemm_flops / (peaks["bf16_tflops"] * 1e12)
+    if hbm_bound:
+        roofline = {
+            "bound": "hbm",
+            "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
+                       "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
+            "achieved": per_kernel[dom]["algorithmic_GBps"], "peak": peaks["hbm_gbs"],
+            "peak_source": f"{peaks['source']} (copy bandwidth)", "unit": "GB/s",
+            "frac": per_kernel[dom]["frac_of_measured_hbm"], "traffic": None,
+            "algorithmic_bytes_per_launch": alg_bytes[dom], "algorithmic_flops_per_launch": gemm_flops,
+            "per_kernel": per_kernel,
+        }
+    else:
+        roofline = {
+            "bound": "tensor",
+            "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
+                       "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
+            "achieved": per_kernel[dom]["tflops"],
+            "peak": peaks["bf16_tflops"],
+            "peak_source": f"{peaks['source']} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
+            "unit": "TFLOP/s",
+            "frac": per_kernel[dom]["tflops"] / peaks["bf16_tflops"],
+            "frac_of_sustained": per_kernel[dom]["tflops"] / peaks["bf16_tflops_sustained"],
+            "traffic": traffic.get(dom),
+            "algorithmic_flops_per_launch": gemm_flops,
+            "algorithmic_bytes_per_launch": alg_bytes[dom],
+            "per_kernel": per_kernel,
+        }
 
     line = {
         "metric": METRIC,
@@ -313,8 +343,10 @@ def run_single(args):
         "config": {
             "workload": shape.name + ("_fwd_bwd" if args.only is None else "_" + args.only),
             "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
-            "group_sizes": "fwd: multinomial(Dirichlet(2)); bwd: same, each group at a random offset mod 128",
-            "l2": "inputs larger than L2 (weights 940 MB per GEMM)",
+            "group_sizes": {"mixtral": "fwd: multinomial(Dirichlet(2)); bwd: same, each group at a random offset mod 128",
+                            "decode": "64 tokens x uniform top-4 of 64 experts",
+                            "deepseek": "multinomial(Dirichlet(0.3)), ~20% empty"}[args.workload],
+            "l2": "inputs larger than L2 (weights %d MB per GEMM)" % (shape.g * shape.k * shape.n * 2 // 1000000),
             "timing": "CUDA events on the launch stream; per-kernel events inside the timed region",
         },
         "clocks": clocks,
@@ -322,13 +354,13 @@ def run_single(args):
         "roofline": roofline,
     }
 
-    if not args.no_e2e and args.only is None:
+    if not args.no_e2e and args.only is None and args.workload == "mixtral":
         line["e2e"] = run_e2e(args, shape, dev, rd, x, A, dout, gs_fwd, kernels)
-    if args.only is None and not args.no_other_workloads:
+    if args.only is None and not args.no_other_workloads and args.workload == "mixtral":
         del x, A, dout, y, dx, dA
         torch.cuda.empty_cache()
         line["other_workloads"] = run_other_workloads(dev, peaks)
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and args.workload == "mixtral":
         line["cpu_baseline"] = run_cpu_baseline(shape, kernels)
     print(json.dumps(line), flush=True)
 
@@ -532,6 +564,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
+    ap.add_argument("--workload", default="mixtral", choices=["mixtral", "decode", "deepseek"],
+                    help="N=1 only; the headline line is the default (mixtral); the others are for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -329,6 +329,16 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // the tgmm stages whose tail rows it must clear in its own shared memory.
     const uint32_t idesc =
         make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
+    // Stage-0 operand descriptors; later stages / k-steps only add to the 16-byte-unit address.
+    constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;       // A: MN-major (tgmm) or K-major
+    constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;    // B: K-major or MN-major
+    const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
+                                  : make_smem_desc(stage_base, 16, 1024);
+    const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kABytes, 16, 1024)
+                                     : make_smem_desc(stage_base + kABytes, kBoxBytes, 1024);
+    const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
+    const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
+    const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);  // same for A and B (SBO, version, swizzle)
     uint32_t it = 0;
     uint32_t local_tile = 0;
     uint32_t tail_parity = 0;  // bit s: parity of the next tail hand-shake on stage s
@@ -371,9 +381,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (lane == 0) RD_TRACE_EVENT(1, local_tile, 1);
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
-      for (int kb = 0; kb < kb_count; ++kb, ++it) {
-        const uint32_t s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
+      uint32_t s = it % kStages;
+      uint32_t ph = (it / kStages) & 1u;
+      for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
         if (!mbar_wait<kPair>(smem_u32(&bar_full[s]), ph, abort_ptr)) {
           ok = false;
           break;
@@ -381,10 +391,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0 && kb == 0) RD_TRACE_EVENT(1, local_tile, 2);
         if (lane == 0 && kb == kb_count - 1) RD_TRACE_EVENT(1, local_tile, 3);
         const uint32_t sa = stage_base + s * kStageBytes;
-        const uint32_t sb = sa + kABytes;
-        // Contraction depth that is really there in this stage: the group's last rows (tgmm)
-        // or the last columns of k (gmm).  Whole 16-deep MMAs past it are skipped.
-        const int live = kTgmm ? t.rows - kb * kTileK : p.k - kb * kTileK;
+        // tgmm: contraction depth that is really there in this stage (the group's last rows);
+        // whole 16-deep MMAs past it are skipped.  gmm always issues all four: columns past k
+        // are zero-filled by TMA in both operands.
+        const int live = kTgmm ? t.rows - kb * kTileK : kTileK;
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
         if (kTgmm && tail_stage && kb == kb_count - 1) {
           // Rows past the end of the group belong to the next group (or to nobody): clear them,
@@ -403,21 +413,24 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after_sync();
         if (lane == 0) {
+          // The issue path sits inside the load -> MMA -> free-the-stage loop, so it is kept
+          // short: descriptors are the stage-0 descriptors plus a stage / k-step offset added
+          // to their address field, and only a tgmm tile's last stage looks at n_mma.
+          const uint32_t a_lo = adesc0_lo + s * (kStageBytes >> 4);
+          const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
+          if (kTgmm && n_mma < kTileK / kUmmaK) {
+            for (int kk = 0; kk < n_mma; ++kk) {
+              umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
+                              (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+          } else {
+            umma_f16<kCtas>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
+                            kb > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < kTileK / kUmmaK; ++kk) {
-            if (kk < n_mma) {
-              uint64_t adesc, bdesc;
-              if (kTgmm) {
-                adesc = make_smem_desc(sa + kk * 2048, kBoxBytes, 1024);
-              } else {
-                adesc = make_smem_desc(sa + kk * 32, 16, 1024);
-              }
-              if (kBKMajor) {
-                bdesc = make_smem_desc(sb + kk * 32, 16, 1024);
-              } else {
-                bdesc = make_smem_desc(sb + kk * 2048, kBoxBytes, 1024);
-              }
-              umma_f16<kCtas>(tmem_d, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
+              umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
             }
           }
           // Frees the smem stage (in both CTAs of a pair) when these MMAs retire.

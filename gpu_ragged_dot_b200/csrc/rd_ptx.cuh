@@ -342,6 +342,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+__device__ __forceinline__ uint64_t make_desc64(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B both `ab_format`
 // (0 = fp16, 1 = bf16); *_mn_major = 1 when the operand's M/N index is the contiguous one.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int ab_format, int a_mn_major,
