@@ -26,7 +26,8 @@ _c_size_t = ctypes.c_size_t
 class TileCfg(ctypes.Structure):
     """Mirror of ``rd_tile_cfg``."""
 
-    _fields_ = [("tile_n", ctypes.c_int32), ("max_ctas", ctypes.c_int32), ("cta_group", ctypes.c_int32)]
+    _fields_ = [("tile_n", ctypes.c_int32), ("max_ctas", ctypes.c_int32), ("cta_group", ctypes.c_int32),
+                ("tile_m", ctypes.c_int32)]
 
 
 SIGNATURES = {

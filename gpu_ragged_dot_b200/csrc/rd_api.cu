@@ -10,6 +10,7 @@
 
 #include "../../include/ragged_dot_b200.h"
 #include "rd_gemm.cuh"
+#include "rd_gemm2.cuh"
 #include "rd_metadata.cuh"
 #include "rd_rows.cuh"
 
@@ -178,6 +179,27 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
+template <bool kBKMajor, bool kTgmm>
+int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                 const GemmArgs& args, int ctas, cudaStream_t stream) {
+  auto kernel = rd::ragged_gemm2_kernel<kBKMajor, kTgmm>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rd::kG2SmemBytes) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  kernel<<<ctas, rd::kG2Threads, rd::kG2SmemBytes, stream>>>(ta, tb, tout, args);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+// 256-row tiles on one CTA (rd_gemm2.cuh) move a third less data per flop than 128-row tiles.
+// They pay off when a tile's second half usually exists: tgmm with k >= 256, and gmm when the
+// groups are long (mean rows per group >= 512; a half without rows is skipped, so the cost of a
+// wrong guess is only a shallower smem ring).
+bool choose_two_half(bool tgmm, long long m, int k, int g, int bn) {
+  if (bn != 256) return false;
+  if (tgmm) return k >= 256;
+  return g > 0 && m / g >= 512;
+}
+
 // CTA pairs (256 x 256 tiles, B operand split between the two CTAs) pay off where the
 // 256-row granularity wastes nothing: tgmm, whose tile rows are the dense k axis.  For gmm the
 // tile rows are a group's ragged token rows and the wider tile wastes more than the pair
@@ -277,12 +299,18 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   int cta_group = cfg ? cfg->cta_group : 0;
   if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
   if (cta_group == 0) cta_group = choose_pair(false, 0, bn, sms) ? 2 : 1;
+  int tile_m = cfg ? cfg->tile_m : 0;
+  if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
+  if (tile_m == 256 && (bn != 256 || cta_group != 1)) return RD_ERR_BAD_CONFIG;
+  if (tile_m == 0) tile_m = (cta_group == 1 && choose_two_half(false, m, k, g, bn)) ? 256 : 128;
+  const bool two_half = tile_m == 256;
 
   // Launch the metadata kernel before encoding the tensor maps: besides being the first step
   // of the call, a runtime launch binds the device's primary context to the calling thread,
   // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
   // arrive here without one).
-  launch_internal_metadata(group_sizes, group_to_weight, g, m, rd::kTileM * cta_group, w, stream);
+  launch_internal_metadata(group_sizes, group_to_weight, g, m,
+                           two_half ? rd::kG2TileRows : rd::kTileM * cta_group, w, stream);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   CUtensorMap ta, tb;
@@ -326,6 +354,10 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.out = y;
 
   const int ctas = pick_ctas(cfg);
+  if (two_half) {
+    return trans_rhs ? launch_gemm2<true, false>(ta, tb, tout, args, ctas, stream)
+                     : launch_gemm2<false, false>(ta, tb, tout, args, ctas, stream);
+  }
   if (trans_rhs) {
     if (cta_group == 2) return launch_gemm<256, true, false, 2>(ta, tb, tout, args, ctas, stream);
     if (bn == 256) return launch_gemm<256, true, false, 1>(ta, tb, tout, args, ctas, stream);
@@ -392,11 +424,23 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
                : choose_tile_n(static_cast<long long>((k + rd::kTileM - 1) / rd::kTileM) * g, n, sms);
   if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
   int cta_group = cfg ? cfg->cta_group : 0;
+  int tile_m = cfg ? cfg->tile_m : 0;
   if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
-  if (cta_group == 0)
-    cta_group =
-        choose_pair(true, static_cast<long long>((k + 255) / 256) * g * ((n + 255) / 256), bn, sms) ? 2 : 1;
-  const long long k_tiles = (k + rd::kTileM * cta_group - 1) / (rd::kTileM * cta_group);
+  if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
+  if (tile_m == 256 && (bn != 256 || cta_group == 2)) return RD_ERR_BAD_CONFIG;
+  // Preference order when nothing is forced: 256-row tiles on one CTA, then a CTA pair, then
+  // plain 128-row tiles.
+  if (tile_m == 0 && cta_group != 2) tile_m = choose_two_half(true, m, k, g, bn) ? 256 : 128;
+  if (tile_m == 0) tile_m = 128;
+  if (cta_group == 0) {
+    cta_group = (tile_m == 128 && choose_pair(true, static_cast<long long>((k + 255) / 256) * g *
+                                                        ((n + 255) / 256), bn, sms))
+                    ? 2
+                    : 1;
+  }
+  const bool two_half = tile_m == 256;
+  const int tile_rows = two_half ? rd::kG2TileRows : rd::kTileM * cta_group;
+  const long long k_tiles = (k + tile_rows - 1) / tile_rows;
 
   // Launch the metadata kernel before encoding the tensor maps: besides being the first step
   // of the call, a runtime launch binds the device's primary context to the calling thread,
@@ -442,6 +486,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.out = out;
 
   const int ctas = pick_ctas(cfg);
+  if (two_half) return launch_gemm2<false, true>(ta, tb, tout, args, ctas, stream);
   if (cta_group == 2) return launch_gemm<256, false, true, 2>(ta, tb, tout, args, ctas, stream);
   if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);
   if (bn == 128) return launch_gemm<128, false, true, 1>(ta, tb, tout, args, ctas, stream);

@@ -1,0 +1,403 @@
+// Grouped GEMM kernels with 256-row tiles on ONE CTA ("two-half" tiles).
+//
+// The 128 x 256 kernel in rd_gemm.cuh is bound by how fast shared memory can be refilled:
+// every 64-deep stage moves 16 KB of A and 32 KB of B for 128 x 256 x 64 MMAs, and with four
+// 48 KB stages in flight the load -> MMA -> free-the-stage loop (about 1.6 us) caps the tensor
+// pipe near 75 %.  Here a CTA owns a 256 x 256 tile as two 128-row halves that share each B
+// stage: per stage 32 KB of A + 32 KB of B feed twice the MMAs, a third less traffic per flop,
+// which three 64 KB stages can sustain.  The price is TMEM: the two halves use both 256-column
+// accumulators, so a tile's epilogue no longer overlaps the next tile's main loop by double
+// buffering; instead eight epilogue warps drain the two halves at once and each half's
+// accumulator is handed back as soon as it has been read.
+//
+// A half that has no rows (the last tile of a group with <= 128 rows left; the last 128 rows
+// of k in tgmm) is skipped entirely -- no loads, no MMAs -- so nothing is wasted beyond the
+// 128-row granularity of the other kernel.
+//
+// Same roles, operand layouts, barrier discipline (bounded waits) and epilogue (swizzled smem
+// staging + TMA stores, row-masked stores where a gmm slab crosses its group's end) as
+// rd_gemm.cuh; the helpers of that file are reused.
+#pragma once
+
+#include "rd_gemm.cuh"
+
+namespace rd {
+
+constexpr int kG2EpilogueWarps = 8;
+constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps;
+constexpr int kG2Stages = 3;
+constexpr int kG2TileN = 256;
+constexpr int kG2TileRows = 2 * kTileM;
+constexpr uint32_t kG2ABytes = 2 * kTileM * kTileK * 2;   // two 128-row halves
+constexpr uint32_t kG2BBytes = kG2TileN * kTileK * 2;
+constexpr uint32_t kG2StageBytes = kG2ABytes + kG2BBytes;  // 64 KB
+constexpr int kG2SmemBytes = kG2Stages * kG2StageBytes + kG2EpilogueWarps * kOutBoxBytes + 1024;
+
+// rows: valid rows of the whole 256-row tile (gmm) / rows of the group (tgmm).
+__device__ __forceinline__ TileCoord decode_gmm_tile256(const GemmArgs& p, int tile) {
+  const int mt = tile / p.n_tiles;
+  const int4* rp = reinterpret_cast<const int4*>(p.tile_rec + mt);
+  const int4 a = rp[0];  // group, weight, group_offset, group_size
+  const int4 b = rp[1];  // tile_base, tiles, idx, pad
+  const int local = tile - b.x * p.n_tiles;
+  const int nt = local / b.y;
+  const int mi = local - nt * b.y;
+  TileCoord t;
+  t.group = a.x;
+  t.weight = a.y;
+  t.row0 = a.z + mi * kG2TileRows;
+  t.rows = imin(kG2TileRows, a.w - mi * kG2TileRows);
+  t.rows = imin(t.rows, p.m - t.row0);
+  t.n0 = nt * kG2TileN;
+  t.k0 = 0;
+  return t;
+}
+
+__device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int tile) {
+  const int per_group = p.k_tiles * p.n_tiles;
+  const int gi = tile / per_group;
+  const int rem = tile - gi * per_group;
+  const int kt = rem / p.n_tiles;
+  const int nt = rem - kt * p.n_tiles;
+  TileCoord t;
+  t.group = gi;
+  t.weight = gi;
+  t.row0 = p.group_offsets[gi];
+  t.rows = imax(imin(imax(p.group_sizes[gi], 0), p.m - t.row0), 0);
+  t.n0 = nt * kG2TileN;
+  t.k0 = kt * kG2TileRows;
+  return t;
+}
+
+template <bool kBKMajor, bool kTgmm>
+__global__ void __launch_bounds__(kG2Threads, 1)
+ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
+  static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
+  constexpr int BN = kG2TileN;
+  constexpr int kStages = kG2Stages;
+  constexpr uint32_t kHalfABytes = kTileM * kTileK * 2;  // 16 KB
+  constexpr uint32_t kTmemCols = 2 * BN;                 // accumulator of half h at column h * BN
+
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];   // per half
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];  // per half
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_out);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(smem_u32(&bar_acc_full[h]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[h]), 4);  // the four epilogue warps of that half
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  const int num_tiles =
+      kTgmm ? p.g * p.k_tiles * p.n_tiles : imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
+  const int k_blocks_gmm = (p.k + kTileK - 1) / kTileK;
+  const int tile_step = static_cast<int>(gridDim.x);
+
+  // Number of 128-row halves of a tile that exist.
+  auto halves_of = [&](const TileCoord& t) -> int {
+    if (kTgmm) return (t.k0 + kTileM < p.k) ? 2 : 1;
+    return t.rows > kTileM ? 2 : 1;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+        const int halves = halves_of(t);
+        const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t sa = stage_base + s * kG2StageBytes;
+          const uint32_t sb = sa + kG2ABytes;
+          mbar_arrive_expect_tx(full, halves * kHalfABytes + kG2BBytes);
+          if (kTgmm) {
+            const int r = t.row0 + kb * kTileK;
+            for (int h = 0; h < halves; ++h) {
+              tma_load_2d(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r);
+              tma_load_2d(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r);
+            }
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * kBoxBytes, &tmap_b, full, t.n0 + j * 64, r);
+          } else {
+            for (int h = 0; h < halves; ++h)
+              tma_load_2d(sa + h * kHalfABytes, &tmap_a, full, kb * kTileK, t.row0 + h * kTileM);
+            if (kBKMajor) {
+              tma_load_3d(sb, &tmap_b, full, kb * kTileK, t.n0, t.weight);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * kBoxBytes, &tmap_b, full, t.n0 + j * 64, kb * kTileK, t.weight);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM, BN);
+    constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;
+    constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;
+    const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
+                                  : make_smem_desc(stage_base, 16, 1024);
+    const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kG2ABytes, 16, 1024)
+                                     : make_smem_desc(stage_base + kG2ABytes, kBoxBytes, 1024);
+    const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
+    const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
+    const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);
+    uint32_t it = 0;
+    uint32_t uses[2] = {0u, 0u};  // how often each half's accumulator has been used
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
+      const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+      const int halves = halves_of(t);
+      const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+
+      if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h < halves) {
+            if (!mbar_wait(smem_u32(&bar_acc_empty[h]), (uses[h] & 1u) ^ 1u, abort_ptr)) {
+              ok = false;
+              break;
+            }
+            ++uses[h];
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_full[h]));
+          }
+        }
+        __syncwarp();
+        continue;
+      }
+
+      uint32_t s = it % kStages;
+      uint32_t ph = (it / kStages) & 1u;
+      for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_ptr)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sa = stage_base + s * kG2StageBytes;
+        const int live = kTgmm ? t.rows - kb * kTileK : kTileK;
+        const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
+        if (kTgmm && tail_stage && kb == kb_count - 1) {
+          clear_tail_rows<kG2StageBytes / kBoxBytes>(sa, live, lane);
+          __syncwarp();
+        }
+        const bool last = kb == kb_count - 1;
+        const uint32_t b_lo = bdesc0_lo + s * (kG2StageBytes >> 4);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h < halves) {
+            if (kb == 0) {  // the half's accumulator must have been drained by the epilogue
+              if (!mbar_wait(smem_u32(&bar_acc_empty[h]), (uses[h] & 1u) ^ 1u, abort_ptr)) {
+                ok = false;
+                break;
+              }
+              ++uses[h];
+            }
+            tc_fence_after_sync();
+            if (lane == 0) {
+              const uint32_t tmem_d = tmem_base + h * BN;
+              const uint32_t a_lo = adesc0_lo + s * (kG2StageBytes >> 4) + h * (kHalfABytes >> 4);
+              if (kTgmm && n_mma < kTileK / kUmmaK) {
+                for (int kk = 0; kk < n_mma; ++kk) {
+                  umma_f16<1>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
+                              (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+              } else {
+                umma_f16<1>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
+                            kb > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
+                  umma_f16<1>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
+                }
+              }
+              if (last) umma_commit(smem_u32(&bar_acc_full[h]));  // this half is complete
+            }
+            __syncwarp();
+          }
+        }
+        if (!ok) break;
+        if (lane == 0) umma_commit(smem_u32(&bar_empty[s]));  // both halves have read the stage
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Warps 2..5 drain half 0, warps 6..9 half 1; within a half a warp owns the 32 TMEM lanes
+    // of its quarter (warp index mod 4).
+    const int half = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int r_in_tile = half * kTileM + quarter * 32 + lane;
+    const uint32_t buf = stage_base + kStages * kG2StageBytes + (warp - 2) * kOutBoxBytes;
+    uint32_t uses = 0;
+    bool ok = true;
+    uint16_t* out16 = reinterpret_cast<uint16_t*>(p.out);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
+      const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+      if (half >= halves_of(t)) continue;  // this half does not exist in this tile
+      const int n0 = t.n0;
+      if (!mbar_wait(smem_u32(&bar_acc_full[half]), uses & 1u, abort_ptr)) {
+        ok = false;
+        break;
+      }
+      ++uses;
+      tc_fence_after_sync();
+
+      bool row_ok, warp_has_rows, slab_by_tma, zero_only = false;
+      size_t row_off;
+      int out_row0;
+      const int slab0 = half * kTileM + quarter * 32;  // first tile row of this warp's slab
+      if (kTgmm) {
+        const int kr = t.k0 + r_in_tile;
+        out_row0 = t.k0 + slab0;
+        row_ok = kr < p.k;
+        warp_has_rows = out_row0 < p.k;
+        slab_by_tma = true;
+        row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
+        zero_only = t.rows <= 0;
+      } else {
+        out_row0 = t.row0 + slab0;
+        row_ok = r_in_tile < t.rows;
+        warp_has_rows = slab0 < t.rows;
+        slab_by_tma = slab0 + 32 <= t.rows;
+        row_off = static_cast<size_t>(t.row0 + r_in_tile) * static_cast<size_t>(p.n);
+      }
+
+      const int n_chunks = warp_has_rows ? imin(BN / 64, (p.n - n0 + 63) / 64) : 0;
+      const uint32_t acc_empty_bar = smem_u32(&bar_acc_empty[half]);
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; ++c) {
+        const int col = n0 + c * 64;
+        uint32_t v[64];
+        if (!zero_only) {
+          const uint32_t taddr =
+              tmem_base + half * BN + c * 64 + (static_cast<uint32_t>(quarter * 32) << 16);
+          tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) v[j] = 0u;
+        }
+        if (c == n_chunks - 1) {  // the accumulator is in registers: hand it back
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar);
+        }
+        uint4 o[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          o[q].x = pack2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), p.ab_format);
+          o[q].y = pack2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), p.ab_format);
+          o[q].z = pack2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), p.ab_format);
+          o[q].w = pack2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), p.ab_format);
+        }
+        if (slab_by_tma) {
+          if (lane == 0) bulk_wait_group_read<0>();  // the previous box has left this buffer
+          __syncwarp();
+          const uint32_t row_addr = buf + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t a = row_addr + (((q ^ (lane & 7)) & 7) << 4);  // 128-byte swizzle
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[q].x),
+                         "r"(o[q].y), "r"(o[q].z), "r"(o[q].w)
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (kTgmm) {
+              tma_store_3d(&tmap_out, buf, col, out_row0, t.group);
+            } else {
+              tma_store_2d(&tmap_out, buf, col, out_row0);
+            }
+            bulk_commit_group();
+          }
+        } else if (row_ok) {
+          uint16_t* dst = out16 + row_off + col;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col + q * 8 < p.n) *reinterpret_cast<uint4*>(dst + q * 8) = o[q];
+          }
+        }
+      }
+      if (n_chunks == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar);
+      }
+    }
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
+
+    if (!kTgmm) {
+      // Rows past sum(group_sizes) belong to no group and are defined as zero.
+      constexpr int kEpiThreads = 32 * kG2EpilogueWarps;
+      const int first = imin(imax(p.totals[1], 0), p.m);
+      const size_t chunks_per_row = static_cast<size_t>(p.n) / 8;
+      const size_t total = static_cast<size_t>(p.m - first) * chunks_per_row;
+      const size_t tid = static_cast<size_t>(blockIdx.x) * kEpiThreads + (threadIdx.x - 64);
+      const size_t stride = static_cast<size_t>(gridDim.x) * kEpiThreads;
+      uint4* dst = reinterpret_cast<uint4*>(out16 + static_cast<size_t>(first) * p.n);
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      for (size_t i = tid; i < total; i += stride) dst[i] = z;
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncthreads();
+  if (abort_flag) {
+    if (threadIdx.x == 0) atomicMax(p.status, static_cast<int32_t>(kStatusWaitExpired));
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace rd

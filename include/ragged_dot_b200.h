@@ -53,12 +53,15 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
  *   tile_n    : output columns per tile, one of 64, 128, 256; 0 = library's choice
  *               (the contraction step is always 64).
  *   max_ctas  : cap on the persistent grid (0 = one CTA per SM).
- *   cta_group : 1 = one CTA per 128-row tile; 2 = a pair of CTAs per 256-row tile
- *               (tile_n must be 256); 0 = library's choice. */
+ *   cta_group : 1 = one CTA per tile; 2 = a pair of CTAs per 256-row tile
+ *               (tile_n must be 256, tile_m must not be 256); 0 = library's choice.
+ *   tile_m    : 128, or 256 = one CTA computes 256-row tiles as two 128-row halves sharing
+ *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice. */
 typedef struct rd_tile_cfg {
   int32_t tile_n;
   int32_t max_ctas;
   int32_t cta_group;
+  int32_t tile_m;
 } rd_tile_cfg;
 
 int rd_version(void);

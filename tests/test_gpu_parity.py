@@ -169,29 +169,31 @@ def test_reference_grid_trans_ragged_dot(case):
     _check_tgmm(x, dout, gs, what="grid tgmm")
 
 
-@pytest.mark.parametrize("tile_n,cta_group", [(64, 1), (128, 1), (256, 1), (256, 2)])
+@pytest.mark.parametrize("tile_n,cta_group,tile_m",
+                         [(64, 1, 128), (128, 1, 128), (256, 1, 128), (256, 2, 128), (256, 1, 256)])
 @pytest.mark.parametrize("trans_rhs", [False, True])
-def test_every_tile_shape(tile_n, cta_group, trans_rhs):
-    """Every kernel instantiation, forced through rd_tile_cfg: tile widths 64/128/256 on one CTA
-    and the 256x256 tile on a CTA pair."""
+def test_every_tile_shape(tile_n, cta_group, tile_m, trans_rhs):
+    """Every kernel instantiation, forced through rd_tile_cfg: tile widths 64/128/256 on one CTA,
+    the 256x256 tile on a CTA pair, and the 256x256 two-half tile on one CTA."""
     m, k, n, g = 700, 320, 520, 5
     x, A, dout = _inputs(3, m, k, n, g)
     gs = [130, 0, 257, 1, 300]
-    cfg = _lib.TileCfg(tile_n, 0, cta_group)
+    cfg = _lib.TileCfg(tile_n, 0, cta_group, tile_m)
     Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
     _check_gmm(x, Aa, gs, trans_rhs=trans_rhs, cfg=cfg, what=f"tile_n={tile_n} ctas={cta_group}")
     if not trans_rhs:
         _check_tgmm(x, dout, gs, cfg=cfg, what=f"tgmm tile_n={tile_n} ctas={cta_group}")
 
 
+@pytest.mark.parametrize("cta_group,tile_m", [(2, 128), (1, 256)])
 @pytest.mark.parametrize("trans_rhs", [False, True])
-def test_cta_pair_ragged_boundaries(trans_rhs):
-    """CTA-pair tiles (256 rows) against groups that end inside the first or the second CTA's
-    half, empty groups, and k / n that are not multiples of the tile."""
+def test_256_row_tiles_ragged_boundaries(cta_group, tile_m, trans_rhs):
+    """256-row tiles (CTA pair, and two-half on one CTA) against groups that end inside the
+    first or the second half, empty groups, and k / n that are not multiples of the tile."""
     sizes = [1, 127, 128, 129, 255, 256, 257, 0, 300, 64, 0, 513]
     m, k, n = sum(sizes) + 40, 200, 392
     x, A, dout = _inputs(6, m, k, n, len(sizes))
-    cfg = _lib.TileCfg(256, 0, 2)
+    cfg = _lib.TileCfg(256, 0, cta_group, tile_m)
     Aa = A.transpose(1, 2).contiguous() if trans_rhs else A
     _check_gmm(x, Aa, sizes, trans_rhs=trans_rhs, cfg=cfg, what="pair ragged gmm")
     if not trans_rhs:
