@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(PKG_DIR, "librd_b200.so")
 RD_OK = 0
 RD_DTYPE_F16 = 0
 RD_DTYPE_BF16 = 1
+RD_CFG_NO_ZERO_TAIL = 1
 
 # Every symbol include/ragged_dot_b200.h declares, with its ctypes signature.
 _c_int = ctypes.c_int
@@ -27,7 +28,7 @@ class TileCfg(ctypes.Structure):
     """Mirror of ``rd_tile_cfg``."""
 
     _fields_ = [("tile_n", ctypes.c_int32), ("max_ctas", ctypes.c_int32), ("cta_group", ctypes.c_int32),
-                ("tile_m", ctypes.c_int32)]
+                ("tile_m", ctypes.c_int32), ("flags", ctypes.c_int32)]
 
 
 SIGNATURES = {
@@ -57,6 +58,14 @@ SIGNATURES = {
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
     "rd_gather_rows": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]),
+    "rd_ep_count": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
+    "rd_ep_plan": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                            _c_void_p]),
+    "rd_ep_dispatch": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+         _c_int, _c_void_p, _c_void_p],
+    ),
     "rd_device_status": (_c_int, [_c_void_p, _c_void_p]),
     "rd_gmm_static_scratch": (
         _c_int,

@@ -10,6 +10,7 @@
 
 #include "../../include/ragged_dot_b200.h"
 #include "rd_gemm.cuh"
+#include "rd_dispatch.cuh"
 #include "rd_gemm2.cuh"
 #include "rd_metadata.cuh"
 #include "rd_rows.cuh"
@@ -346,6 +347,7 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.k_tiles = 0;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.zero_tail = (cfg && (cfg->flags & RD_CFG_NO_ZERO_TAIL)) ? 0 : 1;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
   args.tile_rec = w.tile_rec();
@@ -398,6 +400,51 @@ int rd_gather_rows(const void* src, const int32_t* row_index, void* dst, int row
   rd::gather_rows_kernel<<<blocks, rd::kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), row_index, static_cast<uint4*>(dst), rows_out, rows_in,
       row_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_count(const int32_t* routing, int entries, int num_experts, int32_t* counts, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (entries < 0 || num_experts <= 0 || num_experts > 8192) return RD_ERR_BAD_SHAPE;
+  if (counts == nullptr || (entries > 0 && routing == nullptr)) return RD_ERR_BAD_POINTER;
+  if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * num_experts, stream) != cudaSuccess)
+    return RD_ERR_LAUNCH;
+  if (entries == 0) return RD_OK;
+  int blocks = (entries + rd::kEpThreads - 1) / rd::kEpThreads;
+  if (blocks > sm_count()) blocks = sm_count();
+  rd::ep_count_kernel<<<blocks, rd::kEpThreads, sizeof(int32_t) * num_experts, stream>>>(
+      routing, entries, num_experts, counts);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, int32_t* dest_offset,
+               int32_t* segment_sizes, int32_t* fill, int32_t* totals, void* stream) {
+  if (world <= 0 || num_experts <= 0 || num_experts % world != 0 || rank < 0 || rank >= world)
+    return RD_ERR_BAD_SHAPE;
+  if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals) return RD_ERR_BAD_POINTER;
+  rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
+                   int num_experts, int world, const int32_t* dest_offset, int32_t* fill,
+                   const uint64_t* peer_base, int capacity_rows, int32_t* dest_pos, void* stream) {
+  if (tokens < 0 || top_k <= 0 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 ||
+      num_experts <= 0 || num_experts % world != 0 || capacity_rows < 0)
+    return RD_ERR_BAD_SHAPE;
+  if (tokens == 0) return RD_OK;
+  if (!aligned16(x) || !routing || !dest_offset || !fill || !peer_base || !dest_pos)
+    return RD_ERR_BAD_POINTER;
+  const long long entries = static_cast<long long>(tokens) * top_k;
+  const int warps_per_block = rd::kEpThreads / 32;
+  long long blocks = (entries + warps_per_block - 1) / warps_per_block;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  rd::ep_dispatch_kernel<<<static_cast<int>(blocks), rd::kEpThreads, 0,
+                           static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), routing, tokens, top_k, row_bytes / 16, num_experts,
+      num_experts / world, dest_offset, fill, peer_base, capacity_rows, dest_pos);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -478,6 +525,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.k_tiles = static_cast<int>(k_tiles);
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.zero_tail = 0;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
   args.tile_rec = w.tile_rec();

@@ -1,0 +1,114 @@
+// Expert-parallel dispatch without a host round trip: token rows go straight from the local
+// token matrix into the receive buffers of the ranks that own their experts, through peer
+// (NVLink) stores.  It replaces "sort by expert + gather + all-to-all with host-known split
+// sizes" by three small stream-ordered kernels around one exchange of the per-expert counts:
+//
+//   ep_count_kernel     counts[e] = number of (token, slot) pairs routed to expert e
+//   (all ranks exchange counts -> counts_all[W][E]; a tiny all-gather, done by the caller)
+//   ep_plan_kernel      from counts_all: where this rank's rows for expert e start inside the
+//                       owner's receive buffer, and the sizes of the W * El segments this rank
+//                       will receive (they are the group_sizes of the local rd_gmm_indexed)
+//   ep_dispatch_kernel  one warp per (token, slot): copies the row into
+//                       peer_base[owner] + position * row_bytes with 16-byte stores
+//
+// Receive-buffer layout on every rank: segments ordered (source rank, local expert); segment
+// (s, e) holds the rows source s routed to local expert e.  Rows inside a segment land in
+// arrival order (an atomic counter per expert); dest_pos records where each (token, slot) went
+// so results can be brought back.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rd {
+
+constexpr int kEpThreads = 256;
+
+__global__ void __launch_bounds__(kEpThreads)
+ep_count_kernel(const int32_t* __restrict__ routing, int entries, int num_experts,
+                int32_t* __restrict__ counts) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < entries; i += gridDim.x * blockDim.x) {
+    const int e = routing[i];
+    if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
+    if (hist[e]) atomicAdd(&counts[e], hist[e]);
+}
+
+// One CTA.  counts_all[s * E + e]: rows source s routes to global expert e.
+//   dest_offset[e]        first row, inside the receive buffer of e's owner, of MY rows for e
+//   segment_sizes[s*El+j] rows I receive from source s for my local expert j
+//   fill[e]               reset to 0 (arrival counters used by the dispatch kernel)
+//   totals[0]             rows I receive in all
+__global__ void __launch_bounds__(kEpThreads)
+ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int num_experts, int rank,
+               int32_t* __restrict__ dest_offset, int32_t* __restrict__ segment_sizes,
+               int32_t* __restrict__ fill, int32_t* __restrict__ totals) {
+  const int local = num_experts / world;
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const int owner = e / local;
+    const int first = owner * local;
+    int off = 0;
+    for (int s = 0; s < rank; ++s)
+      for (int j = 0; j < local; ++j) off += counts_all[s * num_experts + first + j];
+    for (int j = first; j < e; ++j) off += counts_all[rank * num_experts + j];
+    dest_offset[e] = off;
+    fill[e] = 0;
+  }
+  for (int i = threadIdx.x; i < world * local; i += blockDim.x) {
+    const int s = i / local, j = i - s * local;
+    segment_sizes[i] = counts_all[s * num_experts + rank * local + j];
+  }
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int s = 0; s < world; ++s)
+      for (int j = 0; j < local; ++j) total += counts_all[s * num_experts + rank * local + j];
+    totals[0] = total;
+  }
+}
+
+// peer_base[r]: address of rank r's receive buffer as seen from this GPU (its own buffer for
+// r == rank).  capacity_rows: rows each receive buffer can hold; a position beyond it is
+// dropped and reported as -1 in dest_pos.
+__global__ void __launch_bounds__(kEpThreads)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ routing, int tokens,
+                   int top_k, int vecs_per_row, int num_experts, int experts_per_rank,
+                   const int32_t* __restrict__ dest_offset, int32_t* __restrict__ fill,
+                   const uint64_t* __restrict__ peer_base, int capacity_rows,
+                   int32_t* __restrict__ dest_pos) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kEpThreads / 32;
+  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * warps_per_block;
+  const int entries = tokens * top_k;
+  for (int i = warp_global; i < entries; i += warp_stride) {
+    const int e = routing[i];
+    int pos = -1;
+    if (e >= 0 && e < num_experts) {
+      if (lane == 0) pos = dest_offset[e] + atomicAdd(&fill[e], 1);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      if (pos >= capacity_rows) pos = -1;
+    }
+    if (lane == 0) dest_pos[i] = pos;
+    if (pos < 0) continue;
+    const int owner = e / experts_per_rank;
+    const uint4* src = x + static_cast<size_t>(i / top_k) * vecs_per_row;
+    uint4* dst = reinterpret_cast<uint4*>(peer_base[owner]) + static_cast<size_t>(pos) * vecs_per_row;
+    int v = lane;
+    for (; v + 96 < vecs_per_row; v += 128) {
+      const uint4 a = src[v], b = src[v + 32], c = src[v + 64], d = src[v + 96];
+      dst[v] = a;
+      dst[v + 32] = b;
+      dst[v + 64] = c;
+      dst[v + 96] = d;
+    }
+    for (; v < vecs_per_row; v += 32) dst[v] = src[v];
+  }
+  __threadfence_system();  // rows must be visible to their owners before the ranks synchronise
+}
+
+}  // namespace rd

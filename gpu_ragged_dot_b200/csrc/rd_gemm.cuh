@@ -77,6 +77,7 @@ struct GemmArgs {
   int k_tiles;      // tgmm: tiles along the output's k axis (128 * kCtas rows each); gmm: unused
   int max_m_tiles;  // static upper bound on live row tiles (gmm)
   int ab_format;    // 0 = fp16, 1 = bf16
+  int zero_tail;    // gmm: write zeros to the rows past sum(group_sizes)
   const int32_t* group_sizes;
   const int32_t* group_offsets;
   const TileRecord* tile_rec;  // gmm: one record per live row tile (of 128 * kCtas rows)
@@ -591,7 +592,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) bulk_wait_group<0>();
     __syncwarp();
 
-    if (!kTgmm) {
+    if (!kTgmm && p.zero_tail) {
       // Rows past sum(group_sizes) belong to no group: jax.lax.ragged_dot defines them as 0
       // (the reference writes them from its last live program, gpu_ragged_dot.py:155-165).
       const int first = imin(imax(p.totals[1], 0), p.m);

@@ -372,7 +372,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) bulk_wait_group<0>();
     __syncwarp();
 
-    if (!kTgmm) {
+    if (!kTgmm && p.zero_tail) {
       // Rows past sum(group_sizes) belong to no group and are defined as zero.
       constexpr int kEpiThreads = 32 * kG2EpilogueWarps;
       const int first = imin(imax(p.totals[1], 0), p.m);

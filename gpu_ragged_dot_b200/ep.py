@@ -15,6 +15,13 @@ Per step, on each rank (T tokens, top_k routing, E experts, El = E / W per rank)
 
 `plan_dispatch` and `exchange_rows` use only torch + torch.distributed and run on any backend
 (the CPU tests drive them over gloo); `ExpertParallelRaggedDot` adds the CUDA steps.
+
+A second dispatch mode, ``dispatch="p2p"``, has no host round trip at all: the counts are
+all-gathered (NCCL, E int32 per rank), `rd_ep_plan` turns them into write offsets on the device,
+and `rd_ep_dispatch` stores every row directly into the owner's receive buffer through peer
+memory (torch symmetric memory supplies the peer addresses and the cross-rank barrier).  The
+receive buffer has a fixed capacity (every row of every rank could land on one rank), the
+local GEMM gets that capacity as its static row bound and the true segment sizes on the device.
 """
 
 from __future__ import annotations
@@ -77,9 +84,13 @@ class ExpertParallelRaggedDot:
     """Holds this rank's experts' weights and runs the four steps above on its GPU."""
 
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None):
+                 dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
+                 dispatch: str = "nccl", capacity_rows: Optional[int] = None):
         from . import workloads
 
+        assert dispatch in ("nccl", "p2p")
+        self.dispatch, self.capacity_rows, self._p2p = dispatch, capacity_rows, None
+        self.dtype = dtype
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -101,9 +112,71 @@ class ExpertParallelRaggedDot:
             tot["gemm"] += e[2].elapsed_time(e[3])
         return {k: v / max(steps, 1) for k, v in tot.items()}
 
+    # ------------------------------------------------------------------ peer-store dispatch
+    def _p2p_setup(self, capacity_rows: int):
+        """Allocate the receive buffer in symmetric memory and fetch every rank's address."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty((capacity_rows, self.k), dtype=self.dtype, device=self.device)
+        if self.world > 1:
+            hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+        else:
+            hdl, ptrs = None, [buf.data_ptr()]
+        self._p2p = {
+            "buf": buf, "hdl": hdl, "capacity": capacity_rows,
+            "peer_base": torch.tensor(ptrs, dtype=torch.int64, device=self.device),
+            "counts_all": torch.empty((self.world, self.num_experts), dtype=torch.int32, device=self.device),
+            "y": torch.empty((capacity_rows, self.n), dtype=self.dtype, device=self.device),
+            "seg2e": torch.arange(self.local_experts, dtype=torch.int32, device=self.device).repeat(self.world),
+        }
+
+    def forward_p2p(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
+        """Dispatch by peer stores + local ragged_dot, fully stream-ordered (no host sync).
+
+        Returns (y [capacity, n], segment_sizes [W*El], dest_pos [T, top_k], totals [1]); only the
+        first totals[0] rows of y are defined; dest_pos says where on its owner each row went."""
+        from . import _lib, ops
+
+        tokens, top_k = routing.shape
+        if self._p2p is None:
+            cap = self.capacity_rows or tokens * top_k * self.world
+            self._p2p_setup(cap)
+        st = self._p2p
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
+        if timed:
+            ev[0].record()
+        routing = routing.to(torch.int32)
+        counts = ops.ep_count(routing, self.num_experts)
+        if self.world > 1:
+            # Also the "receive buffers are free again" barrier: it cannot complete before every
+            # rank has finished the GEMM of its previous step (stream order on each rank).
+            dist.all_gather_into_tensor(st["counts_all"].view(-1), counts, group=self.group)
+        else:
+            st["counts_all"].copy_(counts.view(1, -1))
+        dest_offset, seg_sizes, fill, totals = ops.ep_plan(st["counts_all"], self.rank)
+        if timed:
+            ev[1].record()
+        dest_pos = ops.ep_dispatch(x_tokens, routing, self.num_experts, self.world, dest_offset, fill,
+                                   st["peer_base"], st["capacity"])
+        if self.world > 1:
+            st["hdl"].barrier(channel=0)  # every rank's rows have landed everywhere
+        if timed:
+            ev[2].record()
+        cfg = _lib.TileCfg(0, 0, 0, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        y = ops.gmm_forward(st["buf"], self.weights, seg_sizes, group_to_weight=st["seg2e"], cfg=cfg,
+                            out=st["y"])
+        if timed:
+            ev[3].record()
+            self._events.append(ev)
+        return y, seg_sizes, dest_pos, totals
+
     def forward(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
         """Returns (y [rows_received, n], plan).  y's rows are ordered (source rank, local expert)."""
         from . import ops
+
+        if self.dispatch == "p2p":
+            return self.forward_p2p(x_tokens, routing, timed=timed)
 
         plan = plan_dispatch(routing, self.num_experts, self.group)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None

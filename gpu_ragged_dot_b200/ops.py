@@ -224,6 +224,55 @@ def gather_rows(src: torch.Tensor, row_index: torch.Tensor, out: Optional[torch.
     return dst
 
 
+def ep_count(routing: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """counts[e] of a [tokens, top_k] int32 routing table (``rd_ep_count``)."""
+    lib = _lib.load()
+    r = _as_i32(routing.reshape(-1))
+    counts = torch.empty(num_experts, dtype=torch.int32, device=r.device)
+    with torch.cuda.device(r.device):
+        rc = lib.rd_ep_count(r.data_ptr(), r.numel(), num_experts, counts.data_ptr(), _stream_ptr(r.device))
+    _lib.check(rc, "rd_ep_count")
+    return counts
+
+
+def ep_plan(counts_all: torch.Tensor, rank: int):
+    """(dest_offset[E], segment_sizes[W*El], fill[E], totals[1]) from counts_all[W, E] (``rd_ep_plan``)."""
+    lib = _lib.load()
+    assert counts_all.dim() == 2 and counts_all.dtype == torch.int32 and counts_all.is_contiguous()
+    world, experts = counts_all.shape
+    dev = counts_all.device
+    dest_offset = torch.empty(experts, dtype=torch.int32, device=dev)
+    segment_sizes = torch.empty(experts, dtype=torch.int32, device=dev)  # world * (experts / world)
+    fill = torch.empty(experts, dtype=torch.int32, device=dev)
+    totals = torch.empty(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.rd_ep_plan(counts_all.data_ptr(), world, experts, rank, dest_offset.data_ptr(),
+                            segment_sizes.data_ptr(), fill.data_ptr(), totals.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "rd_ep_plan")
+    return dest_offset, segment_sizes, fill, totals
+
+
+def ep_dispatch(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world: int,
+                dest_offset: torch.Tensor, fill: torch.Tensor, peer_base: torch.Tensor,
+                capacity_rows: int) -> torch.Tensor:
+    """Copy every routed row of x into its owner's receive buffer (``rd_ep_dispatch``);
+    peer_base is an int64 device tensor of `world` buffer addresses.  Returns dest_pos."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    x = _dense16(x)
+    r = _as_i32(routing.reshape(-1))
+    tokens, top_k = routing.shape
+    assert peer_base.dtype == torch.int64 and peer_base.numel() == world and peer_base.is_cuda
+    dest_pos = torch.empty(tokens * top_k, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_ep_dispatch(x.data_ptr(), r.data_ptr(), tokens, top_k, x.shape[1] * x.element_size(),
+                                num_experts, world, dest_offset.data_ptr(), fill.data_ptr(),
+                                peer_base.data_ptr(), capacity_rows, dest_pos.data_ptr(),
+                                _stream_ptr(x.device))
+    _lib.check(rc, "rd_ep_dispatch")
+    return dest_pos.view(tokens, top_k)
+
+
 def tgmm_forward(
     x: torch.Tensor,
     y: torch.Tensor,

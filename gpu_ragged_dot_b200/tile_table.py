@@ -40,5 +40,5 @@ def lookup(op: str, m: int, k: int, n: int, g: int) -> Optional[_lib.TileCfg]:
             and e.get("m_min", 0) <= m <= e.get("m_max", 1 << 62)
         ):
             return _lib.TileCfg(int(e["tile_n"]), int(e.get("max_ctas", 0)), int(e.get("cta_group", 0)),
-                                int(e.get("tile_m", 0)))
+                                int(e.get("tile_m", 0)), 0)
     return None

@@ -56,12 +56,16 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
  *   cta_group : 1 = one CTA per tile; 2 = a pair of CTAs per 256-row tile
  *               (tile_n must be 256, tile_m must not be 256); 0 = library's choice.
  *   tile_m    : 128, or 256 = one CTA computes 256-row tiles as two 128-row halves sharing
- *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice. */
+ *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice.
+ *   flags     : RD_CFG_NO_ZERO_TAIL = rd_gmm leaves the rows past sum(group_sizes) unwritten
+ *               (for callers that pass an upper bound as m and never read those rows). */
+#define RD_CFG_NO_ZERO_TAIL 1
 typedef struct rd_tile_cfg {
   int32_t tile_n;
   int32_t max_ctas;
   int32_t cta_group;
   int32_t tile_m;
+  int32_t flags;
 } rd_tile_cfg;
 
 int rd_version(void);
@@ -101,6 +105,29 @@ int rd_gmm_indexed(const void* x, const void* A, int num_weights, const int32_t*
  * yields a zero row. */
 int rd_gather_rows(const void* src, const int32_t* row_index, void* dst, int rows_out, int rows_in,
                    int row_bytes, void* stream);
+
+/* Expert-parallel dispatch without a host round trip (no counterpart in the reference, which
+ * has no multi-device code).  E experts are sharded E / world per rank; every rank runs, on
+ * its stream:
+ *   rd_ep_count     counts[e] = number of (token, slot) pairs of routing[tokens, top_k] that
+ *                   name expert e (counts is zeroed first);
+ *   (the caller all-gathers the counts of all ranks into counts_all[world][E]);
+ *   rd_ep_plan      dest_offset[E], segment_sizes[world * E/world] (the group sizes of the local
+ *                   rd_gmm_indexed, segment (s, j) = rows from source s for local expert j),
+ *                   totals[0] = rows this rank receives, fill[E] reset;
+ *   rd_ep_dispatch  copies every routed row of x straight into the receive buffer of the rank
+ *                   that owns its expert: peer_base[r] (a device array of `world` addresses) is
+ *                   rank r's buffer as seen from this GPU (peer memory over NVLink, or local
+ *                   memory for r == rank); dest_pos[tokens * top_k] records the row position.
+ * The caller synchronises the ranks after rd_ep_dispatch (all rows have landed) before the
+ * local rd_gmm_indexed reads the buffer, and must not dispatch into a buffer its owner is
+ * still reading.  Plain peer stores only: no multicast, no TMA from or to peer memory. */
+int rd_ep_count(const int32_t* routing, int entries, int num_experts, int32_t* counts, void* stream);
+int rd_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, int32_t* dest_offset,
+               int32_t* segment_sizes, int32_t* fill, int32_t* totals, void* stream);
+int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
+                   int num_experts, int world, const int32_t* dest_offset, int32_t* fill,
+                   const uint64_t* peer_base, int capacity_rows, int32_t* dest_pos, void* stream);
 
 /* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
  * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass
