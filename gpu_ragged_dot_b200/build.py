@@ -17,7 +17,6 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC_DIR = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "librd_b200.so")
 SOURCES = ["rd_api.cu"]
-HEADERS = ["rd_ptx.cuh", "rd_metadata.cuh", "rd_gemm.cuh"]
 
 NVCC_FLAGS = [
     "-gencode",
@@ -42,7 +41,7 @@ def _stale() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC_DIR, f) for f in SOURCES + HEADERS]
+    deps = [os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR) if f.endswith((".cu", ".cuh", ".h"))]
     deps.append(os.path.join(PKG_DIR, "..", "include", "ragged_dot_b200.h"))
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
