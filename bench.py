@@ -35,8 +35,8 @@ if ROOT not in sys.path:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel on this workload, from
 # the ncu captures summarised in profiles/ragged_gemm_mixtral_m8192_k4096_n14336_g8.md.
-DRAM_TRAFFIC_BYTES_PER_LAUNCH = {"fwd": 1.038238e9 + 229.12128e6, "dlhs": 1.501015e9 + 68.167168e6,
-                                 "drhs": 1.002836e9 + 887.103488e6}
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = {"fwd": 1.140598e9 + 229.923328e6, "dlhs": 1.588072e9 + 60.262912e6,
+                                 "drhs": 0.819250944e9 + 882.65984e6}
 
 METRIC = "ragged_dot fwd+bwd TFLOP/s (2*m*k*n useful flops per GEMM)"
 UNIT = "TFLOP/s"
@@ -302,8 +302,8 @@ def run_single(args):
     if hbm_bound:
         roofline = {
             "bound": "hbm",
-            "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
-                       "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
+            "kernel": {"fwd": "ragged_gemm(2)_kernel<gmm>", "dlhs": "ragged_gemm(2)_kernel<gmm, trans_rhs>",
+                       "drhs": "ragged_gemm2_kernel<tgmm>"}[dom],
             "achieved": per_kernel[dom]["algorithmic_GBps"], "peak": peaks["hbm_gbs"],
             "peak_source": f"{peaks['source']} (copy bandwidth)", "unit": "GB/s",
             "frac": per_kernel[dom]["frac_of_measured_hbm"], "traffic": None,
@@ -313,8 +313,8 @@ def run_single(args):
     else:
         roofline = {
             "bound": "tensor",
-            "kernel": {"fwd": "ragged_gemm_kernel<gmm>", "dlhs": "ragged_gemm_kernel<gmm, trans_rhs>",
-                       "drhs": "ragged_gemm_kernel<tgmm>"}[dom],
+            "kernel": {"fwd": "ragged_gemm2_kernel<gmm>", "dlhs": "ragged_gemm2_kernel<gmm, trans_rhs>",
+                       "drhs": "ragged_gemm2_kernel<tgmm>"}[dom],
             "achieved": per_kernel[dom]["tflops"],
             "peak": peaks["bf16_tflops"],
             "peak_source": f"{peaks['source']} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
