@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(PKG_DIR, "librd_b200.so")
 RD_OK = 0
 RD_DTYPE_F16 = 0
 RD_DTYPE_BF16 = 1
+RD_DTYPE_F32 = 2
 RD_CFG_NO_ZERO_TAIL = 1
 
 # Every symbol include/ragged_dot_b200.h declares, with its ctypes signature.

@@ -12,6 +12,7 @@
 #include "rd_gemm.cuh"
 #include "rd_dispatch.cuh"
 #include "rd_gemm2.cuh"
+#include "rd_gemm_f32.cuh"
 #include "rd_metadata.cuh"
 #include "rd_rows.cuh"
 
@@ -41,27 +42,29 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// rank-2 or rank-3 tiled map over a dense row-major 16-bit tensor, 128-byte swizzle,
+// rank-2 or rank-3 tiled map over a dense row-major 16-bit or 32-bit float tensor, 128-byte swizzle,
 // zero fill outside the bounds.  dims / box are innermost first.
 int encode_map(CUtensorMap* map, const void* base, int dtype, int rank, const uint64_t* dims,
-               const uint32_t* box) {
+               const uint32_t* box, bool atom32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return RD_ERR_DRIVER;
   cuuint64_t gdims[3];
   cuuint64_t gstrides[2];
   cuuint32_t gbox[3];
   cuuint32_t estr[3] = {1, 1, 1};
-  uint64_t stride = 2;
+  uint64_t stride = dtype == RD_DTYPE_F32 ? 4 : 2;
   for (int i = 0; i < rank; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];
     stride *= dims[i];
     if (i + 1 < rank) gstrides[i] = stride;
   }
-  const CUtensorMapDataType dt =
-      dtype == RD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == RD_DTYPE_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == RD_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                         : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides,
-                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fprintf(stderr,
@@ -180,6 +183,20 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
+template <int BN, bool kBKMajor, bool kTgmm>
+int launch_gemm_f32(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                    const GemmArgs& args, int ctas, cudaStream_t stream) {
+  constexpr int kStageBytes = rd::f32_stage_bytes<BN>();
+  constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
+  constexpr int kSmem = kStages * kStageBytes + rd::kOutStagingBytes + 1024;
+  auto kernel = rd::ragged_gemm_f32_kernel<BN, kBKMajor, kStages, kTgmm>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  kernel<<<ctas, rd::kGemmThreads, kSmem, stream>>>(ta, tb, tout, args);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
 template <bool kBKMajor, bool kTgmm>
 int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
                  const GemmArgs& args, int ctas, cudaStream_t stream) {
@@ -225,8 +242,8 @@ int rd_version(void) { return RD_VERSION; }
 const char* rd_status_string(int code) {
   switch (code) {
     case RD_OK: return "ok";
-    case RD_ERR_BAD_SHAPE: return "bad shape: sizes must be >= 0 and k, n multiples of 8";
-    case RD_ERR_BAD_DTYPE: return "unsupported dtype: only 16-bit float (f16, bf16) inputs";
+    case RD_ERR_BAD_SHAPE: return "bad shape: sizes must be >= 0 and rows of k, n elements multiples of 16 bytes";
+    case RD_ERR_BAD_DTYPE: return "unsupported dtype: f16, bf16 or f32";
     case RD_ERR_BAD_POINTER: return "null or misaligned pointer (16-byte alignment required)";
     case RD_ERR_WORKSPACE: return "workspace too small (see rd_workspace_bytes)";
     case RD_ERR_BAD_CONFIG: return "unsupported tile configuration";
@@ -280,13 +297,17 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
                     size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
                     const rd_tile_cfg* cfg, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (m < 0 || k < 0 || n < 0 || g < 0 || num_weights < 0 || (k & 7) || (n & 7))
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16 && dtype != RD_DTYPE_F32) return RD_ERR_BAD_DTYPE;
+  const bool f32 = dtype == RD_DTYPE_F32;
+  const int esize = f32 ? 4 : 2;            // bytes per element
+  const int amask = f32 ? 3 : 7;            // rows must be multiples of 16 bytes
+  const int row_elems = 128 / esize;        // elements per 128-byte swizzle row
+  if (m < 0 || k < 0 || n < 0 || g < 0 || num_weights < 0 || (k & amask) || (n & amask))
     return RD_ERR_BAD_SHAPE;
-  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
   if (m == 0 || n == 0) return RD_OK;
   if (!aligned16(y)) return RD_ERR_BAD_POINTER;
   if (g == 0 || k == 0 || num_weights == 0) {  // nothing contributes: every row is a zero row
-    cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * 2, stream);
+    cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * esize, stream);
     return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
   }
   if (!aligned16(x) || !aligned16(A) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
@@ -303,6 +324,11 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   int tile_m = cfg ? cfg->tile_m : 0;
   if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
   if (tile_m == 256 && (bn != 256 || cta_group != 1)) return RD_ERR_BAD_CONFIG;
+  if (f32) {  // the float32 (TF32) kernels exist as single-CTA 128-row tiles only
+    if (cta_group == 2 || tile_m == 256) return RD_ERR_BAD_CONFIG;
+    cta_group = 1;
+    tile_m = 128;
+  }
   if (tile_m == 0) tile_m = (cta_group == 1 && choose_two_half(false, m, k, g, bn)) ? 256 : 128;
   const bool two_half = tile_m == 256;
 
@@ -317,26 +343,26 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {rd::kTileK, rd::kTileM};
+    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), rd::kTileM};
     rc = encode_map(&ta, x, dtype, 2, dims, box);
     if (rc != RD_OK) return rc;
   }
-  if (trans_rhs) {  // A[g, n, k]: rows of k, K-major operand, one [BN][64] box per stage
+  if (trans_rhs) {  // A[g, n, k]: rows of k, K-major operand, one [BN][128 B] box per stage
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
                               static_cast<uint64_t>(num_weights)};
-    const uint32_t box[3] = {rd::kTileK, static_cast<uint32_t>(bn / cta_group), 1};
+    const uint32_t box[3] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(bn / cta_group), 1};
     rc = encode_map(&tb, A, dtype, 3, dims, box);
-  } else {  // A[g, k, n]: rows of n, MN-major operand, [64 k][64 n] boxes
+  } else {  // A[g, k, n]: rows of n, MN-major operand, [stage-depth k][128 B of n] boxes
     const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
                               static_cast<uint64_t>(num_weights)};
-    const uint32_t box[3] = {64, rd::kTileK, 1};
-    rc = encode_map(&tb, A, dtype, 3, dims, box);
+    const uint32_t box[3] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems), 1};
+    rc = encode_map(&tb, A, dtype, 3, dims, box, /*atom32=*/f32);  // MN-major fp32: 32-byte atoms
   }
   if (rc != RD_OK) return rc;
   CUtensorMap tout;
-  {  // y[m, n] written as [32 rows][64 cols] boxes
+  {  // y[m, n] written as [32 rows][128 B] boxes
     const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {64, 32};
+    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), 32};
     rc = encode_map(&tout, y, dtype, 2, dims, box);
     if (rc != RD_OK) return rc;
   }
@@ -356,6 +382,16 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.out = y;
 
   const int ctas = pick_ctas(cfg);
+  if (f32) {
+    if (trans_rhs) {
+      if (bn == 256) return launch_gemm_f32<256, true, false>(ta, tb, tout, args, ctas, stream);
+      if (bn == 128) return launch_gemm_f32<128, true, false>(ta, tb, tout, args, ctas, stream);
+      return launch_gemm_f32<64, true, false>(ta, tb, tout, args, ctas, stream);
+    }
+    if (bn == 256) return launch_gemm_f32<256, false, false>(ta, tb, tout, args, ctas, stream);
+    if (bn == 128) return launch_gemm_f32<128, false, false>(ta, tb, tout, args, ctas, stream);
+    return launch_gemm_f32<64, false, false>(ta, tb, tout, args, ctas, stream);
+  }
   if (two_half) {
     return trans_rhs ? launch_gemm2<true, false>(ta, tb, tout, args, ctas, stream)
                      : launch_gemm2<false, false>(ta, tb, tout, args, ctas, stream);
@@ -452,12 +488,16 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
             void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
             const rd_tile_cfg* cfg, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (m < 0 || k < 0 || n < 0 || g < 0 || (k & 7) || (n & 7)) return RD_ERR_BAD_SHAPE;
-  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16 && dtype != RD_DTYPE_F32) return RD_ERR_BAD_DTYPE;
+  const bool f32 = dtype == RD_DTYPE_F32;
+  const int esize = f32 ? 4 : 2;
+  const int amask = f32 ? 3 : 7;
+  const int row_elems = 128 / esize;
+  if (m < 0 || k < 0 || n < 0 || g < 0 || (k & amask) || (n & amask)) return RD_ERR_BAD_SHAPE;
   if (g == 0 || k == 0 || n == 0) return RD_OK;
   if (!aligned16(out)) return RD_ERR_BAD_POINTER;
   if (m == 0) {  // every group is empty
-    cudaMemsetAsync(out, 0, static_cast<size_t>(g) * k * n * 2, stream);
+    cudaMemsetAsync(out, 0, static_cast<size_t>(g) * k * n * esize, stream);
     return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
   }
   if (!aligned16(x) || !aligned16(dout) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
@@ -475,6 +515,11 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
   if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
   if (tile_m == 256 && (bn != 256 || cta_group == 2)) return RD_ERR_BAD_CONFIG;
+  if (f32) {  // the float32 (TF32) kernels exist as single-CTA 128-row tiles only
+    if (cta_group == 2 || tile_m == 256) return RD_ERR_BAD_CONFIG;
+    cta_group = 1;
+    tile_m = 128;
+  }
   // Preference order when nothing is forced: 256-row tiles on one CTA, then a CTA pair, then
   // plain 128-row tiles.
   if (tile_m == 0 && cta_group != 2) tile_m = choose_two_half(true, m, k, g, bn) ? 256 : 128;
@@ -499,22 +544,22 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   CUtensorMap ta, tb;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {64, rd::kTileK};
-    rc = encode_map(&ta, x, dtype, 2, dims, box);
+    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
+    rc = encode_map(&ta, x, dtype, 2, dims, box, /*atom32=*/f32);
     if (rc != RD_OK) return rc;
   }
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {64, rd::kTileK};
-    rc = encode_map(&tb, dout, dtype, 2, dims, box);
+    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
+    rc = encode_map(&tb, dout, dtype, 2, dims, box, /*atom32=*/f32);
     if (rc != RD_OK) return rc;
   }
 
   CUtensorMap tout;
-  {  // out[g, k, n] written as [32 rows][64 cols] boxes of one group
+  {  // out[g, k, n] written as [32 rows][128 B] boxes of one group
     const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
                               static_cast<uint64_t>(g)};
-    const uint32_t box[3] = {64, 32, 1};
+    const uint32_t box[3] = {static_cast<uint32_t>(row_elems), 32, 1};
     rc = encode_map(&tout, out, dtype, 3, dims, box);
     if (rc != RD_OK) return rc;
   }
@@ -534,6 +579,11 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.out = out;
 
   const int ctas = pick_ctas(cfg);
+  if (f32) {
+    if (bn == 256) return launch_gemm_f32<256, false, true>(ta, tb, tout, args, ctas, stream);
+    if (bn == 128) return launch_gemm_f32<128, false, true>(ta, tb, tout, args, ctas, stream);
+    return launch_gemm_f32<64, false, true>(ta, tb, tout, args, ctas, stream);
+  }
   if (two_half) return launch_gemm2<false, true>(ta, tb, tout, args, ctas, stream);
   if (cta_group == 2) return launch_gemm<256, false, true, 2>(ta, tb, tout, args, ctas, stream);
   if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);

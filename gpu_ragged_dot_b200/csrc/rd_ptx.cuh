@@ -331,14 +331,17 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //   K-major operand  : rows of 128 B (64 bf16 along K); 8-row groups `sbo` bytes apart.
 //   MN-major operand : rows of 128 B (64 bf16 along M/N), one row per K index; groups of
 //                      8 K-rows `sbo` bytes apart, blocks of 64 M/N elements `lbo` bytes apart.
+//   layout_type 2 = 128-byte swizzle in 16-byte units (everything 16-bit, and K-major fp32);
+//   layout_type 1 = 128-byte swizzle in 32-byte units, the only layout the tensor core accepts
+//                   for MN-major 32-bit (TF32) operands: K-groups are 4 rows, not 8.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // SWIZZLE_128B
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

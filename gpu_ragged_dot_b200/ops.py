@@ -10,6 +10,8 @@ Differences from the reference, all deliberate:
     compatibility but are hints only -- tiles come from the committed tile table
     (``tile_table.py``), which replaces the tune-jax search of tuning.py:49-58.
   * ``interpret=True`` raises: there is no CPU path.
+  * float32 inputs are multiplied as TF32 on the tensor cores with fp32 accumulation and give
+    float32 results (the precision the reference's Triton ``tl.dot`` uses for float32).
   * rows past ``sum(group_sizes)`` are always zero, also when every group is empty (the
     reference leaves them unwritten in that case, gpu_ragged_dot.py:155-157).
   * the VJP of ``tgmm`` is the mathematically correct one; the reference's
@@ -66,7 +68,8 @@ class GMMGroupLookupMetadata(NamedTuple):
     total_row_its: torch.Tensor
 
 
-_DTYPE_CODE = {torch.float16: _lib.RD_DTYPE_F16, torch.bfloat16: _lib.RD_DTYPE_BF16}
+_DTYPE_CODE = {torch.float16: _lib.RD_DTYPE_F16, torch.bfloat16: _lib.RD_DTYPE_BF16,
+               torch.float32: _lib.RD_DTYPE_F32}
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -164,16 +167,17 @@ def gmm_forward(
         group_to_weight = _as_i32(group_to_weight)
         assert group_to_weight.shape == gs.shape
     if x.dtype not in _DTYPE_CODE or A.dtype != x.dtype:
-        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {A.dtype}")
+        raise NotImplementedError(f"inputs must both be float16, bfloat16 or float32, got {x.dtype} / {A.dtype}")
     m, k = x.shape
     g = gs.shape[0]
     n = A.shape[-1] if not trans_rhs else A.shape[-2]
     k_rhs = A.shape[-2] if not trans_rhs else A.shape[-1]
     assert k_rhs == k, f"contraction mismatch: x has k={k}, A has {k_rhs}"
 
-    # TMA needs 16-byte row strides: pad k and n up to multiples of 8 with zeros (exact).
-    xp = _dense16(_pad_last(x))
-    Ap = _dense16(_pad_last2(A))
+    # TMA needs 16-byte row strides: pad k and n up to multiples of 16 bytes with zeros (exact).
+    mult = 16 // x.element_size()
+    xp = _dense16(_pad_last(x, mult))
+    Ap = _dense16(_pad_last2(A, mult))
     kp = xp.shape[1]
     np_ = Ap.shape[-1] if not trans_rhs else Ap.shape[-2]
     padded_n = np_ != n
@@ -288,11 +292,12 @@ def tgmm_forward(
     assert y.dim() == 2 and x.dim() == 2 and x.shape[0] == y.shape[0]
     gs = _as_i32(group_sizes)
     if x.dtype not in _DTYPE_CODE or y.dtype != x.dtype:
-        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {y.dtype}")
+        raise NotImplementedError(f"inputs must both be float16, bfloat16 or float32, got {x.dtype} / {y.dtype}")
     (m, k), n = x.shape, y.shape[-1]
     g = gs.numel()
-    xp = _dense16(_pad_last(x))
-    yp = _dense16(_pad_last(y))
+    mult = 16 // x.element_size()
+    xp = _dense16(_pad_last(x, mult))
+    yp = _dense16(_pad_last(y, mult))
     kp, np_ = xp.shape[1], yp.shape[1]
     padded = (kp != k) or (np_ != n)
     if out is not None and not padded:

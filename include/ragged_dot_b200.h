@@ -12,12 +12,13 @@
  * with rd_device_status().
  *
  * Shapes follow the reference's signature (gpu_ragged_dot.py:362-376, README.md:52-67):
- *   x            [m, k]      row-major, 16-bit float
+ *   x            [m, k]      row-major, f16 / bf16 / f32 (all tensors of a call share the type)
  *   A            [g, k, n]   (trans_rhs == 0)  or  [g, n, k]  (trans_rhs != 0)
  *   group_sizes  [g]         int32, sum <= m; rows past the sum are written as zeros
  *   y            [m, n]
- * k and n must be multiples of 8 and every pointer 16-byte aligned (TMA strides); the Python
- * host layer pads other shapes before calling.
+ * Rows of k and of n elements must be multiples of 16 bytes (k, n multiples of 8 for 16-bit
+ * types, of 4 for f32) and every pointer 16-byte aligned (TMA strides); the Python host layer
+ * pads other shapes before calling.
  */
 #ifndef RAGGED_DOT_B200_H_
 #define RAGGED_DOT_B200_H_
@@ -33,8 +34,8 @@ extern "C" {
 
 enum rd_error {
   RD_OK = 0,
-  RD_ERR_BAD_SHAPE = 1,       /* negative size, or k / n not a multiple of 8 */
-  RD_ERR_BAD_DTYPE = 2,       /* dtype is not RD_DTYPE_F16 / RD_DTYPE_BF16 */
+  RD_ERR_BAD_SHAPE = 1,       /* negative size, or k / n rows not a multiple of 16 bytes */
+  RD_ERR_BAD_DTYPE = 2,       /* dtype is not one of rd_dtype */
   RD_ERR_BAD_POINTER = 3,     /* null or not 16-byte aligned */
   RD_ERR_WORKSPACE = 4,       /* workspace smaller than rd_workspace_bytes() */
   RD_ERR_BAD_CONFIG = 5,      /* rd_tile_cfg names a tile the kernels do not have */
@@ -46,7 +47,9 @@ enum rd_error {
   RD_ERR_SCRATCH_SETUP = 11   /* rd_gmm_static_scratch: scratch address could not be resolved */
 };
 
-enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1 };
+/* F32: float32 in and out, multiplied on the tensor cores as TF32 with fp32 accumulation (what
+ * the reference's Triton kernel and jax.lax.ragged_dot do for float32 on NVIDIA GPUs). */
+enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1, RD_DTYPE_F32 = 2 };
 
 /* Tile choice for one call; replaces the reference's block_m/block_k/block_n + tune-jax
  * search (tuning.py:49-58).  Pass NULL to let the library choose.

@@ -63,6 +63,16 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.detach().to("cpu").to(torch.float32)
 
 
+def to_tf32(t: torch.Tensor, mode: str = "truncate") -> torch.Tensor:
+    """float32 values reduced to TF32 (10 explicit mantissa bits), the operand precision of the
+    tensor cores for float32 inputs.  "truncate" drops the low 13 bits; "nearest" rounds to
+    nearest, ties away from zero (cvt.rna.tf32.f32)."""
+    bits = _f32(t).contiguous().view(torch.int32)
+    if mode == "nearest":
+        bits = bits + 0x1000
+    return (bits & ~0x1FFF).view(torch.float32)
+
+
 def _group_ranges(group_sizes, m: int):
     gs = np.asarray(torch.as_tensor(group_sizes).cpu().numpy(), dtype=np.int64)
     start = 0

@@ -489,3 +489,66 @@ def test_expert_parallel_p2p_single_rank_matches_nccl_path():
     order = torch.sort(routing.reshape(-1).cpu().long(), stable=True).indices  # sorted row -> entry
     pos = dest_pos.reshape(-1).cpu().long()
     _assert_close(yb.cpu()[pos[order]], ya.cpu(), "p2p vs nccl path")
+
+
+# ------------------------------------------------------------------ float32 inputs (TF32 on the tensor cores)
+def _f32_err(got, x, A, gs, fn, axis, mask):
+    """Relative-L2 error against the fp32 oracle fed TF32-reduced operands, for both ways the
+    hardware might reduce them; returns the smaller (and which)."""
+    errs = {}
+    for mode in ("truncate", "nearest"):
+        want = fn(oracle.to_tf32(x, mode), oracle.to_tf32(A, mode), gs)
+        errs[mode] = float(oracle.rel_l2_err(got, want, axis=axis, mask=mask).max())
+    best = min(errs, key=errs.get)
+    return errs[best], best, errs
+
+
+@pytest.mark.parametrize("case", GRID[:10], ids=lambda c: "-".join(f"{k}{v}" for k, v in c.items()))
+def test_reference_grid_float32(case):
+    """float32 cases of the reference grid (tests.py:93): rel-L2 5e-4 per row for gmm and its
+    transposed form, 1e-4 per group for tgmm, against an oracle with TF32 operands; and within
+    2e-3 of the exact fp32 product."""
+    m, k, n, g = case["m"], case["k"], case["n"], case["g"]
+    x, A, dout = _inputs(case["seed"], m, k, n, g, dtype=torch.float32, random_inputs=case["random_inputs"])
+    target_m = max(min(round(m * case["fill_in"]), m), 0)
+    gs = torch.from_numpy(oracle.reference_group_sizes(case["seed"] + 17, g, target_m))
+    rows = torch.arange(m) < target_m
+    xd, Ad, dd, gd = _to_dev(x, A, dout, gs)
+
+    y = ops.gmm_forward(xd, Ad, gd).cpu()
+    assert y.dtype == torch.float32
+    e, mode, all_e = _f32_err(y, x, A, gs, lambda a, b, c: oracle.ragged_dot(a, b, c), -1, rows)
+    assert e < 5e-4, f"gmm f32 rel-L2 {all_e}"
+    exact = float(oracle.rel_l2_err(y, oracle.ragged_dot(x, A, gs), axis=-1, mask=rows).max())
+    assert exact < 2e-3, f"gmm f32 vs exact fp32: {exact:.2e}"
+    if target_m < m:
+        assert float(y[target_m:].abs().max()) == 0.0
+
+    At = A.transpose(1, 2).contiguous()
+    yt = ops.gmm_forward(xd, At.to(DEV), gd, trans_rhs=True).cpu()
+    e, _, all_e = _f32_err(yt, x, At, gs, lambda a, b, c: oracle.ragged_dot(a, b, c, trans_rhs=True), -1, rows)
+    assert e < 5e-4, f"gmm trans f32 rel-L2 {all_e}"
+
+    out = ops.tgmm_forward(xd, dd, gd).cpu()
+    e, _, all_e = _f32_err(out, x, dout, gs, lambda a, b, c: oracle.trans_ragged_dot(a, b, c), (-1, -2), gs != 0)
+    assert e < 1e-4, f"tgmm f32 rel-L2 {all_e}"
+    for gi in (gs == 0).nonzero().flatten().tolist():
+        assert float(out[gi].abs().max()) == 0.0
+
+
+def test_float32_vjp_and_tile_widths():
+    m, k, n, g = 600, 200, 328, 5
+    x, A, dout = _inputs(51, m, k, n, g, dtype=torch.float32)
+    gs = torch.tensor([130, 0, 257, 1, 200], dtype=torch.int32)
+    rows = torch.arange(m) < int(gs.sum())
+    for tile_n in (64, 128, 256):
+        cfg = _lib.TileCfg(tile_n, 0, 0, 0, 0)
+        y = ops.gmm_forward(x.to(DEV), A.to(DEV), gs.to(DEV), cfg=cfg).cpu()
+        e, _, all_e = _f32_err(y, x, A, gs, lambda a, b, c: oracle.ragged_dot(a, b, c), -1, rows)
+        assert e < 5e-4, f"tile_n={tile_n}: {all_e}"
+    xd, Ad = x.to(DEV).requires_grad_(True), A.to(DEV).requires_grad_(True)
+    y = rd.ragged_dot(xd, Ad, gs.to(DEV))
+    y.backward(dout.to(DEV))
+    dx_ref, dA_ref = oracle.ragged_dot_vjp(x, A, gs, dout)
+    assert float(oracle.rel_l2_err(xd.grad.cpu(), dx_ref, axis=-1, mask=rows).max()) < 2e-3
+    assert float(oracle.rel_l2_err(Ad.grad.cpu(), dA_ref, axis=(-1, -2), mask=gs != 0).max()) < 2e-3
