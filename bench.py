@@ -365,6 +365,97 @@ def run_single(args):
     print(json.dumps(line), flush=True)
 
 
+def run_permute(args):
+    """`--workload permute`: the MoE-layer use of the path on the Mixtral shape (4096 tokens, top-2
+    routing over 8 experts -> 8192 sorted rows): y[out_rows[r]] = x[in_rows[r]] @ A[expert of r].
+    Times the permutation-fused kernels (rd_gmm_permuted / rd_tgmm_permuted) against
+    rd_gather_rows + rd_gmm / rd_tgmm + rd_gather_rows, variants interleaved in one process."""
+    import random
+    import statistics
+
+    from gpu_ragged_dot_b200 import _lib, ops, workloads
+
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = workloads.MIXTRAL
+    top_k = 2
+    tokens = shape.m // top_k
+    routing = workloads.topk_routing(tokens, shape.g, top_k, seed=0)  # [tokens, top_k]
+    flat = routing.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    gs = torch.from_numpy(np.bincount(flat, minlength=shape.g).astype(np.int32)).to(dev)
+    in_rows = torch.from_numpy((order // top_k).astype(np.int32)).to(dev)
+    out_rows = torch.from_numpy(order.astype(np.int32)).to(dev)
+    inv_rows = torch.empty_like(out_rows)
+    inv_rows[out_rows.long()] = torch.arange(shape.m, dtype=torch.int32, device=dev)
+    x = workloads.normal_tensor((tokens, shape.k), 1.0, 1, dev)
+    A = workloads.normal_tensor((shape.g, shape.k, shape.n), shape.k ** -0.5, 2, dev)
+    dy = workloads.normal_tensor((shape.m, shape.n), 1.0, 3, dev)
+    ws = ops._workspace(shape.m, shape.g, dev)
+    xs = torch.empty((shape.m, shape.k), dtype=torch.bfloat16, device=dev)
+    ys = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev)
+    dys = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev)
+    dA = torch.empty_like(A)
+
+    def fwd_fused():
+        ops.gmm_permuted_forward(x, A, gs, in_rows=in_rows, out_rows=out_rows, out=y, y_rows=shape.m, workspace=ws)
+
+    def fwd_fused_gather_only():
+        ops.gmm_permuted_forward(x, A, gs, in_rows=in_rows, out=ys, workspace=ws)
+
+    def fwd_two_pass():
+        ops.gather_rows(x, in_rows, out=xs)
+        ops.gmm_forward(xs, A, gs, out=ys, workspace=ws)
+        ops.gather_rows(ys, inv_rows, out=y)
+
+    def fwd_two_pass_gather_only():
+        ops.gather_rows(x, in_rows, out=xs)
+        ops.gmm_forward(xs, A, gs, out=ys, workspace=ws)
+
+    def drhs_fused():
+        ops.tgmm_permuted_forward(x, dy, gs, x_rows_index=in_rows, y_rows_index=out_rows, out=dA, workspace=ws)
+
+    def drhs_two_pass():
+        ops.gather_rows(x, in_rows, out=xs)
+        ops.gather_rows(dy, out_rows, out=dys)
+        ops.tgmm_forward(xs, dys, gs, out=dA, workspace=ws)
+
+    variants = {"fwd_fused": fwd_fused, "fwd_two_pass": fwd_two_pass,
+                "fwd_fused_gather_only": fwd_fused_gather_only,
+                "fwd_two_pass_gather_only": fwd_two_pass_gather_only,
+                "drhs_fused": drhs_fused, "drhs_two_pass": drhs_two_pass}
+    for fn in variants.values():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    times = {name: [] for name in variants}
+    rng = random.Random(0)
+    for _ in range(5):
+        names = list(variants)
+        rng.shuffle(names)
+        for name in names:
+            times[name].append(_time_ms(variants[name], args.steps))
+    clocks = sampler.stop()
+    assert ops.device_status(ws) == 0, "device reported an expired wait"
+    flops = 2.0 * shape.m * shape.k * shape.n
+    res = {name: {"ms": round(statistics.median(v), 4),
+                  "tflops": round(flops / statistics.median(v) / 1e9, 1)} for name, v in times.items()}
+    ms = res["fwd_fused"]["ms"]
+    print(json.dumps({
+        "metric": "ragged_dot_permuted_fwd_tflops", "value": res["fwd_fused"]["tflops"], "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "permute: mixtral shape, 4096 tokens x top-2 of 8 experts, gather + scatter "
+                               "fused into the GEMM", "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
+                   "l2": "operands larger than L2"},
+        "variants": res, "clocks": clocks, "gpu_launches": 2 * args.steps,
+    }), flush=True)
+
+
 def _time_ms(fn, reps):
     for _ in range(3):
         fn()
@@ -595,7 +686,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
-    ap.add_argument("--workload", default="mixtral", choices=["mixtral", "decode", "deepseek"],
+    ap.add_argument("--workload", default="mixtral", choices=["mixtral", "decode", "deepseek", "permute"],
                     help="N=1 only; the headline line is the default (mixtral); the others are for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -606,6 +697,8 @@ def main():
     _, world, _ = dist_env()
     if world > 1 or args.gpus > 1:
         run_expert_parallel(args)
+    elif args.workload == "permute":
+        run_permute(args)
     else:
         run_single(args)
 

@@ -13,9 +13,10 @@ from .ops import (  # noqa: F401
     gmm_forward,
     make_group_metadata,
     ragged_dot,
+    ragged_dot_permuted,
     tgmm,
     tgmm_forward,
     trans_ragged_dot,
 )
 
-__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot"]
+__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted"]

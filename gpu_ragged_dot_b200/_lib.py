@@ -14,6 +14,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "librd_b200.so")
 
 RD_OK = 0
+RD_ERR_BAD_SHAPE, RD_ERR_BAD_DTYPE, RD_ERR_BAD_POINTER, RD_ERR_WORKSPACE, RD_ERR_BAD_CONFIG = 1, 2, 3, 4, 5
+RD_ERR_TENSOR_MAP, RD_ERR_LAUNCH, RD_ERR_DRIVER, RD_ERR_DEVICE_WAIT, RD_ERR_TOO_LARGE = 6, 7, 8, 9, 10
+RD_ERR_SCRATCH_SETUP = 11
 RD_DTYPE_F16 = 0
 RD_DTYPE_BF16 = 1
 RD_DTYPE_F32 = 2
@@ -56,6 +59,20 @@ SIGNATURES = {
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
         + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_gmm_permuted": (
+        _c_int,
+        [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+         _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_tgmm_permuted": (
+        _c_int,
+        [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+         _c_size_t]
+        + [_c_int] * 5
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
     "rd_gather_rows": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]),

@@ -13,6 +13,7 @@
 #include "rd_dispatch.cuh"
 #include "rd_gemm2.cuh"
 #include "rd_gemm_f32.cuh"
+#include "rd_gemm_perm.cuh"
 #include "rd_metadata.cuh"
 #include "rd_rows.cuh"
 
@@ -195,6 +196,29 @@ int launch_gemm_f32(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensor
     return RD_ERR_LAUNCH;
   kernel<<<ctas, rd::kGemmThreads, kSmem, stream>>>(ta, tb, tout, args);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+template <int BN, bool kBKMajor, bool kTgmm>
+int launch_gemm_perm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                     const GemmArgs& args, const rd::PermArgs& perm, int ctas, cudaStream_t stream) {
+  constexpr int kStageBytes = rd::stage_bytes<BN, 1>();
+  constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
+  constexpr int kSmem = kStages * kStageBytes + rd::kOutStagingBytes + 1024;
+  auto kernel = rd::ragged_gemm_perm_kernel<BN, kBKMajor, kStages, kTgmm>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  kernel<<<ctas, rd::kPermThreads, kSmem, stream>>>(ta, tb, tout, args, perm);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+// Tile-load map over a [rows, cols] 16-bit tensor with boxes of [box_rows][64 columns].  The
+// permuted kernels use it for an operand without a row index; with one they read the tensor
+// through its base pointer and the map is only prefetched.
+int encode_rows_map(CUtensorMap* map, const void* base, int dtype, int cols, int rows, int box_rows) {
+  const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+  const uint32_t box[2] = {64, static_cast<uint32_t>(box_rows)};
+  return encode_map(map, base, dtype, 2, dims, box);
 }
 
 template <bool kBKMajor, bool kTgmm>
@@ -589,6 +613,166 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);
   if (bn == 128) return launch_gemm<128, false, true, 1>(ta, tb, tout, args, ctas, stream);
   return launch_gemm<64, false, true, 1>(ta, tb, tout, args, ctas, stream);
+}
+
+int rd_gmm_permuted(const void* x, int x_rows, const int32_t* in_rows, const void* A, int num_weights,
+                    const int32_t* group_sizes, const int32_t* group_to_weight, void* y, int y_rows,
+                    const int32_t* out_rows, void* workspace, size_t workspace_bytes, int m, int k,
+                    int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (m < 0 || k < 0 || n < 0 || g < 0 || num_weights < 0 || x_rows < 0 || y_rows < 0 || (k & 7) ||
+      (n & 7))
+    return RD_ERR_BAD_SHAPE;
+  if (in_rows == nullptr && x_rows < m) return RD_ERR_BAD_SHAPE;
+  if (out_rows == nullptr && y_rows != m) return RD_ERR_BAD_SHAPE;
+  if (m == 0 || n == 0 || y_rows == 0) return RD_OK;
+  if (!aligned16(y)) return RD_ERR_BAD_POINTER;
+  if (g == 0 || k == 0 || num_weights == 0 || x_rows == 0) {
+    // Nothing contributes.  Without out_rows every row of y is a zero row; with out_rows the
+    // rows that would have been written are not known without reading the indices, and the
+    // call leaves y alone only if there is no group at all.
+    if (out_rows == nullptr || g == 0) {
+      if (out_rows == nullptr) cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * 2, stream);
+      return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+    }
+    return RD_ERR_BAD_SHAPE;
+  }
+  if (!aligned16(x) || !aligned16(A) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  if (group_to_weight == nullptr && num_weights != g) return RD_ERR_BAD_SHAPE;
+  Workspace w;
+  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  if (rc != RD_OK) return rc;
+  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(0, n, 0);
+  if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+  if (cfg && (cfg->cta_group == 2 || cfg->tile_m == 256)) return RD_ERR_BAD_CONFIG;
+
+  launch_internal_metadata(group_sizes, group_to_weight, g, m, rd::kTileM, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
+  CUtensorMap ta, tb, tout;
+  rc = encode_rows_map(&ta, x, dtype, k, x_rows, rd::kTileM);
+  if (rc != RD_OK) return rc;
+  if (trans_rhs) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_weights)};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(bn), 1};
+    rc = encode_map(&tb, A, dtype, 3, dims, box);
+  } else {
+    const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                              static_cast<uint64_t>(num_weights)};
+    const uint32_t box[3] = {64, 64, 1};
+    rc = encode_map(&tb, A, dtype, 3, dims, box);
+  }
+  if (rc != RD_OK) return rc;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(y_rows)};
+    const uint32_t box[2] = {64, 32};
+    rc = encode_map(&tout, y, dtype, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+
+  GemmArgs args;
+  args.m = m; args.k = k; args.n = n; args.g = g;
+  args.n_tiles = (n + bn - 1) / bn;
+  args.k_tiles = 0;
+  args.max_m_tiles = w.layout.max_tiles;
+  args.ab_format = dtype;
+  args.zero_tail = (cfg && (cfg->flags & RD_CFG_NO_ZERO_TAIL)) ? 0 : 1;
+  args.group_sizes = group_sizes;
+  args.group_offsets = w.group_offsets();
+  args.tile_rec = w.tile_rec();
+  args.totals = w.totals();
+  args.status = w.status();
+  args.out = y;
+  rd::PermArgs perm;
+  perm.a_rows = in_rows;
+  perm.a_base = x;
+  perm.a_rows_in = x_rows;
+  perm.b_rows = nullptr;
+  perm.b_base = nullptr;
+  perm.b_rows_in = 0;
+  perm.out_rows = out_rows;
+  perm.out_rows_n = y_rows;
+
+  const int ctas = pick_ctas(cfg);
+  if (trans_rhs) {
+    if (bn == 256) return launch_gemm_perm<256, true, false>(ta, tb, tout, args, perm, ctas, stream);
+    if (bn == 128) return launch_gemm_perm<128, true, false>(ta, tb, tout, args, perm, ctas, stream);
+    return launch_gemm_perm<64, true, false>(ta, tb, tout, args, perm, ctas, stream);
+  }
+  if (bn == 256) return launch_gemm_perm<256, false, false>(ta, tb, tout, args, perm, ctas, stream);
+  if (bn == 128) return launch_gemm_perm<128, false, false>(ta, tb, tout, args, perm, ctas, stream);
+  return launch_gemm_perm<64, false, false>(ta, tb, tout, args, perm, ctas, stream);
+}
+
+int rd_tgmm_permuted(const void* x, int x_rows, const int32_t* x_row_index, const void* dout,
+                     int dout_rows, const int32_t* dout_row_index, const int32_t* group_sizes,
+                     void* out, void* workspace, size_t workspace_bytes, int m, int k, int n, int g,
+                     int dtype, const rd_tile_cfg* cfg, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (m < 0 || k < 0 || n < 0 || g < 0 || x_rows < 0 || dout_rows < 0 || (k & 7) || (n & 7))
+    return RD_ERR_BAD_SHAPE;
+  if ((x_row_index == nullptr && x_rows < m) || (dout_row_index == nullptr && dout_rows < m))
+    return RD_ERR_BAD_SHAPE;
+  if (g == 0 || k == 0 || n == 0) return RD_OK;
+  if (!aligned16(out)) return RD_ERR_BAD_POINTER;
+  if (m == 0 || x_rows == 0 || dout_rows == 0) {
+    cudaMemsetAsync(out, 0, static_cast<size_t>(g) * k * n * 2, stream);
+    return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+  }
+  if (!aligned16(x) || !aligned16(dout) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  Workspace w;
+  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  if (rc != RD_OK) return rc;
+  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(0, n, 0);
+  if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+  if (cfg && (cfg->cta_group == 2 || cfg->tile_m == 256)) return RD_ERR_BAD_CONFIG;
+
+  launch_internal_metadata(group_sizes, nullptr, g, m, rd::kTileM, w, stream);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
+  CUtensorMap ta, tb, tout;
+  rc = encode_rows_map(&ta, x, dtype, k, x_rows, 64);
+  if (rc != RD_OK) return rc;
+  rc = encode_rows_map(&tb, dout, dtype, n, dout_rows, 64);
+  if (rc != RD_OK) return rc;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                              static_cast<uint64_t>(g)};
+    const uint32_t box[3] = {64, 32, 1};
+    rc = encode_map(&tout, out, dtype, 3, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+
+  GemmArgs args;
+  args.m = m; args.k = k; args.n = n; args.g = g;
+  args.n_tiles = (n + bn - 1) / bn;
+  args.k_tiles = (k + rd::kTileM - 1) / rd::kTileM;
+  args.max_m_tiles = w.layout.max_tiles;
+  args.ab_format = dtype;
+  args.zero_tail = 0;
+  args.group_sizes = group_sizes;
+  args.group_offsets = w.group_offsets();
+  args.tile_rec = w.tile_rec();
+  args.totals = w.totals();
+  args.status = w.status();
+  args.out = out;
+  rd::PermArgs perm;
+  perm.a_rows = x_row_index;
+  perm.a_base = x;
+  perm.a_rows_in = x_rows;
+  perm.b_rows = dout_row_index;
+  perm.b_base = dout;
+  perm.b_rows_in = dout_rows;
+  perm.out_rows = nullptr;
+  perm.out_rows_n = 0;
+
+  const int ctas = pick_ctas(cfg);
+  if (bn == 256) return launch_gemm_perm<256, false, true>(ta, tb, tout, args, perm, ctas, stream);
+  if (bn == 128) return launch_gemm_perm<128, false, true>(ta, tb, tout, args, perm, ctas, stream);
+  return launch_gemm_perm<64, false, true>(ta, tb, tout, args, perm, ctas, stream);
 }
 
 int rd_device_status(const void* workspace, void* stream) {

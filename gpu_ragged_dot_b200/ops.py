@@ -322,6 +322,243 @@ def tgmm_forward(
     return res
 
 
+def gmm_permuted_forward(
+    x: torch.Tensor,
+    A: torch.Tensor,
+    group_sizes: torch.Tensor,
+    in_rows: Optional[torch.Tensor] = None,
+    out_rows: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    y_rows: Optional[int] = None,
+    m: Optional[int] = None,
+    trans_rhs: bool = False,
+    cfg: Optional[_lib.TileCfg] = None,
+    workspace: Optional[torch.Tensor] = None,
+    group_to_weight: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One call of ``rd_gmm_permuted``: for sorted row r < sum(group_sizes),
+    ``y[out_rows[r]] = x[in_rows[r]] @ A[group of r]``, with the gather and the scatter done
+    inside the GEMM kernel (TMA row gathers in the loader, indexed row stores in the epilogue).
+
+    ``m`` is the number of sorted rows (default: len(in_rows), else len(out_rows), else x rows).
+    With ``out_rows`` the result has ``y_rows`` rows (default m) and rows that no sorted row names
+    keep the content of ``out`` (zeros when ``out`` is not given)."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    _require_cuda(A, "A")
+    assert A.dim() == 3 and x.dim() == 2
+    if x.dtype not in (torch.float16, torch.bfloat16) or A.dtype != x.dtype:
+        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {A.dtype}")
+    gs = _as_i32(group_sizes)
+    g = gs.shape[0]
+    if group_to_weight is None:
+        assert A.shape[0] == g, f"{A.shape[0]=} != {g=}"
+    else:
+        group_to_weight = _as_i32(group_to_weight)
+        assert group_to_weight.shape == gs.shape
+    if in_rows is not None:
+        in_rows = _as_i32(in_rows)
+    if out_rows is not None:
+        out_rows = _as_i32(out_rows)
+    if m is None:
+        m = in_rows.numel() if in_rows is not None else (out_rows.numel() if out_rows is not None else x.shape[0])
+    assert in_rows is None or in_rows.numel() >= m
+    assert out_rows is None or out_rows.numel() >= m
+    x_rows, k = x.shape
+    n = A.shape[-1] if not trans_rhs else A.shape[-2]
+    k_rhs = A.shape[-2] if not trans_rhs else A.shape[-1]
+    assert k_rhs == k, f"contraction mismatch: x has k={k}, A has {k_rhs}"
+    if out_rows is None:
+        y_rows = m
+    elif y_rows is None:
+        y_rows = out.shape[0] if out is not None else m
+
+    xp = _dense16(_pad_last(x, 8))
+    Ap = _dense16(_pad_last2(A, 8))
+    kp = xp.shape[1]
+    np_ = Ap.shape[-1] if not trans_rhs else Ap.shape[-2]
+    padded_n = np_ != n
+    if out is not None and not padded_n:
+        assert out.shape == (y_rows, n) and out.dtype == x.dtype and out.is_contiguous()
+        y = out
+    elif out_rows is not None:
+        y = torch.zeros((y_rows, np_), dtype=x.dtype, device=x.device)
+        if out is not None:
+            y[:, :n] = out
+    else:
+        y = torch.empty((y_rows, np_), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else _workspace(m, g, x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_gmm_permuted(
+            xp.data_ptr(), x_rows, in_rows.data_ptr() if in_rows is not None else None,
+            Ap.data_ptr(), Ap.shape[0], gs.data_ptr(),
+            group_to_weight.data_ptr() if group_to_weight is not None else None,
+            y.data_ptr(), y_rows, out_rows.data_ptr() if out_rows is not None else None,
+            ws.data_ptr(), ws.numel(), m, kp, np_, g, int(bool(trans_rhs)), _DTYPE_CODE[x.dtype],
+            _cfg_ptr(cfg), _stream_ptr(x.device),
+        )
+    _lib.check(rc, "rd_gmm_permuted")
+    if padded_n:
+        y = y[:, :n].contiguous()
+        if out is not None:
+            out.copy_(y)
+            y = out
+    return y
+
+
+def tgmm_permuted_forward(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    group_sizes: torch.Tensor,
+    x_rows_index: Optional[torch.Tensor] = None,
+    y_rows_index: Optional[torch.Tensor] = None,
+    m: Optional[int] = None,
+    cfg: Optional[_lib.TileCfg] = None,
+    out: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One call of ``rd_tgmm_permuted``: out[i] = x[x_rows_index[rows of group i]]^T .
+    y[y_rows_index[rows of group i]], both gathers done by the kernel's loader."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    _require_cuda(y, "y")
+    assert y.dim() == 2 and x.dim() == 2
+    if x.dtype not in (torch.float16, torch.bfloat16) or y.dtype != x.dtype:
+        raise NotImplementedError(f"inputs must both be float16 or bfloat16, got {x.dtype} / {y.dtype}")
+    gs = _as_i32(group_sizes)
+    g = gs.numel()
+    if x_rows_index is not None:
+        x_rows_index = _as_i32(x_rows_index)
+    if y_rows_index is not None:
+        y_rows_index = _as_i32(y_rows_index)
+    if m is None:
+        m = (x_rows_index.numel() if x_rows_index is not None
+             else (y_rows_index.numel() if y_rows_index is not None else x.shape[0]))
+    k, n = x.shape[1], y.shape[1]
+    xp = _dense16(_pad_last(x, 8))
+    yp = _dense16(_pad_last(y, 8))
+    kp, np_ = xp.shape[1], yp.shape[1]
+    padded = (kp != k) or (np_ != n)
+    if out is not None and not padded:
+        assert out.shape == (g, k, n) and out.dtype == x.dtype and out.is_contiguous()
+        res = out
+    else:
+        res = torch.empty((g, kp, np_), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else _workspace(m, g, x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_tgmm_permuted(
+            xp.data_ptr(), xp.shape[0], x_rows_index.data_ptr() if x_rows_index is not None else None,
+            yp.data_ptr(), yp.shape[0], y_rows_index.data_ptr() if y_rows_index is not None else None,
+            gs.data_ptr(), res.data_ptr(), ws.data_ptr(), ws.numel(), m, kp, np_, g,
+            _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+        )
+    _lib.check(rc, "rd_tgmm_permuted")
+    if padded:
+        res = res[:, :k, :n].contiguous()
+        if out is not None:
+            out.copy_(res)
+            res = out
+    return res
+
+
+def _fused_permute_pays(m: int, g: int, scatter: bool) -> bool:
+    """Measured on B200: the fused kernel (cp.async row gathers feeding 128-row tiles) beats
+    gather_rows + the TMA-fed kernels only when it also saves the scatter pass over y and the
+    groups are long enough to be compute-bound (Mixtral-like shapes: +5 %); on short groups and
+    for gather-only calls the TMA-fed two-pass route is 2-6 % faster."""
+    return scatter and g > 0 and m // g >= 512
+
+
+def _gmm_permuted_two_pass(x, A, gs, in_rows, out_rows, y_rows, m, trans_rhs):
+    xs = x if in_rows is None else gather_rows(x, in_rows[:m].clamp(0, x.shape[0] - 1))
+    if xs.shape[0] != m:
+        xs = xs[:m] if xs.shape[0] > m else torch.nn.functional.pad(xs, (0, 0, 0, m - xs.shape[0]))
+    ys = gmm_forward(xs.contiguous(), A, gs, trans_rhs=trans_rhs)
+    if out_rows is None:
+        return ys
+    # Only the rows below sum(group_sizes) have a destination; the others are parked on an extra
+    # row that is dropped (no host read of group_sizes).
+    live = torch.arange(m, device=x.device) < gs.sum()
+    dest = torch.where(live & (out_rows[:m] >= 0) & (out_rows[:m] < y_rows), out_rows[:m].long(),
+                       torch.full((), y_rows, dtype=torch.long, device=x.device))
+    y = torch.zeros((y_rows + 1, ys.shape[1]), dtype=ys.dtype, device=x.device)
+    y.index_copy_(0, dest, ys)
+    return y[:y_rows]
+
+
+class _GmmPermutedFn(torch.autograd.Function):
+    """y = scatter(gmm(gather(x))) and its backward pass: dx_sorted = gmm(dy gathered by
+    out_rows, A transposed), summed into x's rows; dA = tgmm(x gathered by in_rows, dy gathered
+    by out_rows).  `fused` selects the permutation-fused kernels or gather_rows + the plain ones."""
+
+    @staticmethod
+    def forward(ctx, x, A, group_sizes, in_rows, out_rows, y_rows, m, trans_rhs, fused):
+        ctx.save_for_backward(x, A, group_sizes, in_rows, out_rows)
+        ctx.m, ctx.trans_rhs, ctx.fused = m, trans_rhs, fused
+        g = group_sizes.numel()
+        use_fused = fused if fused is not None else _fused_permute_pays(m, g, out_rows is not None)
+        if use_fused:
+            return gmm_permuted_forward(x, A, group_sizes, in_rows=in_rows, out_rows=out_rows, y_rows=y_rows,
+                                        m=m, trans_rhs=trans_rhs)
+        return _gmm_permuted_two_pass(x, A, _as_i32(group_sizes), in_rows, out_rows, y_rows, m, trans_rhs)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, A, gs, in_rows, out_rows = ctx.saved_tensors
+        m, trans_rhs, fused = ctx.m, ctx.trans_rhs, ctx.fused
+        dy = dy.contiguous()
+        dx = dA = None
+        # Gather-only calls: the TMA-fed kernels after gather_rows are the faster route unless
+        # the caller forces the fused kernels.
+        use_fused = bool(fused)
+        dys = None
+        if not use_fused:
+            dys = dy if out_rows is None else gather_rows(dy, out_rows[:m].clamp(0, dy.shape[0] - 1))
+        if ctx.needs_input_grad[0]:
+            if use_fused:
+                dxs = gmm_permuted_forward(dy, A, gs, in_rows=out_rows, m=m, trans_rhs=not trans_rhs)
+            else:
+                dxs = gmm_forward(dys, A, gs, trans_rhs=not trans_rhs)
+            if in_rows is None:
+                dx = dxs[: x.shape[0]] if dxs.shape[0] >= x.shape[0] else torch.nn.functional.pad(
+                    dxs, (0, 0, 0, x.shape[0] - dxs.shape[0]))
+            else:  # a token row may feed several sorted rows (top-k routing): sum them in fp32
+                idx = in_rows[:m].long().clamp_(0, x.shape[0] - 1)
+                dx = torch.zeros(x.shape, dtype=torch.float32, device=x.device).index_add_(0, idx, dxs.float())
+                dx = dx.to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            if use_fused:
+                if not trans_rhs:
+                    dA = tgmm_permuted_forward(x, dy, gs, x_rows_index=in_rows, y_rows_index=out_rows, m=m)
+                else:
+                    dA = tgmm_permuted_forward(dy, x, gs, x_rows_index=out_rows, y_rows_index=in_rows, m=m)
+            else:
+                xs = x if in_rows is None else gather_rows(x, in_rows[:m].clamp(0, x.shape[0] - 1))
+                dA = tgmm_forward(xs, dys, gs) if not trans_rhs else tgmm_forward(dys, xs, gs)
+        return dx, dA, None, None, None, None, None, None, None
+
+
+def ragged_dot_permuted(x, A, group_sizes, in_rows=None, out_rows=None, y_rows=None, m=None,
+                        trans_rhs=False, fused=None):
+    """``ragged_dot`` on un-sorted rows: ``y[out_rows[r]] = x[in_rows[r]] @ A[group of r]`` for the
+    sorted rows r < sum(group_sizes), zeros elsewhere; differentiable in x and A.  This is what an
+    MoE layer does around the reference's ``ragged_dot`` (gpu_ragged_dot.py:362) with
+    ``x[sorted_token_idx]`` before and the inverse permutation after.
+
+    ``fused=True`` runs the permutation-fused kernels (``rd_gmm_permuted`` / ``rd_tgmm_permuted``:
+    the sorted copies never exist), ``False`` gathers rows first and calls the plain kernels,
+    ``None`` picks by the measured rule in ``_fused_permute_pays``."""
+    if m is None:
+        m = in_rows.numel() if in_rows is not None else (out_rows.numel() if out_rows is not None else x.shape[0])
+    if in_rows is not None:
+        in_rows = _as_i32(in_rows)
+    if out_rows is not None:
+        out_rows = _as_i32(out_rows)
+        if y_rows is None:
+            y_rows = m
+    return _GmmPermutedFn.apply(x, A, group_sizes, in_rows, out_rows, y_rows, m, trans_rhs, fused)
+
+
 def _check_static_args(x, interpret, compute_dtype, acc_dtype):
     if interpret:
         raise NotImplementedError(

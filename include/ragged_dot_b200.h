@@ -139,6 +139,31 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
             void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
             const rd_tile_cfg* cfg, void* stream);
 
+/* Grouped GEMMs with the row permutation of a mixture-of-experts layer fused in.  The
+ * reference takes rows that are already sorted by group (gpu_ragged_dot.py:362-376) and leaves
+ * x_sorted = x[row_index] and the inverse permutation of the result to its caller; these entry
+ * points read and write the un-sorted tensors, so the sorted copies never exist (16-bit types).
+ *
+ *   rd_gmm_permuted   for r < sum(group_sizes):  y[out_rows[r], :] = x[in_rows[r], :] . W(r)
+ *     x        [x_rows, k];  in_rows  [m] int32, values in [0, x_rows), NULL = identity
+ *                            (then x_rows >= m);  A / num_weights / group_to_weight as for
+ *                            rd_gmm_indexed (group_to_weight NULL = group i uses A[i])
+ *     y        [y_rows, n];  out_rows [m] int32, NULL = identity (then y_rows == m and rows past
+ *                            sum(group_sizes) are zeroed as in rd_gmm).  With out_rows only the
+ *                            rows named are written (entries outside [0, y_rows) are dropped);
+ *                            rows named twice hold one of the results.
+ *   rd_tgmm_permuted  out[i] = x[x_row_index[rows of group i], :]^T . dout[dout_row_index[...], :]
+ *     either index may be NULL (identity).
+ * m is the static bound on the sorted rows (sum(group_sizes) <= m sizes the workspace). */
+int rd_gmm_permuted(const void* x, int x_rows, const int32_t* in_rows, const void* A, int num_weights,
+                    const int32_t* group_sizes, const int32_t* group_to_weight, void* y, int y_rows,
+                    const int32_t* out_rows, void* workspace, size_t workspace_bytes, int m, int k,
+                    int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg, void* stream);
+int rd_tgmm_permuted(const void* x, int x_rows, const int32_t* x_row_index, const void* dout,
+                     int dout_rows, const int32_t* dout_row_index, const int32_t* group_sizes,
+                     void* out, void* workspace, size_t workspace_bytes, int m, int k, int n, int g,
+                     int dtype, const rd_tile_cfg* cfg, void* stream);
+
 /* rd_gmm for callers that cannot supply a workspace and cannot allocate one.  It has no
  * counterpart in the reference (there XLA allocates every buffer).  Meant for an operator slot
  * whose argument list is fixed to inputs and outputs, inside a framework that owns all device

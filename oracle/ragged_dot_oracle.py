@@ -140,6 +140,24 @@ def ragged_dot_vjp(x, A, group_sizes, dout, trans_rhs: bool = False) -> Tuple[to
     return dx, dA
 
 
+def ragged_dot_permuted(x, A, group_sizes, in_rows=None, out_rows=None, y_rows=None,
+                        trans_rhs: bool = False, out=None) -> torch.Tensor:
+    """What a mixture-of-experts caller wraps around the reference's ragged_dot
+    (gpu_ragged_dot.py:362-376): gather the token rows into group order, multiply, and put the
+    result rows back: y[out_rows[r]] = (x[in_rows] . A)[r] for r < sum(group_sizes); other rows of
+    y keep `out` (zeros by default).  Without out_rows it is ragged_dot on the gathered rows."""
+    gs = torch.as_tensor(group_sizes).to(torch.int64)
+    total = int(gs.sum())
+    xs = x if in_rows is None else x[torch.as_tensor(in_rows).long()]
+    ys = ragged_dot(xs, A, gs, trans_rhs=trans_rhs)
+    if out_rows is None:
+        return ys
+    y_rows = ys.shape[0] if y_rows is None else y_rows
+    y = torch.zeros((y_rows, ys.shape[1]), dtype=ys.dtype) if out is None else out.clone()
+    y[torch.as_tensor(out_rows).long()[:total]] = ys[:total]
+    return y
+
+
 def rel_l2_err(a: torch.Tensor, b: torch.Tensor, axis=-1, mask=None) -> torch.Tensor:
     """err_fn of tests.py:74-79: ||a-b|| / max(||b||, 1e-7) along `axis`, zero where masked out."""
     a, b = _f32(a), _f32(b)
