@@ -584,7 +584,8 @@ def run_cpu_baseline(shape, kernels):
 
 # ---------------------------------------------------------------------------- our arm, N > 1
 def run_expert_parallel(args):
-    """N > 1: expert parallel forward.  Two dispatch modes are timed on the same inputs:
+    """N > 1: expert parallel forward.  Three dispatch modes are timed on the same inputs ("overlap":
+    ring-phased peer stores running under the flag-gated local GEMM), among them:
     "nccl" (sort + gather + NCCL all-to-all with host-known split sizes) and "p2p" (device-side
     plan + rows stored straight into the owners' receive buffers through peer memory, no host
     round trip).  `value` is the faster one; both are reported."""
@@ -603,7 +604,7 @@ def run_expert_parallel(args):
     peaks = measured_peaks()
     results = {}
     clocks = None
-    for mode in ("nccl", "p2p"):
+    for mode in ("nccl", "p2p", "overlap"):
         try:
             layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode)
             for _ in range(max(args.warmup, 3)):
@@ -631,26 +632,30 @@ def run_expert_parallel(args):
         clocks = sampler.stop()
         ms = e0.elapsed_time(e1) / args.steps
         parts = layer.timers_ms(args.steps)
-        t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"]], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"], parts.get("own_rows", 0.0)],
+                         dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         results[mode] = t.tolist()
         del layer
         torch.cuda.empty_cache()
     if rank == 0 and results:
         best = min(results, key=lambda m: results[m][0])
-        ms, gemm_ms, a2a_ms, first_ms = results[best]
+        ms, gemm_ms, a2a_ms, first_ms, _ = results[best]
         rows_global = tokens * top_k * world
         flops = 2.0 * rows_global * shape.k * shape.n
         gemm_tf = 2.0 * tokens * top_k * shape.k * shape.n / (gemm_ms * 1e-3) / 1e12
         row_bytes_out = tokens * top_k * shape.k * 2 * (world - 1) / world
         modes = {}
-        for m_, (t_ms, g_ms, x_ms, p_ms) in results.items():
+        for m_, (t_ms, g_ms, x_ms, p_ms, own_ms) in results.items():
             modes[m_] = {
                 "ms_per_step": t_ms, "tflops": flops / (t_ms * 1e-3) / 1e12,
                 "breakdown_ms": ({"sort_plan_gather": p_ms, "all_to_all": x_ms, "local_ragged_dot": g_ms}
                                  if m_ == "nccl" else
                                  {"count_allgather_plan": p_ms, "peer_store_dispatch_and_barrier": x_ms,
-                                  "local_ragged_dot": g_ms}),
+                                  "local_ragged_dot": g_ms} if m_ == "p2p" else
+                                 {"count_allgather_plan": p_ms, "peer_store_phases_from_plan_end": x_ms,
+                                  "own_rows_copied_from_plan_end": own_ms,
+                                  "flag_gated_ragged_dot_from_plan_end": g_ms}),
                 "exchange_GBps_per_gpu": row_bytes_out / (x_ms * 1e-3) / 1e9,
             }
         line = {
@@ -661,14 +666,26 @@ def run_expert_parallel(args):
                        "top_k": top_k, "experts": experts, "experts_per_gpu": experts // world,
                        "k": shape.k, "n": shape.n, "dispatch": best,
                        "collective": {"nccl": "NCCL all-to-all (rows) + all-to-all (counts)",
-                                      "p2p": "NCCL all-gather (counts) + peer stores over NVLink + symmetric-memory barrier"}[best],
+                                      "p2p": "NCCL all-gather (counts) + peer stores over NVLink + symmetric-memory barrier",
+                                      "overlap": "NCCL all-gather (counts) + ring-phased peer stores over NVLink overlapped "
+                                                 "with the local GEMM, which waits per source on ready flags"}[best],
                        "l2": "inputs larger than L2 (268 MB of rows per GPU)"},
             "clocks": clocks,
-            "gpu_launches": (3 if best == "nccl" else 5) * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> (local experts)",
-                         "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": gemm_tf / peaks["bf16_tflops"], "traffic": None,
-                         "peak_source": peaks["source"]},
+            "gpu_launches": {"nccl": 3, "p2p": 5, "overlap": 4 + world}[best] * args.steps,
+            "roofline": ({"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> (local experts)",
+                          "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                          "frac": gemm_tf / peaks["bf16_tflops"], "traffic": None,
+                          "peak_source": peaks["source"]} if best != "overlap" else
+                         # fused exchange + GEMM: target = slower of flops / GEMM peak and NVLink bytes / 770 GB/s
+                         # (measured peer-copy bandwidth per direction per GPU); achieved is over the span from
+                         # the end of the plan to the end of the GEMM, waits on remote rows included.
+                         {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> gated by ready flags + ep_dispatch_phase_kernel",
+                          "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                          "target_ms": max(2.0 * tokens * top_k * shape.k * shape.n / (peaks["bf16_tflops"] * 1e9),
+                                           row_bytes_out / 770e9 * 1e3),
+                          "frac": max(2.0 * tokens * top_k * shape.k * shape.n / (peaks["bf16_tflops"] * 1e9),
+                                      row_bytes_out / 770e9 * 1e3) / gemm_ms,
+                          "traffic": None, "peak_source": peaks["source"] + "; NVLink 770 GB/s per direction"}),
             "dispatch_modes": modes,
             "e2e": None,
         }

@@ -61,6 +61,19 @@ SIGNATURES = {
         + [_c_int] * 6
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
+    "rd_ep_plan_ring": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                 _c_void_p, _c_void_p]),
+    "rd_ep_dispatch_phase": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+         _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    ),
+    "rd_gmm_indexed_when_ready": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p, _c_int, _c_int, _c_void_p],
+    ),
     "rd_gmm_permuted": (
         _c_int,
         [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,

@@ -316,10 +316,16 @@ int rd_metadata(const int32_t* group_sizes, int g, int m, int chunk_m, int32_t* 
 
 // Shared body of rd_gmm / rd_gmm_indexed.  `num_weights` is A's leading dimension;
 // `group_to_weight` (device, [g]) is null when group i uses A[i].
+struct ReadyFlags {
+  const int32_t* flags;  // null: no waiting
+  int groups_per_flag;
+  int epoch;
+};
+
 static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
                     const int32_t* group_to_weight, int num_weights, void* y, void* workspace,
                     size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
-                    const rd_tile_cfg* cfg, void* stream_v) {
+                    const rd_tile_cfg* cfg, void* stream_v, ReadyFlags ready = {nullptr, 1, 0}) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16 && dtype != RD_DTYPE_F32) return RD_ERR_BAD_DTYPE;
   const bool f32 = dtype == RD_DTYPE_F32;
@@ -391,7 +397,7 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
     if (rc != RD_OK) return rc;
   }
 
-  GemmArgs args;
+  GemmArgs args = {};
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
   args.k_tiles = 0;
@@ -404,9 +410,13 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.totals = w.totals();
   args.status = w.status();
   args.out = y;
+  args.ready_flags = ready.flags;
+  args.groups_per_flag = ready.groups_per_flag > 0 ? ready.groups_per_flag : 1;
+  args.ready_epoch = ready.epoch;
 
   const int ctas = pick_ctas(cfg);
   if (f32) {
+    if (ready.flags != nullptr) return RD_ERR_BAD_DTYPE;  // the float32 kernels do not wait on flags
     if (trans_rhs) {
       if (bn == 256) return launch_gemm_f32<256, true, false>(ta, tb, tout, args, ctas, stream);
       if (bn == 128) return launch_gemm_f32<128, true, false>(ta, tb, tout, args, ctas, stream);
@@ -483,8 +493,61 @@ int rd_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, 
     return RD_ERR_BAD_SHAPE;
   if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals) return RD_ERR_BAD_POINTER;
   rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals);
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 0, nullptr);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int rank,
+                    int32_t* dest_offset, int32_t* segment_sizes, int32_t* fill, int32_t* totals,
+                    int32_t* phase_done, void* stream) {
+  if (world <= 0 || num_experts <= 0 || num_experts % world != 0 || rank < 0 || rank >= world)
+    return RD_ERR_BAD_SHAPE;
+  if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals || !phase_done)
+    return RD_ERR_BAD_POINTER;
+  rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 1, phase_done);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_dispatch_phase(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
+                         int num_experts, int world, int rank, int phase, const int32_t* dest_offset,
+                         int32_t* fill, void* dest_base, int capacity_rows, int32_t* dest_pos,
+                         int32_t* phase_done, int32_t* dest_ready_flag, int epoch, int max_blocks,
+                         void* stream) {
+  if (tokens < 0 || top_k <= 0 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 ||
+      num_experts <= 0 || num_experts % world != 0 || capacity_rows < 0 || rank < 0 ||
+      rank >= world || phase < 0 || phase >= world)
+    return RD_ERR_BAD_SHAPE;
+  if (!aligned16(dest_base) || !dest_offset || !fill || !dest_pos || !phase_done || !dest_ready_flag ||
+      (tokens > 0 && (!aligned16(x) || !routing)))
+    return RD_ERR_BAD_POINTER;
+  const long long entries = static_cast<long long>(tokens) * top_k;
+  const int warps_per_block = rd::kEpThreads / 32;
+  long long blocks = (entries + warps_per_block - 1) / warps_per_block;
+  // The phases run next to the local GEMM's persistent CTAs: by default two blocks per SM, so
+  // that both kinds of block stay resident together.
+  const int cap = max_blocks > 0 ? max_blocks : sm_count() * 2;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;  // the flag is written even when there is nothing to send
+  rd::ep_dispatch_phase_kernel<<<static_cast<int>(blocks), rd::kEpThreads, 0,
+                                 static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), routing, tokens, top_k, row_bytes / 16, num_experts,
+      num_experts / world, (rank + phase) % world, dest_offset, fill, static_cast<uint4*>(dest_base),
+      capacity_rows, dest_pos, phase_done + phase, dest_ready_flag, epoch, phase == 0 ? 1 : 0);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                              const int32_t* group_to_weight, void* y, void* workspace,
+                              size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs,
+                              int dtype, const rd_tile_cfg* cfg, const int32_t* ready_flags,
+                              int groups_per_flag, int epoch, void* stream) {
+  if (g > 0 && group_to_weight == nullptr) return RD_ERR_BAD_POINTER;
+  if (ready_flags == nullptr) return RD_ERR_BAD_POINTER;
+  if (groups_per_flag <= 0) return RD_ERR_BAD_SHAPE;
+  if (cfg && cfg->cta_group == 2) return RD_ERR_BAD_CONFIG;  // CTA pairs do not wait on flags
+  return gmm_impl(x, A, group_sizes, group_to_weight, num_weights, y, workspace, workspace_bytes, m, k,
+                  n, g, trans_rhs, dtype, cfg, stream, ReadyFlags{ready_flags, groups_per_flag, epoch});
 }
 
 int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
@@ -588,7 +651,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
     if (rc != RD_OK) return rc;
   }
 
-  GemmArgs args;
+  GemmArgs args = {};
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
   args.k_tiles = static_cast<int>(k_tiles);
@@ -672,7 +735,7 @@ int rd_gmm_permuted(const void* x, int x_rows, const int32_t* in_rows, const voi
     if (rc != RD_OK) return rc;
   }
 
-  GemmArgs args;
+  GemmArgs args = {};
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
   args.k_tiles = 0;
@@ -746,7 +809,7 @@ int rd_tgmm_permuted(const void* x, int x_rows, const int32_t* x_row_index, cons
     if (rc != RD_OK) return rc;
   }
 
-  GemmArgs args;
+  GemmArgs args = {};
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
   args.k_tiles = (k + rd::kTileM - 1) / rd::kTileM;

@@ -44,25 +44,39 @@ ep_count_kernel(const int32_t* __restrict__ routing, int entries, int num_expert
 //   segment_sizes[s*El+j] rows I receive from source s for my local expert j
 //   fill[e]               reset to 0 (arrival counters used by the dispatch kernel)
 //   totals[0]             rows I receive in all
+//
+// ring != 0 selects the layout of the overlapped exchange: on rank d the segments are ordered by
+// "position" q = (d - source) mod W, i.e. d's own rows first, then those of d-1, d-2, ...; a
+// source sends to d in phase q of its dispatch, so positions fill in the order the local GEMM
+// reads them.  phase_done[W] (may be null) are the per-phase block counters, reset here.
 __global__ void __launch_bounds__(kEpThreads)
 ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int num_experts, int rank,
                int32_t* __restrict__ dest_offset, int32_t* __restrict__ segment_sizes,
-               int32_t* __restrict__ fill, int32_t* __restrict__ totals) {
+               int32_t* __restrict__ fill, int32_t* __restrict__ totals, int ring,
+               int32_t* __restrict__ phase_done) {
   const int local = num_experts / world;
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     const int owner = e / local;
     const int first = owner * local;
     int off = 0;
-    for (int s = 0; s < rank; ++s)
+    // Segments in front of mine in the owner's buffer: sources 0..rank-1, or (ring) the
+    // sources at positions 0..my position-1, which are owner, owner-1, ...
+    const int before = ring ? (owner - rank + world) % world : rank;
+    for (int q = 0; q < before; ++q) {
+      const int s = ring ? (owner - q + world) % world : q;
       for (int j = 0; j < local; ++j) off += counts_all[s * num_experts + first + j];
+    }
     for (int j = first; j < e; ++j) off += counts_all[rank * num_experts + j];
     dest_offset[e] = off;
     fill[e] = 0;
   }
   for (int i = threadIdx.x; i < world * local; i += blockDim.x) {
-    const int s = i / local, j = i - s * local;
+    const int q = i / local, j = i - q * local;
+    const int s = ring ? (rank - q + world) % world : q;
     segment_sizes[i] = counts_all[s * num_experts + rank * local + j];
   }
+  if (phase_done != nullptr)
+    for (int i = threadIdx.x; i < world; i += blockDim.x) phase_done[i] = 0;
   if (threadIdx.x == 0) {
     int total = 0;
     for (int s = 0; s < world; ++s)
@@ -109,6 +123,65 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ rout
     for (; v < vecs_per_row; v += 32) dst[v] = src[v];
   }
   __threadfence_system();  // rows must be visible to their owners before the ranks synchronise
+}
+
+// One phase of the overlapped exchange: copies the (token, slot) pairs whose expert lives on
+// rank `dest` = (rank + phase) mod W, and when the last block has finished (its stores fenced
+// at system scope) writes `epoch` into ready_flag, the word ready[phase] of dest's flag array:
+// "the rows of position `phase` have landed".  Phases run one after the other on one stream,
+// and in phase p all ranks together form a permutation (r -> r+p), so every NVLink port
+// carries one flow at a time and dest's positions complete in the order its GEMM reads them.
+__global__ void __launch_bounds__(kEpThreads)
+ep_dispatch_phase_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ routing,
+                         int tokens, int top_k, int vecs_per_row, int num_experts,
+                         int experts_per_rank, int dest, const int32_t* __restrict__ dest_offset,
+                         int32_t* __restrict__ fill, uint4* __restrict__ dest_base,
+                         int capacity_rows, int32_t* __restrict__ dest_pos,
+                         int32_t* __restrict__ phase_done, int32_t* ready_flag, int epoch,
+                         int report_invalid) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kEpThreads / 32;
+  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * warps_per_block;
+  const int entries = tokens * top_k;
+  const int e_lo = dest * experts_per_rank, e_hi = e_lo + experts_per_rank;
+  for (int i = warp_global; i < entries; i += warp_stride) {
+    const int e = routing[i];
+    if (e < e_lo || e >= e_hi) {
+      // An expert id outside [0, E) belongs to no phase: one phase (report_invalid) marks it.
+      if (report_invalid && (e < 0 || e >= num_experts) && lane == 0) dest_pos[i] = -1;
+      continue;
+    }
+    int pos = 0;
+    if (lane == 0) pos = dest_offset[e] + atomicAdd(&fill[e], 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos >= capacity_rows) pos = -1;
+    if (lane == 0) dest_pos[i] = pos;
+    if (pos < 0) continue;
+    const uint4* src = x + static_cast<size_t>(i / top_k) * vecs_per_row;
+    uint4* dst = dest_base + static_cast<size_t>(pos) * vecs_per_row;
+    int v = lane;
+    for (; v + 96 < vecs_per_row; v += 128) {
+      const uint4 a = src[v], b = src[v + 32], c = src[v + 64], d = src[v + 96];
+      dst[v] = a;
+      dst[v + 32] = b;
+      dst[v + 64] = c;
+      dst[v + 96] = d;
+    }
+    for (; v < vecs_per_row; v += 32) dst[v] = src[v];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(phase_done, 1) + 1;
+    if (done == static_cast<int>(gridDim.x)) {
+      // Every block has fenced its stores before its increment; order this thread's flag store
+      // after having seen them all.
+      __threadfence_system();
+      *reinterpret_cast<volatile int32_t*>(ready_flag) = epoch;
+      __threadfence_system();
+    }
+  }
 }
 
 }  // namespace rd

@@ -84,6 +84,12 @@ struct GemmArgs {
   const int32_t* totals;       // {live row tiles, min(sum(group_sizes), m)}
   int32_t* status;
   void* out;
+  // gmm, optional: rows of group i may be read once ready_flags[i / groups_per_flag] >=
+  // ready_epoch (the rows are being written by other kernels, possibly on other GPUs, while
+  // this kernel runs).  Null: all rows are there at launch.
+  const int32_t* ready_flags;
+  int groups_per_flag;
+  int ready_epoch;
 };
 
 // Coordinates of one CTA's share of a tile.
@@ -273,11 +279,22 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int ready_slot = -1;  // last ready flag this producer has seen set
       for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
                                   : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
         const int nb = t.n0 + cta_rank * kBCols;  // first B column this CTA loads
         const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        if (!kTgmm && p.ready_flags != nullptr) {
+          const int slot = t.group / p.groups_per_flag;
+          if (slot != ready_slot) {
+            if (!wait_flag_ge(p.ready_flags + slot, p.ready_epoch, abort_ptr)) {
+              ok = false;
+              break;
+            }
+            ready_slot = slot;
+          }
+        }
         RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 0);
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages;

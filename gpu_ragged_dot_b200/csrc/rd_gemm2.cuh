@@ -133,10 +133,21 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int ready_slot = -1;  // last ready flag this producer has seen set
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
         const int halves = halves_of(t);
         const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        if (!kTgmm && p.ready_flags != nullptr) {
+          const int slot = t.group / p.groups_per_flag;
+          if (slot != ready_slot) {
+            if (!wait_flag_ge(p.ready_flags + slot, p.ready_epoch, abort_ptr)) {
+              ok = false;
+              break;
+            }
+            ready_slot = slot;
+          }
+        }
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;

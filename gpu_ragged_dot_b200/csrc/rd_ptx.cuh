@@ -145,6 +145,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait until the 32-bit word at `flag` (written by a kernel on this or another GPU, at
+// system scope, after the data it guards) is >= `value`.  The proxy fence orders the TMA loads
+// that follow after the acquire.  Same expiry rule as mbar_wait.
+__device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int value, volatile int* abort_flag) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= value) break;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > RD_WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(256);
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -85,11 +85,15 @@ class ExpertParallelRaggedDot:
 
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
-                 dispatch: str = "nccl", capacity_rows: Optional[int] = None):
+                 dispatch: str = "nccl", capacity_rows: Optional[int] = None,
+                 own_blocks: int = 0, side_blocks: int = 0):
         from . import workloads
 
-        assert dispatch in ("nccl", "p2p")
+        assert dispatch in ("nccl", "p2p", "overlap")
         self.dispatch, self.capacity_rows, self._p2p = dispatch, capacity_rows, None
+        self._ov, self._epoch = None, 0
+        # overlap mode: grid caps of the phase kernels (0 = library default), phase 0 / the others
+        self.own_blocks, self.side_blocks = own_blocks, side_blocks
         self.dtype = dtype
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -109,7 +113,10 @@ class ExpertParallelRaggedDot:
         for e in self._events:
             tot["permute"] += e[0].elapsed_time(e[1])
             tot["a2a"] += e[1].elapsed_time(e[2])
-            tot["gemm"] += e[2].elapsed_time(e[3])
+            # overlap mode: exchange and GEMM both start when the plan is done and run together
+            tot["gemm"] += (e[1] if self.dispatch == "overlap" else e[2]).elapsed_time(e[3])
+        if self.dispatch == "overlap":  # when the GEMM could start: own rows copied
+            tot["own_rows"] = sum(e[1].elapsed_time(e[4]) for e in self._events)
         return {k: v / max(steps, 1) for k, v in tot.items()}
 
     # ------------------------------------------------------------------ peer-store dispatch
@@ -171,12 +178,116 @@ class ExpertParallelRaggedDot:
             self._events.append(ev)
         return y, seg_sizes, dest_pos, totals
 
+    # ------------------------------------------------------------------ overlapped exchange + GEMM
+    def _overlap_setup(self, capacity_rows: int):
+        """Receive buffer and ready flags in symmetric memory, persistent plan buffers, side stream."""
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+
+        dev = self.device
+        buf = symm_mem.empty((capacity_rows, self.k), dtype=self.dtype, device=dev)
+        flags = symm_mem.empty((max(self.world, 4),), dtype=torch.int32, device=dev)
+        flags.zero_()
+        if self.world > 1:
+            grp = self.group if self.group is not None else dist.group.WORLD
+            hb = symm_mem.rendezvous(buf, grp)
+            hf = symm_mem.rendezvous(flags, grp)
+            buf_ptrs, flag_ptrs = [int(p) for p in hb.buffer_ptrs], [int(p) for p in hf.buffer_ptrs]
+            torch.cuda.synchronize(dev)
+            hf.barrier(channel=0)  # every rank's flags are zero before anyone stores an epoch
+            torch.cuda.synchronize(dev)
+        else:
+            hb = hf = None
+            buf_ptrs, flag_ptrs = [buf.data_ptr()], [flags.data_ptr()]
+        E, W = self.num_experts, self.world
+        self._ov = {
+            "buf": buf, "flags": flags, "handles": (hb, hf), "capacity": capacity_rows,
+            "buf_ptrs": buf_ptrs, "flag_ptrs": flag_ptrs,
+            "counts_all": torch.empty((W, E), dtype=torch.int32, device=dev),
+            "plan": {name: torch.empty(size, dtype=torch.int32, device=dev)
+                     for name, size in (("dest_offset", E), ("segment_sizes", E), ("fill", E), ("totals", 1),
+                                        ("phase_done", W))},
+            "y": torch.empty((capacity_rows, self.n), dtype=self.dtype, device=dev),
+            "ws": ops._workspace(capacity_rows, E, dev),
+            "seg2e": torch.arange(self.local_experts, dtype=torch.int32, device=dev).repeat(W),
+            "side": torch.cuda.Stream(device=dev, priority=-1),
+            "ev_plan": torch.cuda.Event(), "ev_done": torch.cuda.Event(),
+        }
+
+    def forward_overlap(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
+        """Exchange and local ragged_dot running together: after the plan, the W dispatch phases go
+        out on a side stream (phase p sends to rank+p and raises flag p there) while the GEMM,
+        launched at once on the main stream, multiplies position q as soon as flag q is up.
+
+        Returns (y [capacity, n], segment_sizes [W*El] in position order, dest_pos [T, top_k], totals)."""
+        from . import _lib, ops
+
+        tokens, top_k = routing.shape
+        if self._ov is None:
+            self._overlap_setup(self.capacity_rows or tokens * top_k * self.world)
+        st = self._ov
+        self._epoch += 1
+        epoch, W = self._epoch, self.world
+        main = torch.cuda.current_stream(self.device)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
+        if timed:
+            ev[0].record()
+        routing = routing.to(torch.int32).contiguous()
+        x_tokens = x_tokens.contiguous()
+        counts = ops.ep_count(routing, self.num_experts)
+        if W > 1:
+            # Also the "receive buffers are free again" barrier (see forward_p2p).
+            dist.all_gather_into_tensor(st["counts_all"].view(-1), counts, group=self.group)
+        else:
+            st["counts_all"].copy_(counts.view(1, -1))
+        plan = ops.ep_plan_ring(st["counts_all"], self.rank, st["plan"])
+        dest_pos = torch.empty(tokens * top_k, dtype=torch.int32, device=self.device)
+        if timed:
+            ev[1].record()
+        st["ev_plan"].record(main)
+        side = st["side"]
+        side.wait_event(st["ev_plan"])
+
+        def phase(p):
+            d = (self.rank + p) % W
+            ops.ep_dispatch_phase(x_tokens, routing, self.num_experts, W, self.rank, p, plan,
+                                  st["buf_ptrs"][d], st["capacity"], dest_pos, st["flag_ptrs"][d] + 4 * p, epoch,
+                                  max_blocks=self.own_blocks if p == 0 else self.side_blocks)
+
+        # Phases to other ranks go out on the side stream (launched first, high priority); the
+        # local GEMM never waits for them -- it waits for the other GPUs' phases.
+        with torch.cuda.stream(side):
+            for p in range(1, W):
+                phase(p)
+            if timed:
+                ev[2].record(side)
+            st["ev_done"].record(side)
+        # Phase 0 (this rank's own rows, a local copy) runs on the main stream in front of the
+        # GEMM, so the GEMM never waits for a kernel of its own GPU.
+        phase(0)
+        if timed:
+            ev.append(torch.cuda.Event(enable_timing=True))
+            ev[4].record()
+        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        y = ops.gmm_forward(st["buf"], self.weights, plan["segment_sizes"], group_to_weight=st["seg2e"],
+                            cfg=cfg, out=st["y"], workspace=st["ws"],
+                            ready=(st["flags"], self.local_experts, epoch))
+        if timed:
+            ev[3].record()
+        # The step is over on this rank when its own sends are, too.
+        main.wait_event(st["ev_done"])
+        if timed:
+            self._events.append(ev)
+        return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
+
     def forward(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
         """Returns (y [rows_received, n], plan).  y's rows are ordered (source rank, local expert)."""
         from . import ops
 
         if self.dispatch == "p2p":
             return self.forward_p2p(x_tokens, routing, timed=timed)
+        if self.dispatch == "overlap":
+            return self.forward_overlap(x_tokens, routing, timed=timed)
 
         plan = plan_dispatch(routing, self.num_experts, self.group)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None

@@ -151,11 +151,14 @@ def gmm_forward(
     out: Optional[torch.Tensor] = None,
     workspace: Optional[torch.Tensor] = None,
     group_to_weight: Optional[torch.Tensor] = None,
+    ready: Optional[tuple] = None,
 ) -> torch.Tensor:
     """One call of ``rd_gmm``: y[m,n] = ragged x[m,k] . A[g,k,n] (or A[g,n,k] with trans_rhs).
 
     With ``group_to_weight`` (int32 [g], values in [0, A.shape[0])) it is ``rd_gmm_indexed``:
-    group i multiplies by A[group_to_weight[i]] and g may differ from A.shape[0]."""
+    group i multiplies by A[group_to_weight[i]] and g may differ from A.shape[0].
+    With ``ready = (flags int32 tensor, groups_per_flag, epoch)`` it is
+    ``rd_gmm_indexed_when_ready``: group i's rows are read once flags[i // groups_per_flag] >= epoch."""
     lib = _lib.load()
     _require_cuda(x, "x")
     _require_cuda(A, "A")
@@ -163,6 +166,7 @@ def gmm_forward(
     gs = _as_i32(group_sizes)
     if group_to_weight is None:
         assert A.shape[0] == gs.shape[0], f"{A.shape[0]=} != {gs.shape[0]=}"
+        assert ready is None, "ready flags need group_to_weight (rd_gmm_indexed_when_ready)"
     else:
         group_to_weight = _as_i32(group_to_weight)
         assert group_to_weight.shape == gs.shape
@@ -196,11 +200,20 @@ def gmm_forward(
                 m, kp, np_, g, int(bool(trans_rhs)), _DTYPE_CODE[x.dtype], _cfg_ptr(cfg),
                 _stream_ptr(x.device),
             )
-        else:
+        elif ready is None:
             rc = lib.rd_gmm_indexed(
                 xp.data_ptr(), Ap.data_ptr(), Ap.shape[0], gs.data_ptr(), group_to_weight.data_ptr(),
                 y.data_ptr(), ws.data_ptr(), ws.numel(), m, kp, np_, g, int(bool(trans_rhs)),
                 _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+            )
+        else:
+            flags, groups_per_flag, epoch = ready
+            assert flags.dtype == torch.int32 and flags.is_cuda
+            rc = lib.rd_gmm_indexed_when_ready(
+                xp.data_ptr(), Ap.data_ptr(), Ap.shape[0], gs.data_ptr(), group_to_weight.data_ptr(),
+                y.data_ptr(), ws.data_ptr(), ws.numel(), m, kp, np_, g, int(bool(trans_rhs)),
+                _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), flags.data_ptr(), int(groups_per_flag), int(epoch),
+                _stream_ptr(x.device),
             )
     _lib.check(rc, "rd_gmm")
     if padded_n:
@@ -275,6 +288,45 @@ def ep_dispatch(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world:
                                 _stream_ptr(x.device))
     _lib.check(rc, "rd_ep_dispatch")
     return dest_pos.view(tokens, top_k)
+
+
+def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = None) -> dict:
+    """``rd_ep_plan_ring``: the plan of the overlapped exchange (receive buffer ordered by position
+    q = (rank - source) mod W).  Returns / refills a dict with dest_offset[E], segment_sizes[E],
+    fill[E], totals[1], phase_done[W]."""
+    lib = _lib.load()
+    assert counts_all.dim() == 2 and counts_all.dtype == torch.int32 and counts_all.is_contiguous()
+    world, experts = counts_all.shape
+    dev = counts_all.device
+    if bufs is None:
+        bufs = {name: torch.empty(size, dtype=torch.int32, device=dev)
+                for name, size in (("dest_offset", experts), ("segment_sizes", experts), ("fill", experts),
+                                   ("totals", 1), ("phase_done", world))}
+    with torch.cuda.device(dev):
+        rc = lib.rd_ep_plan_ring(counts_all.data_ptr(), world, experts, rank, bufs["dest_offset"].data_ptr(),
+                                 bufs["segment_sizes"].data_ptr(), bufs["fill"].data_ptr(),
+                                 bufs["totals"].data_ptr(), bufs["phase_done"].data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "rd_ep_plan_ring")
+    return bufs
+
+
+def ep_dispatch_phase(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world: int, rank: int,
+                      phase: int, plan: dict, dest_base: int, capacity_rows: int, dest_pos: torch.Tensor,
+                      dest_ready_flag: int, epoch: int, max_blocks: int = 0) -> None:
+    """``rd_ep_dispatch_phase`` on the current stream: rows for rank (rank + phase) % world go to the
+    buffer at address ``dest_base``; ``dest_ready_flag`` is the address of word ``phase`` of that
+    rank's flag array."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    assert x.is_contiguous() and routing.dtype == torch.int32 and routing.is_contiguous()
+    tokens, top_k = routing.shape
+    with torch.cuda.device(x.device):
+        rc = lib.rd_ep_dispatch_phase(
+            x.data_ptr(), routing.data_ptr(), tokens, top_k, x.shape[1] * x.element_size(), num_experts, world,
+            rank, phase, plan["dest_offset"].data_ptr(), plan["fill"].data_ptr(), dest_base, capacity_rows,
+            dest_pos.data_ptr(), plan["phase_done"].data_ptr(), dest_ready_flag, epoch, max_blocks,
+            _stream_ptr(x.device))
+    _lib.check(rc, "rd_ep_dispatch_phase")
 
 
 def tgmm_forward(

@@ -132,6 +132,40 @@ int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k,
                    int num_experts, int world, const int32_t* dest_offset, int32_t* fill,
                    const uint64_t* peer_base, int capacity_rows, int32_t* dest_pos, void* stream);
 
+/* Expert-parallel dispatch overlapped with the local GEMM (same roles as the three functions
+ * above, no counterpart in the reference).  The receive buffer of rank d is laid out by
+ * "position" q = (d - source) mod world: d's own rows first, then those of d-1, d-2, ...
+ *   rd_ep_plan_ring       as rd_ep_plan for that layout (segment q*El + j = rows from source
+ *                         (rank - q) mod world for local expert j); resets phase_done[world].
+ *   rd_ep_dispatch_phase  phase p of the exchange, p = 0 .. world-1, launched in that order on one
+ *                         stream: copies the rows routed to rank (rank + p) mod world into
+ *                         dest_base (that rank's buffer as seen from this GPU) and, when its last
+ *                         block is done, stores `epoch` to *dest_ready_flag, which must be word p of
+ *                         that rank's flag array.  In phase p the ranks form the permutation
+ *                         r -> r + p, so every NVLink port carries one flow at a time.
+ *                         max_blocks caps the grid (0 = two blocks per SM).
+ *   rd_gmm_indexed_when_ready  rd_gmm_indexed whose loader, before it reads the rows of group i,
+ *                         waits (bounded: expiry gives RD_ERR_DEVICE_WAIT through the status word)
+ *                         until ready_flags[i / groups_per_flag] >= epoch.  Launched right after
+ *                         the plan, it multiplies position q while positions q+1.. are still
+ *                         arriving.  Epochs must increase from call to call; flags start at 0.
+ * The caller keeps one exchange in flight per buffer: a rank may start the next exchange only
+ * when every rank has finished reading its buffer (e.g. the all-gather of the next counts, issued
+ * after the GEMM in stream order).  Plain peer stores and loads of flags only. */
+int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int rank,
+                    int32_t* dest_offset, int32_t* segment_sizes, int32_t* fill, int32_t* totals,
+                    int32_t* phase_done, void* stream);
+int rd_ep_dispatch_phase(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
+                         int num_experts, int world, int rank, int phase, const int32_t* dest_offset,
+                         int32_t* fill, void* dest_base, int capacity_rows, int32_t* dest_pos,
+                         int32_t* phase_done, int32_t* dest_ready_flag, int epoch, int max_blocks,
+                         void* stream);
+int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                              const int32_t* group_to_weight, void* y, void* workspace,
+                              size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs,
+                              int dtype, const rd_tile_cfg* cfg, const int32_t* ready_flags,
+                              int groups_per_flag, int epoch, void* stream);
+
 /* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
  * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass
  * (gpu_ragged_dot.py:401).  Empty groups produce zero blocks. */

@@ -1,6 +1,6 @@
-"""Two-GPU expert-parallel check (skipped unless two CUDA devices are visible): both dispatch
-modes, NCCL all-to-all and peer stores, against a routing + GEMM oracle built from every rank's
-inputs.  Ranks are child processes, one per GPU; NVLS is switched off for the collectives."""
+"""Two-GPU expert-parallel check (skipped unless two CUDA devices are visible): the three
+dispatch modes -- NCCL all-to-all, peer stores + barrier, and the phased peer stores overlapped
+with the flag-gated local GEMM -- against a routing + GEMM oracle built from every rank's inputs.  Ranks are child processes, one per GPU; NVLS is switched off for the collectives."""
 
 import os
 import socket
@@ -33,14 +33,20 @@ def _worker(rank, world, port, out_dir):
     x = workloads.normal_tensor((T, k), 1.0, 1000 + rank, dev)
     routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=3000 + rank)).to(dev)
     res = {"x": x.cpu(), "routing": routing.cpu()}
-    for mode in ("nccl", "p2p"):
+    for mode in ("nccl", "p2p", "overlap"):
         layer = ep.ExpertParallelRaggedDot(E, k, n, dev, seed=2000 + rank, dispatch=mode)
-        for step in range(2):  # twice: the second step reuses the receive buffer
+        for step in range(3):  # several steps: the later ones reuse the receive buffer (and flags)
             out = layer.forward(x, routing)
         torch.cuda.synchronize()
         if mode == "nccl":
             y, plan = out
             res["nccl"] = {"y": y.cpu(), "seg": plan.segment_sizes.cpu()}
+        elif mode == "overlap":
+            from gpu_ragged_dot_b200 import ops
+            y, seg, dest_pos, totals = out
+            res["overlap"] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu(),
+                              "status": ops.device_status(layer._ov["ws"]),
+                              "flags": layer._ov["flags"][:world].cpu()}
         else:
             y, seg, dest_pos, totals = out
             res["p2p"] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu()}
@@ -84,3 +90,23 @@ def test_expert_parallel_two_gpus(tmp_path):
                 assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
                 assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
                 off += len(idx)
+        # overlapped mode: receive buffer ordered by position q = (d - source) mod W
+        ov = res[d]["overlap"]
+        assert ov["status"] == 0, "a bounded wait expired on the device"
+        assert ov["flags"].tolist() == [3] * world  # third step's epoch on every position
+        off = 0
+        seg_ring = []
+        for q in range(world):
+            s = (d - q) % world
+            flat = res[s]["routing"].reshape(-1)
+            for j in range(local):
+                idx = (flat == d * local + j).nonzero().flatten()
+                seg_ring.append(len(idx))
+                if len(idx):
+                    rows = res[s]["x"][idx // top_k].float()
+                    want = (rows @ w[j]).to(torch.bfloat16).float()
+                    pos = res[s]["overlap"]["pos"].reshape(-1)[idx].long()
+                    assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
+                    assert torch.allclose(ov["y"][pos].float(), want, rtol=2e-2, atol=2e-2)
+                off += len(idx)
+        assert ov["seg"].tolist() == seg_ring

@@ -474,6 +474,96 @@ def test_ep_plan_and_dispatch_emulated_ranks(world):
         assert bool(torch.isnan(y[total:].float()).all()), "NO_ZERO_TAIL: rows past the total must stay untouched"
 
 
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_ep_ring_phases_emulated_ranks(world):
+    """The overlapped exchange with W ranks emulated on one GPU, everything on one stream so that
+    no kernel ever waits for a later one: all ranks' phase kernels run first (each raises its flag
+    on the destination), then every rank's flag-gated GEMM finds its flags up.  Checks the ring
+    layout (position q = (dest - source) mod W), the flags, and the GEMM against the oracle; two
+    epochs in a row."""
+    E, k, n, T, top_k = 16, 128, 72, 200, 4
+    local = E // world
+    capacity = T * top_k * world
+    weights = workloads.normal_tensor((E, k, n), k ** -0.5, 7, DEV)
+    bufs = [torch.full((capacity, k), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    flags = [torch.zeros(max(world, 4), dtype=torch.int32, device=DEV) for _ in range(world)]
+    for epoch in (1, 2):
+        xs = [workloads.normal_tensor((T, k), 1.0, 1000 * epoch + r, DEV) for r in range(world)]
+        routings = [torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=3000 * epoch + r)).to(DEV)
+                    for r in range(world)]
+        counts_all = torch.stack([ops.ep_count(routings[r], E) for r in range(world)]).contiguous()
+        cnt = counts_all.cpu().numpy()
+        plans, poss = [], []
+        for r in range(world):
+            plan = ops.ep_plan_ring(counts_all, r)
+            # oracle of the ring plan
+            seg_ref = np.array([cnt[(r - q) % world, r * local + j] for q in range(world) for j in range(local)])
+            assert np.array_equal(plan["segment_sizes"].cpu().numpy(), seg_ref)
+            off_ref = np.zeros(E, dtype=np.int64)
+            for e in range(E):
+                owner, first = e // local, (e // local) * local
+                before = (owner - r) % world
+                off_ref[e] = sum(int(cnt[(owner - q) % world, first:first + local].sum()) for q in range(before)) \
+                    + int(cnt[r, first:e].sum())
+            assert np.array_equal(plan["dest_offset"].cpu().numpy(), off_ref)
+            assert int(plan["totals"].cpu()) == int(cnt[:, r * local:(r + 1) * local].sum())
+            dest_pos = torch.full((T * top_k,), -7, dtype=torch.int32, device=DEV)
+            for p in range(world):
+                d = (r + p) % world
+                ops.ep_dispatch_phase(xs[r], routings[r], E, world, r, p, plan, bufs[d].data_ptr(), capacity,
+                                      dest_pos, flags[d].data_ptr() + 4 * p, epoch)
+            plans.append(plan)
+            poss.append(dest_pos)
+        for d in range(world):
+            assert flags[d][:world].cpu().tolist() == [epoch] * world
+            seg = plans[d]["segment_sizes"]
+            total = int(plans[d]["totals"].cpu())
+            got = bufs[d][:total].cpu()
+            off = 0
+            seg_np = seg.cpu().numpy()
+            for q in range(world):
+                s_rank = (d - q) % world
+                flat = routings[s_rank].cpu().reshape(-1)
+                pos = poss[s_rank].cpu().reshape(-1)
+                assert int(pos.min()) >= 0
+                for j in range(local):
+                    idx = (flat == d * local + j).nonzero().flatten()
+                    c = int(seg_np[q * local + j])
+                    assert len(idx) == c
+                    if c:
+                        pp = pos[idx]
+                        assert int(pp.min()) >= off and int(pp.max()) < off + c and len(set(pp.tolist())) == c
+                        assert torch.equal(got[pp.long()].view(torch.int16),
+                                           xs[s_rank].cpu()[idx // top_k].view(torch.int16))
+                    off += c
+            seg2e = torch.arange(local, dtype=torch.int32, device=DEV).repeat(world)
+            y = torch.full((capacity, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+            for tile_m in (128, 256) if n >= 256 else (128,):
+                cfg = _lib.TileCfg(0, 0, 1, tile_m, _lib.RD_CFG_NO_ZERO_TAIL)
+                ws = ops._workspace(capacity, E, DEV)
+                ops.gmm_forward(bufs[d], weights[d * local:(d + 1) * local], seg, group_to_weight=seg2e, cfg=cfg,
+                                out=y, workspace=ws, ready=(flags[d], local, epoch))
+                assert ops.device_status(ws) == 0
+                want = oracle.ragged_dot(got, weights[d * local:(d + 1) * local].cpu()[seg2e.cpu().long()], seg.cpu())
+                _assert_close(y[:total].cpu(), want, f"ep ring rank {d}")
+
+
+def test_flag_gated_gmm_256_row_tiles():
+    """rd_gmm_indexed_when_ready through the 256-row kernel, flags already up."""
+    m, k, n, g = 1500, 128, 512, 6
+    x, A, _ = _inputs(5, m, k, n, 3)
+    gs = torch.tensor([300, 0, 411, 256, 1, 500], dtype=torch.int32)
+    g2w = torch.tensor([0, 1, 2, 0, 1, 2], dtype=torch.int32)
+    flags = torch.tensor([3, 3, 3, 0], dtype=torch.int32, device=DEV)
+    cfg = _lib.TileCfg(256, 0, 1, 256, 0)
+    ws = ops._workspace(m, g, DEV)
+    y = ops.gmm_forward(x.to(DEV), A.to(DEV), gs.to(DEV), group_to_weight=g2w.to(DEV), cfg=cfg, workspace=ws,
+                        ready=(flags, 2, 3))
+    assert ops.device_status(ws) == 0
+    want = oracle.ragged_dot(x, A[g2w.long()], gs)
+    _assert_close(y.cpu(), want, "flag-gated 256-row")
+
+
 def test_expert_parallel_p2p_single_rank_matches_nccl_path():
     from gpu_ragged_dot_b200 import ep
 
