@@ -604,7 +604,7 @@ def run_expert_parallel(args):
     peaks = measured_peaks()
     results = {}
     clocks = None
-    for mode in ("nccl", "p2p", "overlap"):
+    for mode in ("nccl", "p2p", "overlap", "fused"):
         try:
             layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode)
             for _ in range(max(args.warmup, 3)):
@@ -655,7 +655,9 @@ def run_expert_parallel(args):
                                   "local_ragged_dot": g_ms} if m_ == "p2p" else
                                  {"count_allgather_plan": p_ms, "peer_store_phases_from_plan_end": x_ms,
                                   "own_rows_copied_from_plan_end": own_ms,
-                                  "flag_gated_ragged_dot_from_plan_end": g_ms}),
+                                  "flag_gated_ragged_dot_from_plan_end": g_ms} if m_ == "overlap" else
+                                 {"count_allgather_plan_assign": p_ms, "own_rows_copied_from_plan_end": own_ms,
+                                  "fused_send_and_ragged_dot_from_plan_end": g_ms}),
                 "exchange_GBps_per_gpu": row_bytes_out / (x_ms * 1e-3) / 1e9,
             }
         line = {
@@ -668,18 +670,23 @@ def run_expert_parallel(args):
                        "collective": {"nccl": "NCCL all-to-all (rows) + all-to-all (counts)",
                                       "p2p": "NCCL all-gather (counts) + peer stores over NVLink + symmetric-memory barrier",
                                       "overlap": "NCCL all-gather (counts) + ring-phased peer stores over NVLink overlapped "
-                                                 "with the local GEMM, which waits per source on ready flags"}[best],
+                                                 "with the local GEMM, which waits per source on ready flags",
+                                      "fused": "NCCL all-gather (counts) + ONE kernel whose sender CTAs store rows to the "
+                                               "peers over NVLink (ring phases) while its other CTAs multiply the rows "
+                                               "that have arrived (ready flags)"}[best],
                        "l2": "inputs larger than L2 (268 MB of rows per GPU)"},
             "clocks": clocks,
-            "gpu_launches": {"nccl": 3, "p2p": 5, "overlap": 4 + world}[best] * args.steps,
+            "gpu_launches": {"nccl": 3, "p2p": 5, "overlap": 4 + world, "fused": 6}[best] * args.steps,
             "roofline": ({"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> (local experts)",
                           "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                           "frac": gemm_tf / peaks["bf16_tflops"], "traffic": None,
-                          "peak_source": peaks["source"]} if best != "overlap" else
+                          "peak_source": peaks["source"]} if best not in ("overlap", "fused") else
                          # fused exchange + GEMM: target = slower of flops / GEMM peak and NVLink bytes / 770 GB/s
                          # (measured peer-copy bandwidth per direction per GPU); achieved is over the span from
                          # the end of the plan to the end of the GEMM, waits on remote rows included.
-                         {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> gated by ready flags + ep_dispatch_phase_kernel",
+                         {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> gated by ready flags, " +
+                                                      ("sender CTAs in the same launch" if best == "fused"
+                                                       else "ep_dispatch_phase_kernel on a side stream"),
                           "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                           "target_ms": max(2.0 * tokens * top_k * shape.k * shape.n / (peaks["bf16_tflops"] * 1e9),
                                            row_bytes_out / 770e9 * 1e3),

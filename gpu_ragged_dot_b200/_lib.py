@@ -35,6 +35,16 @@ class TileCfg(ctypes.Structure):
                 ("tile_m", ctypes.c_int32), ("flags", ctypes.c_int32)]
 
 
+class EpSend(ctypes.Structure):
+    """Mirror of ``rd_ep_send``."""
+
+    _fields_ = [("x_tokens", ctypes.c_void_p), ("send_index", ctypes.c_void_p), ("send_start", ctypes.c_void_p),
+                ("dest_pos", ctypes.c_void_p), ("phase_done", ctypes.c_void_p),
+                ("peer_base", ctypes.POINTER(ctypes.c_uint64)), ("peer_flags", ctypes.POINTER(ctypes.c_uint64)),
+                ("row_bytes", ctypes.c_int32), ("top_k", ctypes.c_int32), ("world", ctypes.c_int32),
+                ("rank", ctypes.c_int32), ("capacity_rows", ctypes.c_int32), ("sender_ctas", ctypes.c_int32)]
+
+
 SIGNATURES = {
     "rd_version": (_c_int, []),
     "rd_status_string": (ctypes.c_char_p, [_c_int]),
@@ -62,7 +72,17 @@ SIGNATURES = {
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
     "rd_ep_plan_ring": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                                 _c_void_p, _c_void_p]),
+                                 _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
+    "rd_ep_assign": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                              _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
+    "rd_ep_send_list": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
+                                 _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p]),
+    "rd_gmm_ep_fused": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p, _c_int, _c_int, ctypes.POINTER(EpSend), _c_void_p],
+    ),
     "rd_ep_dispatch_phase": (
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,

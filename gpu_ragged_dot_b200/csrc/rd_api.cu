@@ -325,7 +325,8 @@ struct ReadyFlags {
 static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
                     const int32_t* group_to_weight, int num_weights, void* y, void* workspace,
                     size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs, int dtype,
-                    const rd_tile_cfg* cfg, void* stream_v, ReadyFlags ready = {nullptr, 1, 0}) {
+                    const rd_tile_cfg* cfg, void* stream_v, ReadyFlags ready = {nullptr, 1, 0},
+                    const rd::EpSendArgs* send = nullptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16 && dtype != RD_DTYPE_F32) return RD_ERR_BAD_DTYPE;
   const bool f32 = dtype == RD_DTYPE_F32;
@@ -413,8 +414,13 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.ready_flags = ready.flags;
   args.groups_per_flag = ready.groups_per_flag > 0 ? ready.groups_per_flag : 1;
   args.ready_epoch = ready.epoch;
+  if (send != nullptr) {
+    if (f32 || cta_group == 2) return RD_ERR_BAD_CONFIG;  // the sender role lives in the 16-bit 1-CTA kernels
+    args.send = *send;
+  }
 
   const int ctas = pick_ctas(cfg);
+  if (send != nullptr && send->sender_ctas >= ctas) return RD_ERR_BAD_CONFIG;
   if (f32) {
     if (ready.flags != nullptr) return RD_ERR_BAD_DTYPE;  // the float32 kernels do not wait on flags
     if (trans_rhs) {
@@ -493,19 +499,60 @@ int rd_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, 
     return RD_ERR_BAD_SHAPE;
   if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals) return RD_ERR_BAD_POINTER;
   rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 0, nullptr);
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 0, nullptr, nullptr,
+      nullptr);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
 int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int rank,
                     int32_t* dest_offset, int32_t* segment_sizes, int32_t* fill, int32_t* totals,
-                    int32_t* phase_done, void* stream) {
+                    int32_t* phase_done, int32_t* send_start, int32_t* list_fill, void* stream) {
   if (world <= 0 || num_experts <= 0 || num_experts % world != 0 || rank < 0 || rank >= world)
     return RD_ERR_BAD_SHAPE;
   if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals || !phase_done)
     return RD_ERR_BAD_POINTER;
+  if ((send_start == nullptr) != (list_fill == nullptr)) return RD_ERR_BAD_POINTER;
   rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 1, phase_done);
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 1, phase_done,
+      send_start, list_fill);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_assign(const int32_t* routing, int entries, int num_experts, int world, int rank,
+                 const int32_t* dest_offset, int32_t* fill, int capacity_rows, int32_t* dest_pos,
+                 const int32_t* send_start, int32_t* list_fill, int32_t* send_index, void* stream) {
+  if (entries < 0 || world <= 0 || num_experts <= 0 || num_experts % world != 0 || rank < 0 ||
+      rank >= world || capacity_rows < 0)
+    return RD_ERR_BAD_SHAPE;
+  if (entries == 0) return RD_OK;
+  if (!routing || !dest_offset || !fill || !dest_pos || !send_start || !list_fill || !send_index)
+    return RD_ERR_BAD_POINTER;
+  int blocks = (entries + rd::kEpThreads - 1) / rd::kEpThreads;
+  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+  rd::ep_assign_kernel<<<blocks, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      routing, entries, num_experts, num_experts / world, world, rank, dest_offset, fill, capacity_rows,
+      dest_pos, send_start, list_fill, send_index);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_send_list(const void* x, int top_k, int row_bytes, const int32_t* send_index,
+                    const int32_t* send_start, int phase, int world, int max_rows,
+                    const int32_t* dest_pos, void* dest_base, int capacity_rows, int32_t* phase_done,
+                    int32_t* dest_ready_flag, int epoch, void* stream) {
+  if (top_k <= 0 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 || phase < 0 || phase >= world ||
+      max_rows < 0 || capacity_rows < 0)
+    return RD_ERR_BAD_SHAPE;
+  if (!aligned16(dest_base) || !send_index || !send_start || !dest_pos || !phase_done ||
+      !dest_ready_flag || (max_rows > 0 && !aligned16(x)))
+    return RD_ERR_BAD_POINTER;
+  const int warps_per_block = rd::kEpThreads / 32;
+  int blocks = (max_rows + warps_per_block - 1) / warps_per_block;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;  // the flag is raised even when the list is empty
+  rd::ep_send_list_kernel<<<blocks, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), top_k, row_bytes / 16, send_index, send_start, phase, dest_pos,
+      static_cast<uint4*>(dest_base), capacity_rows, phase_done, dest_ready_flag, epoch);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -836,6 +883,43 @@ int rd_tgmm_permuted(const void* x, int x_rows, const int32_t* x_row_index, cons
   if (bn == 256) return launch_gemm_perm<256, false, true>(ta, tb, tout, args, perm, ctas, stream);
   if (bn == 128) return launch_gemm_perm<128, false, true>(ta, tb, tout, args, perm, ctas, stream);
   return launch_gemm_perm<64, false, true>(ta, tb, tout, args, perm, ctas, stream);
+}
+
+int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                    const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                    int m, int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
+                    const int32_t* ready_flags, int groups_per_flag, int epoch, const rd_ep_send* send,
+                    void* stream) {
+  if (g > 0 && group_to_weight == nullptr) return RD_ERR_BAD_POINTER;
+  if (ready_flags == nullptr || send == nullptr) return RD_ERR_BAD_POINTER;
+  if (groups_per_flag <= 0 || send->world <= 0 || send->world > rd::kEpMaxWorld || send->rank < 0 ||
+      send->rank >= send->world || send->row_bytes <= 0 || (send->row_bytes & 15) || send->top_k <= 0 ||
+      send->sender_ctas <= 0 || send->capacity_rows < 0)
+    return RD_ERR_BAD_SHAPE;
+  if (m == 0 || n == 0 || g == 0 || k == 0) return RD_ERR_BAD_SHAPE;  // the sender role needs a launch
+  if (!aligned16(send->x_tokens) || !send->send_index || !send->send_start || !send->dest_pos ||
+      !send->phase_done || !send->peer_base || !send->peer_flags)
+    return RD_ERR_BAD_POINTER;
+  rd::EpSendArgs a = {};
+  a.x = static_cast<const uint8_t*>(send->x_tokens);
+  a.send_index = send->send_index;
+  a.send_start = send->send_start;
+  a.dest_pos = send->dest_pos;
+  a.phase_done = send->phase_done;
+  for (int r = 0; r < send->world; ++r) {
+    if ((send->peer_base[r] & 15u) || send->peer_base[r] == 0 || send->peer_flags[r] == 0)
+      return RD_ERR_BAD_POINTER;
+    a.peer_base[r] = send->peer_base[r];
+    a.peer_flags[r] = send->peer_flags[r];
+  }
+  a.row_bytes = send->row_bytes;
+  a.top_k = send->top_k;
+  a.world = send->world;
+  a.rank = send->rank;
+  a.capacity_rows = send->capacity_rows;
+  a.sender_ctas = send->sender_ctas;
+  return gmm_impl(x, A, group_sizes, group_to_weight, num_weights, y, workspace, workspace_bytes, m, k,
+                  n, g, trans_rhs, dtype, cfg, stream, ReadyFlags{ready_flags, groups_per_flag, epoch}, &a);
 }
 
 int rd_device_status(const void* workspace, void* stream) {

@@ -53,7 +53,8 @@ __global__ void __launch_bounds__(kEpThreads)
 ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int num_experts, int rank,
                int32_t* __restrict__ dest_offset, int32_t* __restrict__ segment_sizes,
                int32_t* __restrict__ fill, int32_t* __restrict__ totals, int ring,
-               int32_t* __restrict__ phase_done) {
+               int32_t* __restrict__ phase_done, int32_t* __restrict__ send_start,
+               int32_t* __restrict__ list_fill) {
   const int local = num_experts / world;
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     const int owner = e / local;
@@ -77,6 +78,19 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int num_expert
   }
   if (phase_done != nullptr)
     for (int i = threadIdx.x; i < world; i += blockDim.x) phase_done[i] = 0;
+  // Send lists (fused exchange): list positions [send_start[p], send_start[p+1]) hold the entries
+  // this rank sends in phase p, i.e. to rank + p; list_fill[p] counts them as they are assigned.
+  if (list_fill != nullptr)
+    for (int i = threadIdx.x; i < world; i += blockDim.x) list_fill[i] = 0;
+  if (send_start != nullptr && threadIdx.x == 0) {
+    int acc = 0;
+    for (int p = 0; p < world; ++p) {
+      send_start[p] = acc;
+      const int dest = (rank + p) % world;
+      for (int j = 0; j < local; ++j) acc += counts_all[rank * num_experts + dest * local + j];
+    }
+    send_start[world] = acc;
+  }
   if (threadIdx.x == 0) {
     int total = 0;
     for (int s = 0; s < world; ++s)
@@ -177,6 +191,87 @@ ep_dispatch_phase_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
     if (done == static_cast<int>(gridDim.x)) {
       // Every block has fenced its stores before its increment; order this thread's flag store
       // after having seen them all.
+      __threadfence_system();
+      *reinterpret_cast<volatile int32_t*>(ready_flag) = epoch;
+      __threadfence_system();
+    }
+  }
+}
+
+// Fused exchange, step 1: one thread per (token, slot) entry.  Assigns the row its position at
+// the expert's owner (dest_pos, as ep_dispatch_kernel does) and appends the entry to the send
+// list of its phase p = (owner - rank) mod W.  Appends are aggregated per warp and phase.
+__global__ void __launch_bounds__(kEpThreads)
+ep_assign_kernel(const int32_t* __restrict__ routing, int entries, int num_experts,
+                 int experts_per_rank, int world, int rank, const int32_t* __restrict__ dest_offset,
+                 int32_t* __restrict__ fill, int capacity_rows, int32_t* __restrict__ dest_pos,
+                 const int32_t* __restrict__ send_start, int32_t* __restrict__ list_fill,
+                 int32_t* __restrict__ send_index) {
+  const int lane = threadIdx.x & 31;
+  const int base = blockIdx.x * blockDim.x;
+  for (int i0 = base; i0 < entries; i0 += gridDim.x * blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    int phase = -1;
+    if (i < entries) {
+      const int e = routing[i];
+      if (e >= 0 && e < num_experts) {
+        int pos = dest_offset[e] + atomicAdd(&fill[e], 1);
+        if (pos >= capacity_rows) pos = -1;
+        dest_pos[i] = pos;
+        phase = (e / experts_per_rank - rank + world) % world;
+      } else {
+        dest_pos[i] = -1;
+      }
+    }
+    // One atomic per distinct phase in the warp; every lane takes its place behind the leader's.
+    const unsigned active = __ballot_sync(0xffffffffu, phase >= 0);
+    if (phase >= 0) {
+      const unsigned peers = __match_any_sync(active, phase);
+      const int leader = __ffs(peers) - 1;
+      int first = 0;
+      if (lane == leader) first = atomicAdd(&list_fill[phase], __popc(peers));
+      first = __shfl_sync(peers, first, leader);
+      const int rank_in = __popc(peers & ((1u << lane) - 1u));
+      send_index[send_start[phase] + first + rank_in] = i;
+    }
+  }
+}
+
+// Copies the rows of one phase's send list (one warp per row) into dest_base and raises the
+// destination's flag when the last block is done.  Used for phase 0 (a rank's own rows, a local
+// copy that runs before the fused kernel).
+__global__ void __launch_bounds__(kEpThreads)
+ep_send_list_kernel(const uint4* __restrict__ x, int top_k, int vecs_per_row,
+                    const int32_t* __restrict__ send_index, const int32_t* __restrict__ send_start,
+                    int phase, const int32_t* __restrict__ dest_pos, uint4* __restrict__ dest_base,
+                    int capacity_rows, int32_t* __restrict__ phase_done, int32_t* ready_flag,
+                    int epoch) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kEpThreads / 32;
+  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * warps_per_block;
+  const int lo = send_start[phase], hi = send_start[phase + 1];
+  for (int j = lo + warp_global; j < hi; j += warp_stride) {
+    const int i = send_index[j];
+    const int pos = dest_pos[i];
+    if (pos < 0 || pos >= capacity_rows) continue;
+    const uint4* src = x + static_cast<size_t>(i / top_k) * vecs_per_row;
+    uint4* dst = dest_base + static_cast<size_t>(pos) * vecs_per_row;
+    int v = lane;
+    for (; v + 96 < vecs_per_row; v += 128) {
+      const uint4 a = src[v], b = src[v + 32], c = src[v + 64], d = src[v + 96];
+      dst[v] = a;
+      dst[v + 32] = b;
+      dst[v + 64] = c;
+      dst[v + 96] = d;
+    }
+    for (; v < vecs_per_row; v += 32) dst[v] = src[v];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(phase_done + phase, 1) + 1;
+    if (done == static_cast<int>(gridDim.x)) {
       __threadfence_system();
       *reinterpret_cast<volatile int32_t*>(ready_flag) = epoch;
       __threadfence_system();

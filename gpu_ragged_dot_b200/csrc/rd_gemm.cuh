@@ -37,6 +37,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "rd_ep_send.cuh"
 #include "rd_metadata.cuh"
 #include "rd_ptx.cuh"
 
@@ -90,6 +91,9 @@ struct GemmArgs {
   const int32_t* ready_flags;
   int groups_per_flag;
   int ready_epoch;
+  // gmm on one CTA per tile, optional (send.world > 0): the first send.sender_ctas CTAs of the
+  // grid run the expert-parallel sender role (rd_ep_send.cuh) instead of multiplying.
+  EpSendArgs send;
 };
 
 // Coordinates of one CTA's share of a tile.
@@ -211,7 +215,8 @@ template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b,
-                   const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
+                   const __grid_constant__ CUtensorMap tmap_out,
+                   const __grid_constant__ GemmArgs p) {
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
   static_assert(kCtas == 1 || (kCtas == 2 && BN >= 128), "a CTA pair needs BN >= 128");
@@ -236,6 +241,18 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int cta_rank = kPair ? static_cast<int>(cluster_cta_rank()) : 0;
   const bool leader = cta_rank == 0;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+
+  // Fused expert-parallel exchange: some CTAs of the grid send rows instead of multiplying.
+  const int sender_ctas = (!kTgmm && !kPair && p.send.world > 0) ? p.send.sender_ctas : 0;
+  const int gemm_ctas = static_cast<int>(gridDim.x) - sender_ctas;
+  // The senders are the FIRST CTAs of the grid, so they are resident before any CTA that may wait
+  // for another GPU's senders.
+  if (static_cast<int>(blockIdx.x) < sender_ctas) {
+    ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &abort_flag,
+                   p.status);
+    return;
+  }
+  const int cta_index = static_cast<int>(blockIdx.x) - sender_ctas;  // among the multiplying CTAs
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -270,8 +287,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     num_tiles = imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
   }
-  const int tile_start = static_cast<int>(blockIdx.x) / kCtas;
-  const int tile_step = static_cast<int>(gridDim.x) / kCtas;
+  const int tile_start = cta_index / kCtas;
+  const int tile_step = gemm_ctas / kCtas;
   const int k_blocks_gmm = (p.k + kTileK - 1) / kTileK;
 
   if (warp == 0) {
@@ -615,8 +632,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int first = imin(imax(p.totals[1], 0), p.m);
       const size_t chunks_per_row = static_cast<size_t>(p.n) / 8;
       const size_t total = static_cast<size_t>(p.m - first) * chunks_per_row;
-      const size_t tid = static_cast<size_t>(blockIdx.x) * 128 + (threadIdx.x - 64);
-      const size_t stride = static_cast<size_t>(gridDim.x) * 128;
+      const size_t tid = static_cast<size_t>(cta_index) * 128 + (threadIdx.x - 64);
+      const size_t stride = static_cast<size_t>(gemm_ctas) * 128;
       uint4* dst = reinterpret_cast<uint4*>(out16 + static_cast<size_t>(first) * p.n);
       const uint4 z = make_uint4(0u, 0u, 0u, 0u);
       for (size_t i = tid; i < total; i += stride) dst[i] = z;

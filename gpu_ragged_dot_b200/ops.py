@@ -293,7 +293,7 @@ def ep_dispatch(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world:
 def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = None) -> dict:
     """``rd_ep_plan_ring``: the plan of the overlapped exchange (receive buffer ordered by position
     q = (rank - source) mod W).  Returns / refills a dict with dest_offset[E], segment_sizes[E],
-    fill[E], totals[1], phase_done[W]."""
+    fill[E], totals[1], phase_done[W], send_start[W+1], list_fill[W]."""
     lib = _lib.load()
     assert counts_all.dim() == 2 and counts_all.dtype == torch.int32 and counts_all.is_contiguous()
     world, experts = counts_all.shape
@@ -301,11 +301,13 @@ def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = Non
     if bufs is None:
         bufs = {name: torch.empty(size, dtype=torch.int32, device=dev)
                 for name, size in (("dest_offset", experts), ("segment_sizes", experts), ("fill", experts),
-                                   ("totals", 1), ("phase_done", world))}
+                                   ("totals", 1), ("phase_done", world), ("send_start", world + 1),
+                                   ("list_fill", world))}
     with torch.cuda.device(dev):
         rc = lib.rd_ep_plan_ring(counts_all.data_ptr(), world, experts, rank, bufs["dest_offset"].data_ptr(),
                                  bufs["segment_sizes"].data_ptr(), bufs["fill"].data_ptr(),
-                                 bufs["totals"].data_ptr(), bufs["phase_done"].data_ptr(), _stream_ptr(dev))
+                                 bufs["totals"].data_ptr(), bufs["phase_done"].data_ptr(),
+                                 bufs["send_start"].data_ptr(), bufs["list_fill"].data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "rd_ep_plan_ring")
     return bufs
 
@@ -327,6 +329,55 @@ def ep_dispatch_phase(x: torch.Tensor, routing: torch.Tensor, num_experts: int, 
             dest_pos.data_ptr(), plan["phase_done"].data_ptr(), dest_ready_flag, epoch, max_blocks,
             _stream_ptr(x.device))
     _lib.check(rc, "rd_ep_dispatch_phase")
+
+
+def ep_assign(routing: torch.Tensor, num_experts: int, world: int, rank: int, plan: dict, capacity_rows: int,
+              dest_pos: torch.Tensor, send_index: torch.Tensor) -> None:
+    """``rd_ep_assign``: positions at the owners (dest_pos) and the per-phase send lists."""
+    lib = _lib.load()
+    assert routing.dtype == torch.int32 and routing.is_contiguous() and routing.is_cuda
+    entries = routing.numel()
+    assert dest_pos.numel() >= entries and send_index.numel() >= entries
+    with torch.cuda.device(routing.device):
+        rc = lib.rd_ep_assign(routing.data_ptr(), entries, num_experts, world, rank, plan["dest_offset"].data_ptr(),
+                              plan["fill"].data_ptr(), capacity_rows, dest_pos.data_ptr(),
+                              plan["send_start"].data_ptr(), plan["list_fill"].data_ptr(), send_index.data_ptr(),
+                              _stream_ptr(routing.device))
+    _lib.check(rc, "rd_ep_assign")
+
+
+def ep_send_list(x: torch.Tensor, top_k: int, send_index: torch.Tensor, plan: dict, phase: int, world: int,
+                 dest_pos: torch.Tensor, dest_base: int, capacity_rows: int, dest_ready_flag: int, epoch: int) -> None:
+    """``rd_ep_send_list``: copy one phase's rows with an ordinary kernel and raise the flag."""
+    lib = _lib.load()
+    assert x.is_contiguous() and x.is_cuda
+    with torch.cuda.device(x.device):
+        rc = lib.rd_ep_send_list(x.data_ptr(), top_k, x.shape[1] * x.element_size(), send_index.data_ptr(),
+                                 plan["send_start"].data_ptr(), phase, world, send_index.numel(), dest_pos.data_ptr(),
+                                 dest_base, capacity_rows, plan["phase_done"].data_ptr(), dest_ready_flag, epoch,
+                                 _stream_ptr(x.device))
+    _lib.check(rc, "rd_ep_send_list")
+
+
+def gmm_ep_fused(recv: torch.Tensor, A: torch.Tensor, segment_sizes: torch.Tensor, group_to_weight: torch.Tensor,
+                 out: torch.Tensor, workspace: torch.Tensor, flags: torch.Tensor, groups_per_flag: int, epoch: int,
+                 send: "_lib.EpSend", cfg: Optional[_lib.TileCfg] = None) -> torch.Tensor:
+    """``rd_gmm_ep_fused``: the flag-gated local ragged_dot over the receive buffer, with the last
+    ``send.sender_ctas`` CTAs of the same launch sending this rank's rows to the other ranks."""
+    lib = _lib.load()
+    m, k = recv.shape
+    g = segment_sizes.numel()
+    n = A.shape[-1]
+    assert recv.is_contiguous() and A.is_contiguous() and out.shape == (m, n) and out.is_contiguous()
+    assert k % 8 == 0 and n % 8 == 0 and recv.dtype == A.dtype == out.dtype
+    with torch.cuda.device(recv.device):
+        rc = lib.rd_gmm_ep_fused(
+            recv.data_ptr(), A.data_ptr(), A.shape[0], segment_sizes.data_ptr(), group_to_weight.data_ptr(),
+            out.data_ptr(), workspace.data_ptr(), workspace.numel(), m, k, n, g, 0, _DTYPE_CODE[recv.dtype],
+            _cfg_ptr(cfg), flags.data_ptr(), int(groups_per_flag), int(epoch), ctypes.byref(send),
+            _stream_ptr(recv.device))
+    _lib.check(rc, "rd_gmm_ep_fused")
+    return out
 
 
 def tgmm_forward(

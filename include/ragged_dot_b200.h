@@ -154,7 +154,7 @@ int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k,
  * after the GEMM in stream order).  Plain peer stores and loads of flags only. */
 int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int rank,
                     int32_t* dest_offset, int32_t* segment_sizes, int32_t* fill, int32_t* totals,
-                    int32_t* phase_done, void* stream);
+                    int32_t* phase_done, int32_t* send_start, int32_t* list_fill, void* stream);
 int rd_ep_dispatch_phase(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
                          int num_experts, int world, int rank, int phase, const int32_t* dest_offset,
                          int32_t* fill, void* dest_base, int capacity_rows, int32_t* dest_pos,
@@ -165,6 +165,43 @@ int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, con
                               size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs,
                               int dtype, const rd_tile_cfg* cfg, const int32_t* ready_flags,
                               int groups_per_flag, int epoch, void* stream);
+
+/* The same exchange with the sending done INSIDE the GEMM kernel (one launch does both): 
+ * `sender_ctas` CTAs of the persistent grid push this rank's rows of phases 1 .. world-1 to
+ * their owners (bulk async copies global -> shared, plain stores shared -> peer memory, then the
+ * owner's ready flag), the other CTAs multiply the positions that have arrived.
+ *   rd_ep_plan_ring  with send_start[world + 1] and list_fill[world] (both non-NULL) also sizes the
+ *                    per-phase send lists;
+ *   rd_ep_assign     dest_pos[i] for every (token, slot) entry and the send lists: entries of phase
+ *                    p at send_index[send_start[p] .. send_start[p+1]);
+ *   rd_ep_send_list  copies one phase's list with an ordinary kernel and raises the flag; used for
+ *                    phase 0 (the rank's own rows), before the fused launch; max_rows bounds the
+ *                    list length for the grid size;
+ *   rd_gmm_ep_fused  rd_gmm_indexed_when_ready + the sender role.  peer_base[r] / peer_flags[r]
+ *                    (host arrays of `world` addresses) are rank r's receive buffer and flag array
+ *                    as seen from this GPU.  16-bit types, one CTA per tile (cta_group != 2). */
+typedef struct rd_ep_send {
+  const void* x_tokens;        /* [tokens, row_bytes] */
+  const int32_t* send_index;   /* from rd_ep_assign */
+  const int32_t* send_start;   /* from rd_ep_plan_ring */
+  const int32_t* dest_pos;     /* from rd_ep_assign */
+  int32_t* phase_done;         /* [world], reset by rd_ep_plan_ring */
+  const uint64_t* peer_base;   /* host array [world] */
+  const uint64_t* peer_flags;  /* host array [world] */
+  int32_t row_bytes, top_k, world, rank, capacity_rows, sender_ctas;
+} rd_ep_send;
+int rd_ep_assign(const int32_t* routing, int entries, int num_experts, int world, int rank,
+                 const int32_t* dest_offset, int32_t* fill, int capacity_rows, int32_t* dest_pos,
+                 const int32_t* send_start, int32_t* list_fill, int32_t* send_index, void* stream);
+int rd_ep_send_list(const void* x, int top_k, int row_bytes, const int32_t* send_index,
+                    const int32_t* send_start, int phase, int world, int max_rows,
+                    const int32_t* dest_pos, void* dest_base, int capacity_rows, int32_t* phase_done,
+                    int32_t* dest_ready_flag, int epoch, void* stream);
+int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+                    const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                    int m, int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
+                    const int32_t* ready_flags, int groups_per_flag, int epoch, const rd_ep_send* send,
+                    void* stream);
 
 /* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
  * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass

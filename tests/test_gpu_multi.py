@@ -33,7 +33,7 @@ def _worker(rank, world, port, out_dir):
     x = workloads.normal_tensor((T, k), 1.0, 1000 + rank, dev)
     routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=3000 + rank)).to(dev)
     res = {"x": x.cpu(), "routing": routing.cpu()}
-    for mode in ("nccl", "p2p", "overlap"):
+    for mode in ("nccl", "p2p", "overlap", "fused"):
         layer = ep.ExpertParallelRaggedDot(E, k, n, dev, seed=2000 + rank, dispatch=mode)
         for step in range(3):  # several steps: the later ones reuse the receive buffer (and flags)
             out = layer.forward(x, routing)
@@ -41,10 +41,10 @@ def _worker(rank, world, port, out_dir):
         if mode == "nccl":
             y, plan = out
             res["nccl"] = {"y": y.cpu(), "seg": plan.segment_sizes.cpu()}
-        elif mode == "overlap":
+        elif mode in ("overlap", "fused"):
             from gpu_ragged_dot_b200 import ops
             y, seg, dest_pos, totals = out
-            res["overlap"] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu(),
+            res[mode] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu(),
                               "status": ops.device_status(layer._ov["ws"]),
                               "flags": layer._ov["flags"][:world].cpu()}
         else:
@@ -90,23 +90,24 @@ def test_expert_parallel_two_gpus(tmp_path):
                 assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
                 assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
                 off += len(idx)
-        # overlapped mode: receive buffer ordered by position q = (d - source) mod W
-        ov = res[d]["overlap"]
-        assert ov["status"] == 0, "a bounded wait expired on the device"
-        assert ov["flags"].tolist() == [3] * world  # third step's epoch on every position
-        off = 0
-        seg_ring = []
-        for q in range(world):
-            s = (d - q) % world
-            flat = res[s]["routing"].reshape(-1)
-            for j in range(local):
-                idx = (flat == d * local + j).nonzero().flatten()
-                seg_ring.append(len(idx))
-                if len(idx):
-                    rows = res[s]["x"][idx // top_k].float()
-                    want = (rows @ w[j]).to(torch.bfloat16).float()
-                    pos = res[s]["overlap"]["pos"].reshape(-1)[idx].long()
-                    assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
-                    assert torch.allclose(ov["y"][pos].float(), want, rtol=2e-2, atol=2e-2)
-                off += len(idx)
-        assert ov["seg"].tolist() == seg_ring
+        for mode in ("overlap", "fused"):
+            # overlapped modes: receive buffer ordered by position q = (d - source) mod W
+            ov = res[d][mode]
+            assert ov["status"] == 0, "a bounded wait expired on the device"
+            assert ov["flags"].tolist() == [3] * world  # third step's epoch on every position
+            off = 0
+            seg_ring = []
+            for q in range(world):
+                s = (d - q) % world
+                flat = res[s]["routing"].reshape(-1)
+                for j in range(local):
+                    idx = (flat == d * local + j).nonzero().flatten()
+                    seg_ring.append(len(idx))
+                    if len(idx):
+                        rows = res[s]["x"][idx // top_k].float()
+                        want = (rows @ w[j]).to(torch.bfloat16).float()
+                        pos = res[s][mode]["pos"].reshape(-1)[idx].long()
+                        assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
+                        assert torch.allclose(ov["y"][pos].float(), want, rtol=2e-2, atol=2e-2)
+                    off += len(idx)
+            assert ov["seg"].tolist() == seg_ring

@@ -548,6 +548,57 @@ def test_ep_ring_phases_emulated_ranks(world):
                 _assert_close(y[:total].cpu(), want, f"ep ring rank {d}")
 
 
+def test_ep_assign_send_lists_and_fused_single_rank():
+    """Fused exchange on one rank: assign + own-row copy + rd_gmm_ep_fused (whose sender CTAs have
+    nothing to send when world == 1), checked against the NCCL-free reference path."""
+    from gpu_ragged_dot_b200 import ep
+
+    E, k, n, T, top_k = 16, 128, 264, 300, 4
+    x = workloads.normal_tensor((T, k), 1.0, 77, DEV)
+    routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=9)).to(DEV)
+    a = ep.ExpertParallelRaggedDot(E, k, n, torch.device(DEV), seed=5)
+    b = ep.ExpertParallelRaggedDot(E, k, n, torch.device(DEV), seed=5, dispatch="fused")
+    ya, plan = a.forward(x, routing)
+    for step in range(2):
+        yb, seg, dest_pos, totals = b.forward(x, routing)
+    assert ops.device_status(b._ov["ws"]) == 0
+    assert int(totals.cpu()) == T * top_k and seg.cpu().tolist() == plan.segment_sizes.cpu().tolist()
+    order = torch.sort(routing.reshape(-1).cpu().long(), stable=True).indices
+    pos = dest_pos.reshape(-1).cpu().long()
+    assert sorted(pos.tolist()) == list(range(T * top_k))
+    _assert_close(yb.cpu()[pos[order]], ya.cpu(), "fused vs nccl path")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_assign_send_lists_emulated_ranks(world):
+    """rd_ep_plan_ring + rd_ep_assign for W emulated ranks: every phase's send list holds exactly the
+    entries routed to rank + p, and positions at the owners are a permutation of each segment."""
+    E, T, top_k = 16, 200, 4
+    local = E // world
+    capacity = T * top_k * world
+    routings = [torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=40 + r)).to(DEV) for r in range(world)]
+    counts_all = torch.stack([ops.ep_count(routings[r], E) for r in range(world)]).contiguous()
+    for r in range(world):
+        plan = ops.ep_plan_ring(counts_all, r)
+        dest_pos = torch.full((T * top_k,), -9, dtype=torch.int32, device=DEV)
+        send_index = torch.full((T * top_k,), -9, dtype=torch.int32, device=DEV)
+        ops.ep_assign(routings[r].to(torch.int32).contiguous(), E, world, r, plan, capacity, dest_pos, send_index)
+        flat = routings[r].cpu().reshape(-1).numpy()
+        start = plan["send_start"].cpu().numpy()
+        idx = send_index.cpu().numpy()
+        pos = dest_pos.cpu().numpy()
+        off = plan["dest_offset"].cpu().numpy()
+        assert start[0] == 0 and start[world] == T * top_k
+        for p in range(world):
+            d = (r + p) % world
+            want = np.nonzero((flat // local) == d)[0]
+            got = np.sort(idx[start[p]:start[p + 1]])
+            assert np.array_equal(got, want)
+        for e in range(E):
+            mine = np.nonzero(flat == e)[0]
+            assert sorted(pos[mine].tolist()) == list(range(off[e], off[e] + len(mine)))
+
+
 def test_flag_gated_gmm_256_row_tiles():
     """rd_gmm_indexed_when_ready through the 256-row kernel, flags already up."""
     m, k, n, g = 1500, 128, 512, 6
