@@ -40,7 +40,7 @@ class EpSend(ctypes.Structure):
 
     _fields_ = [("x_tokens", ctypes.c_void_p), ("send_index", ctypes.c_void_p), ("send_start", ctypes.c_void_p),
                 ("dest_pos", ctypes.c_void_p), ("phase_done", ctypes.c_void_p),
-                ("peer_base", ctypes.POINTER(ctypes.c_uint64)), ("peer_flags", ctypes.POINTER(ctypes.c_uint64)),
+                ("peer_base", ctypes.c_void_p), ("peer_flags", ctypes.c_void_p),
                 ("row_bytes", ctypes.c_int32), ("top_k", ctypes.c_int32), ("world", ctypes.c_int32),
                 ("rank", ctypes.c_int32), ("capacity_rows", ctypes.c_int32), ("sender_ctas", ctypes.c_int32)]
 

@@ -221,10 +221,15 @@ int encode_rows_map(CUtensorMap* map, const void* base, int dtype, int cols, int
   return encode_map(map, base, dtype, 2, dims, box);
 }
 
-template <bool kBKMajor, bool kTgmm>
+template <bool kBKMajor, bool kTgmm, bool kEp = false>
 int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
                  const GemmArgs& args, int ctas, cudaStream_t stream) {
-  auto kernel = rd::ragged_gemm2_kernel<kBKMajor, kTgmm>;
+  if constexpr (!kTgmm && !kEp) {
+    // ready flags / sender CTAs live in a separate instantiation (see rd_gemm2.cuh)
+    if (args.ready_flags != nullptr || args.send.world > 0)
+      return launch_gemm2<kBKMajor, false, true>(ta, tb, tout, args, ctas, stream);
+  }
+  auto kernel = rd::ragged_gemm2_kernel<kBKMajor, kTgmm, kEp>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rd::kG2SmemBytes) !=
       cudaSuccess)
     return RD_ERR_LAUNCH;
@@ -892,7 +897,7 @@ int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t
                     void* stream) {
   if (g > 0 && group_to_weight == nullptr) return RD_ERR_BAD_POINTER;
   if (ready_flags == nullptr || send == nullptr) return RD_ERR_BAD_POINTER;
-  if (groups_per_flag <= 0 || send->world <= 0 || send->world > rd::kEpMaxWorld || send->rank < 0 ||
+  if (groups_per_flag <= 0 || send->world <= 0 || send->rank < 0 ||
       send->rank >= send->world || send->row_bytes <= 0 || (send->row_bytes & 15) || send->top_k <= 0 ||
       send->sender_ctas <= 0 || send->capacity_rows < 0)
     return RD_ERR_BAD_SHAPE;
@@ -906,12 +911,8 @@ int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t
   a.send_start = send->send_start;
   a.dest_pos = send->dest_pos;
   a.phase_done = send->phase_done;
-  for (int r = 0; r < send->world; ++r) {
-    if ((send->peer_base[r] & 15u) || send->peer_base[r] == 0 || send->peer_flags[r] == 0)
-      return RD_ERR_BAD_POINTER;
-    a.peer_base[r] = send->peer_base[r];
-    a.peer_flags[r] = send->peer_flags[r];
-  }
+  a.peer_base = send->peer_base;
+  a.peer_flags = send->peer_flags;
   a.row_bytes = send->row_bytes;
   a.top_k = send->top_k;
   a.world = send->world;

@@ -20,7 +20,6 @@
 
 namespace rd {
 
-constexpr int kEpMaxWorld = 16;
 constexpr int kEpChunkBytes = 4096;  // bytes per bulk copy / slot
 constexpr int kEpSlots = 4;          // slots per warp: three copies in flight while one is stored
 
@@ -30,8 +29,8 @@ struct EpSendArgs {
   const int32_t* send_start;  // [world + 1] first list position of each phase
   const int32_t* dest_pos;    // [tokens * top_k] row position at the owner (-1: dropped)
   int32_t* phase_done;        // [world] warps that have finished a phase (reset by the plan)
-  uint64_t peer_base[kEpMaxWorld];   // receive buffer of rank r as seen from this GPU
-  uint64_t peer_flags[kEpMaxWorld];  // ready-flag array of rank r as seen from this GPU
+  const uint64_t* peer_base;   // [world] device array: receive buffer of rank r as seen from this GPU
+  const uint64_t* peer_flags;  // [world] device array: ready-flag array of rank r as seen from this GPU
   int row_bytes, top_k, world, rank, capacity_rows, sender_ctas;  // world == 0: no sender role
 };
 
@@ -44,7 +43,7 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 
 // Runs on every thread of a sender CTA.  smem: 1024-byte aligned shared window of at least
 // warps * (kEpSlots * kEpChunkBytes + 64) bytes.
-__device__ __noinline__ void ep_sender_role(const EpSendArgs& a, int epoch, int sender, uint32_t smem,
+__device__ __noinline__ void ep_sender_role(const EpSendArgs a, int epoch, int sender, uint32_t smem,
                                             volatile int* abort_flag, int32_t* status) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

@@ -215,8 +215,7 @@ template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b,
-                   const __grid_constant__ CUtensorMap tmap_out,
-                   const __grid_constant__ GemmArgs p) {
+                   const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
   static_assert(kCtas == 1 || (kCtas == 2 && BN >= 128), "a CTA pair needs BN >= 128");

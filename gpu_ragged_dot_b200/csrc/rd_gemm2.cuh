@@ -69,12 +69,14 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int 
   return t;
 }
 
-template <bool kBKMajor, bool kTgmm>
+// kEp: the expert-parallel variant (ready flags in the loader, sender CTAs in the grid).  It is a
+// separate instantiation because this kernel's main loop is sensitive to code generation: merely
+// routing the tile loops through `cta_index` / `gemm_ctas` variables cost the plain kernel 3-5 %.
+template <bool kBKMajor, bool kTgmm, bool kEp = false>
 __global__ void __launch_bounds__(kG2Threads, 1)
 ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_out,
-                   const __grid_constant__ GemmArgs p) {
+                    const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
   constexpr int BN = kG2TileN;
   constexpr int kStages = kG2Stages;
@@ -93,17 +95,19 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
 
+  static_assert(!(kEp && kTgmm), "the expert-parallel variant is a gmm kernel");
   // Fused expert-parallel exchange: some CTAs of the grid send rows instead of multiplying.
-  const int sender_ctas = (!kTgmm && p.send.world > 0) ? p.send.sender_ctas : 0;
-  const int gemm_ctas = static_cast<int>(gridDim.x) - sender_ctas;
   // The senders are the FIRST CTAs of the grid, so they are resident before any CTA that may wait
   // for another GPU's senders.
-  if (static_cast<int>(blockIdx.x) < sender_ctas) {
-    ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &abort_flag,
-                   p.status);
-    return;
+  int sender_ctas = 0;
+  if constexpr (kEp) {
+    sender_ctas = p.send.world > 0 ? p.send.sender_ctas : 0;
+    if (static_cast<int>(blockIdx.x) < sender_ctas) {
+      ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &abort_flag,
+                     p.status);
+      return;
+    }
   }
-  const int cta_index = static_cast<int>(blockIdx.x) - sender_ctas;  // among the multiplying CTAs
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -133,7 +137,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles =
       kTgmm ? p.g * p.k_tiles * p.n_tiles : imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
   const int k_blocks_gmm = (p.k + kTileK - 1) / kTileK;
-  const int tile_step = gemm_ctas;
+  const int tile_step = kEp ? static_cast<int>(gridDim.x) - sender_ctas : static_cast<int>(gridDim.x);
 
   // Number of 128-row halves of a tile that exist.
   auto halves_of = [&](const TileCoord& t) -> int {
@@ -147,11 +151,11 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t it = 0;
       bool ok = true;
       int ready_slot = -1;  // last ready flag this producer has seen set
-      for (int tile = cta_index; tile < num_tiles && ok; tile += tile_step) {
+      for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
         const int halves = halves_of(t);
         const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
-        if (!kTgmm && p.ready_flags != nullptr) {
+        if (kEp && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
           if (slot != ready_slot) {
             if (!wait_flag_ge(p.ready_flags + slot, p.ready_epoch, abort_ptr)) {
@@ -210,7 +214,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t it = 0;
     uint32_t uses[2] = {0u, 0u};  // how often each half's accumulator has been used
     bool ok = true;
-    for (int tile = cta_index; tile < num_tiles && ok; tile += tile_step) {
+    for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
       const int halves = halves_of(t);
       const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
@@ -298,7 +302,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t uses = 0;
     bool ok = true;
     uint16_t* out16 = reinterpret_cast<uint16_t*>(p.out);
-    for (int tile = cta_index; tile < num_tiles && ok; tile += tile_step) {
+    for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
       if (half >= halves_of(t)) continue;  // this half does not exist in this tile
       const int n0 = t.n0;
@@ -402,8 +406,9 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int first = imin(imax(p.totals[1], 0), p.m);
       const size_t chunks_per_row = static_cast<size_t>(p.n) / 8;
       const size_t total = static_cast<size_t>(p.m - first) * chunks_per_row;
-      const size_t tid = static_cast<size_t>(cta_index) * kEpiThreads + (threadIdx.x - 64);
-      const size_t stride = static_cast<size_t>(gemm_ctas) * kEpiThreads;
+      const size_t tid = static_cast<size_t>(kEp ? blockIdx.x - sender_ctas : blockIdx.x) * kEpiThreads +
+                         (threadIdx.x - 64);
+      const size_t stride = static_cast<size_t>(kEp ? gridDim.x - sender_ctas : gridDim.x) * kEpiThreads;
       uint4* dst = reinterpret_cast<uint4*>(out16 + static_cast<size_t>(first) * p.n);
       const uint4 z = make_uint4(0u, 0u, 0u, 0u);
       for (size_t i = tid; i < total; i += stride) dst[i] = z;

@@ -287,8 +287,6 @@ class ExpertParallelRaggedDot:
         assign and a copy of this rank's own rows, ``rd_gmm_ep_fused`` runs the flag-gated GEMM on
         most CTAs while ``sender_ctas`` CTAs of the same grid push the rows of phases 1..W-1 to
         their owners and raise the owners' flags.  Same return values as ``forward_overlap``."""
-        import ctypes
-
         from . import _lib, ops
 
         tokens, top_k = routing.shape
@@ -321,12 +319,11 @@ class ExpertParallelRaggedDot:
             ev[4].record()
             ev[2].record()
         if "send" not in st:
-            base = (ctypes.c_uint64 * W)(*st["buf_ptrs"])
-            flg = (ctypes.c_uint64 * W)(*st["flag_ptrs"])
-            st["send_arrays"] = (base, flg)
+            st["send_arrays"] = (torch.tensor(st["buf_ptrs"], dtype=torch.int64, device=self.device),
+                                 torch.tensor(st["flag_ptrs"], dtype=torch.int64, device=self.device))
             st["send"] = _lib.EpSend()
-            st["send"].peer_base = ctypes.cast(base, ctypes.POINTER(ctypes.c_uint64))
-            st["send"].peer_flags = ctypes.cast(flg, ctypes.POINTER(ctypes.c_uint64))
+            st["send"].peer_base = st["send_arrays"][0].data_ptr()
+            st["send"].peer_flags = st["send_arrays"][1].data_ptr()
         send = st["send"]
         send.x_tokens, send.send_index = x_tokens.data_ptr(), send_index.data_ptr()
         send.send_start, send.dest_pos = plan["send_start"].data_ptr(), dest_pos.data_ptr()

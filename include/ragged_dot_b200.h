@@ -178,7 +178,7 @@ int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, con
  *                    phase 0 (the rank's own rows), before the fused launch; max_rows bounds the
  *                    list length for the grid size;
  *   rd_gmm_ep_fused  rd_gmm_indexed_when_ready + the sender role.  peer_base[r] / peer_flags[r]
- *                    (host arrays of `world` addresses) are rank r's receive buffer and flag array
+ *                    (device arrays of `world` addresses) are rank r's receive buffer and flag array
  *                    as seen from this GPU.  16-bit types, one CTA per tile (cta_group != 2). */
 typedef struct rd_ep_send {
   const void* x_tokens;        /* [tokens, row_bytes] */
@@ -186,8 +186,8 @@ typedef struct rd_ep_send {
   const int32_t* send_start;   /* from rd_ep_plan_ring */
   const int32_t* dest_pos;     /* from rd_ep_assign */
   int32_t* phase_done;         /* [world], reset by rd_ep_plan_ring */
-  const uint64_t* peer_base;   /* host array [world] */
-  const uint64_t* peer_flags;  /* host array [world] */
+  const uint64_t* peer_base;   /* device array [world] */
+  const uint64_t* peer_flags;  /* device array [world] */
   int32_t row_bytes, top_k, world, rank, capacity_rows, sender_ctas;
 } rd_ep_send;
 int rd_ep_assign(const int32_t* routing, int entries, int num_experts, int world, int rank,
