@@ -532,9 +532,10 @@ int rd_ep_assign(const int32_t* routing, int entries, int num_experts, int world
   if (entries == 0) return RD_OK;
   if (!routing || !dest_offset || !fill || !dest_pos || !send_start || !list_fill || !send_index)
     return RD_ERR_BAD_POINTER;
-  int blocks = (entries + rd::kEpThreads - 1) / rd::kEpThreads;
-  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
-  rd::ep_assign_kernel<<<blocks, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (num_experts + world > 5000) return RD_ERR_BAD_SHAPE;  // shared-memory counters of the kernel
+  const int blocks = (entries + rd::kEpThreads - 1) / rd::kEpThreads;
+  const size_t smem = 2 * static_cast<size_t>(num_experts + world) * sizeof(int32_t);
+  rd::ep_assign_kernel<<<blocks, rd::kEpThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       routing, entries, num_experts, num_experts / world, world, rank, dest_offset, fill, capacity_rows,
       dest_pos, send_start, list_fill, send_index);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;

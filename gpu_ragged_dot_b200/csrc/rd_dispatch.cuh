@@ -198,41 +198,50 @@ ep_dispatch_phase_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
   }
 }
 
-// Fused exchange, step 1: one thread per (token, slot) entry.  Assigns the row its position at
-// the expert's owner (dest_pos, as ep_dispatch_kernel does) and appends the entry to the send
-// list of its phase p = (owner - rank) mod W.  Appends are aggregated per warp and phase.
+// Fused exchange, step 1: one thread per (token, slot) entry, one pass per block.  Assigns the
+// row its position at the expert's owner (dest_pos, as ep_dispatch_kernel does) and appends the
+// entry to the send list of its phase p = (owner - rank) mod W.  Both counters are aggregated
+// in shared memory first, so a block issues one global atomic per expert / phase it touches.
+// Dynamic shared memory: 2 * (num_experts + world) ints.
 __global__ void __launch_bounds__(kEpThreads)
 ep_assign_kernel(const int32_t* __restrict__ routing, int entries, int num_experts,
                  int experts_per_rank, int world, int rank, const int32_t* __restrict__ dest_offset,
                  int32_t* __restrict__ fill, int capacity_rows, int32_t* __restrict__ dest_pos,
                  const int32_t* __restrict__ send_start, int32_t* __restrict__ list_fill,
                  int32_t* __restrict__ send_index) {
-  const int lane = threadIdx.x & 31;
-  const int base = blockIdx.x * blockDim.x;
-  for (int i0 = base; i0 < entries; i0 += gridDim.x * blockDim.x) {
-    const int i = i0 + threadIdx.x;
-    int phase = -1;
-    if (i < entries) {
-      const int e = routing[i];
-      if (e >= 0 && e < num_experts) {
-        int pos = dest_offset[e] + atomicAdd(&fill[e], 1);
-        if (pos >= capacity_rows) pos = -1;
-        dest_pos[i] = pos;
-        phase = (e / experts_per_rank - rank + world) % world;
-      } else {
-        dest_pos[i] = -1;
-      }
+  extern __shared__ int32_t sm[];
+  int32_t* cnt_e = sm;                       // [E]  entries of this block per expert
+  int32_t* cnt_p = sm + num_experts;         // [W]  ... per phase
+  int32_t* base_e = cnt_p + world;           // [E]  first slot of this block at the expert
+  int32_t* base_p = base_e + num_experts;    // [W]  first list slot of this block in the phase
+  for (int j = threadIdx.x; j < num_experts + world; j += blockDim.x) sm[j] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int e = -1, phase = -1, my_e = 0, my_p = 0;
+  if (i < entries) {
+    e = routing[i];
+    if (e >= 0 && e < num_experts) {
+      phase = (e / experts_per_rank - rank + world) % world;
+      my_e = atomicAdd(&cnt_e[e], 1);
+      my_p = atomicAdd(&cnt_p[phase], 1);
+    } else {
+      e = -1;
     }
-    // One atomic per distinct phase in the warp; every lane takes its place behind the leader's.
-    const unsigned active = __ballot_sync(0xffffffffu, phase >= 0);
-    if (phase >= 0) {
-      const unsigned peers = __match_any_sync(active, phase);
-      const int leader = __ffs(peers) - 1;
-      int first = 0;
-      if (lane == leader) first = atomicAdd(&list_fill[phase], __popc(peers));
-      first = __shfl_sync(peers, first, leader);
-      const int rank_in = __popc(peers & ((1u << lane) - 1u));
-      send_index[send_start[phase] + first + rank_in] = i;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < num_experts; j += blockDim.x)
+    if (cnt_e[j] > 0) base_e[j] = atomicAdd(&fill[j], cnt_e[j]);
+  for (int j = threadIdx.x; j < world; j += blockDim.x)
+    if (cnt_p[j] > 0) base_p[j] = atomicAdd(&list_fill[j], cnt_p[j]);
+  __syncthreads();
+  if (i < entries) {
+    if (e >= 0) {
+      int pos = dest_offset[e] + base_e[e] + my_e;
+      if (pos >= capacity_rows) pos = -1;
+      dest_pos[i] = pos;
+      send_index[send_start[phase] + base_p[phase] + my_p] = i;
+    } else {
+      dest_pos[i] = -1;
     }
   }
 }

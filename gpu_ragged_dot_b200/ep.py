@@ -86,13 +86,12 @@ class ExpertParallelRaggedDot:
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
                  dispatch: str = "nccl", capacity_rows: Optional[int] = None,
-                 own_blocks: int = 0, side_blocks: int = 0, sender_ctas: int = 16):
+                 own_blocks: int = 0, side_blocks: int = 0, sender_ctas: int = 0):
         from . import workloads
 
         assert dispatch in ("nccl", "p2p", "overlap", "fused")
         self.dispatch, self.capacity_rows, self._p2p = dispatch, capacity_rows, None
         self._ov, self._epoch = None, 0
-        self.sender_ctas = sender_ctas  # fused mode: CTAs of the GEMM grid that send instead of multiplying
         # overlap mode: grid caps of the phase kernels (0 = library default), phase 0 / the others
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         self.own_blocks, self.side_blocks = own_blocks or 8 * sms, side_blocks
@@ -100,6 +99,10 @@ class ExpertParallelRaggedDot:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        # fused mode: CTAs of the GEMM grid that send instead of multiplying.  One sender CTA moves
+        # about 26-39 GB/s over NVLink (as with NCCL, it takes a few dozen CTAs to fill the links):
+        # 16 are enough for the 134 MB a rank sends at W = 2, more ranks send more (235 MB at W = 8).
+        self.sender_ctas = sender_ctas or (16 if self.world <= 2 else 24)
         assert num_experts % self.world == 0
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
         self.k, self.n, self.device = k, n, device
