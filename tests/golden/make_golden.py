@@ -16,7 +16,7 @@ patterns).  Output buffers start as NaN, so elements the reference never writes 
 fixture.  tests/test_oracle_golden.py checks the CPU oracle against these files; the GPU parity
 tests check the CUDA path against the same files.
 
-    python tests/golden/make_golden.py [path-to-reference-checkout]
+    python tests/golden/make_golden.py <path-to-reference-checkout>
 
 Nothing from the reference is copied: it is imported and executed where it lies.
 """
@@ -336,7 +336,9 @@ GEMM_CASES = [
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of rdyro/gpu_ragged_dot>")
+    ref_dir = sys.argv[1]
     ref = import_reference(ref_dir)
 
     meta = {}
