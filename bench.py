@@ -638,6 +638,93 @@ def run_expert_parallel(args):
         results[mode] = t.tolist()
         del layer
         torch.cuda.empty_cache()
+    # Decode-shaped case of the same expert layout: 64 tokens x top-4 per GPU (m = 256 rows per rank),
+    # weight-bandwidth bound on every rank.  Timed with the two host-sync-free modes.
+    decode = {}
+    d_tokens = 64
+    xd = workloads.normal_tensor((d_tokens, shape.k), 1.0, 5000 + rank, dev)
+    rd_ = torch.from_numpy(workloads.topk_routing(d_tokens, experts, top_k, seed=6000 + rank)).to(dev)
+    for mode in ("p2p", "fused"):
+        try:
+            layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode,
+                                               capacity_rows=d_tokens * top_k * world)
+            for _ in range(max(args.warmup, 3)):
+                out = layer.forward(xd, rd_)
+            torch.cuda.synchronize()
+            ok = torch.ones(1, device=dev)
+        except Exception as e:
+            if rank == 0:
+                sys.stderr.write(f"bench: decode case, mode {mode} unavailable: {e!r}\n")
+            ok = torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0:
+            continue
+        seg = out[1]
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            layer.forward(xd, rd_)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        local = experts // world
+        touched = int((seg.view(world, local).sum(0) > 0).sum())  # local experts with at least one row
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps, float(touched)], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        decode[mode] = {"ms_per_step": float(tmax[0]),
+                        "weight_GBps_all_gpus": float(t[1]) * shape.k * shape.n * 2 / (float(tmax[0]) * 1e-3) / 1e9,
+                        "experts_touched": int(t[1])}
+        del layer
+        torch.cuda.empty_cache()
+    # End to end at N GPUs: every step copies this rank's tokens and routing from pinned host memory,
+    # runs the fastest mode's public forward() and reads the local result rows back to the host.
+    e2e = None
+    if results:
+        best_t = torch.tensor([results.get(m, [1e30])[0] for m in ("nccl", "p2p", "overlap", "fused")],
+                              dtype=torch.float64, device=dev)
+        dist.broadcast(best_t, src=0)
+        mode = ("nccl", "p2p", "overlap", "fused")[int(torch.argmin(best_t))]
+        layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode)
+        hx = x_tokens.cpu().pin_memory()
+        hr = routing.to(torch.int32).cpu().pin_memory()
+        rows_back = tokens * top_k
+        hy = torch.empty((rows_back, shape.n), dtype=torch.bfloat16).pin_memory()
+        dx_ = torch.empty_like(x_tokens)
+        dr_ = torch.empty_like(routing, dtype=torch.int32)
+
+        def step():
+            dx_.copy_(hx, non_blocking=True)
+            dr_.copy_(hr, non_blocking=True)
+            y_ = layer.forward(dx_, dr_)[0]
+            n_rows = min(rows_back, y_.shape[0])
+            hy[:n_rows].copy_(y_[:n_rows], non_blocking=True)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e2e_steps = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0])
+        e2e = {"value": 2.0 * tokens * top_k * world * shape.k * shape.n / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+               "ms_per_step": e2e_ms, "steps": e2e_steps, "dispatch": mode,
+               "h2d_bytes_per_step": world * (hx.numel() * 2 + hr.numel() * 4),
+               "d2h_bytes_per_step": world * hy.numel() * 2,
+               "api": "ExpertParallelRaggedDot.forward per rank, pinned host buffers"}
+        del layer
+        torch.cuda.empty_cache()
     if rank == 0 and results:
         best = min(results, key=lambda m: results[m][0])
         ms, gemm_ms, a2a_ms, first_ms, _ = results[best]
@@ -694,7 +781,10 @@ def run_expert_parallel(args):
                                       row_bytes_out / 770e9 * 1e3) / gemm_ms,
                           "traffic": None, "peak_source": peaks["source"] + "; NVLink 770 GB/s per direction"}),
             "dispatch_modes": modes,
-            "e2e": None,
+            "decode_case": {"tokens_per_gpu": d_tokens, "top_k": top_k, "rows_per_gpu": d_tokens * top_k,
+                            "note": "exchange + local ragged_dot per step; latency-bound (a few small kernels and "
+                                    "one all-gather), weights read once per touched expert", "modes": decode},
+            "e2e": e2e,
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()

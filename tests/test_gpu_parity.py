@@ -325,6 +325,80 @@ def test_mixtral_shape_properties():
         _assert_close(y[r].cpu(), want, f"mixtral row {r}")
 
 
+def test_mixtral_shape_backward_properties():
+    """dlhs and drhs at the benchmark size, ragged group sizes: sampled rows of dlhs and sampled
+    rows of every drhs block against the oracle; drhs is additive over a split of the rows."""
+    s = workloads.MIXTRAL
+    gs_np = workloads.group_sizes_mixtral_ragged(0)
+    x, A, dout = workloads.make_inputs(s, DEV, seed=0)
+    gs = torch.from_numpy(gs_np).to(DEV)
+    dx = ops.gmm_forward(dout, A, gs, trans_rhs=True)
+    dA = ops.tgmm_forward(x, dout, gs)
+    offs = np.concatenate([[0], np.cumsum(gs_np)])
+    rng = np.random.default_rng(1)
+    for r in np.sort(rng.choice(s.m, size=32, replace=False)):
+        gi = int(np.searchsorted(offs, r, side="right") - 1)
+        want = (dout[r].float().cpu() @ A[gi].float().cpu().T).to(torch.bfloat16)
+        _assert_close(dx[r].cpu(), want, f"dlhs row {r}")
+    for gi in range(s.g):
+        lo, hi = int(offs[gi]), int(offs[gi + 1])
+        for kr in rng.choice(s.k, size=4, replace=False):
+            want = (x[lo:hi, kr].float().cpu() @ dout[lo:hi].float().cpu()).to(torch.bfloat16)
+            _assert_close(dA[gi, kr].cpu(), want, f"drhs block {gi} row {kr}")
+    # rows of group gi split in two halves as two groups: the two blocks add up to the one block
+    # (fp32 sums rounded once vs twice: within two bf16 ulps of the larger magnitude)
+    gs2 = np.zeros(2 * s.g, dtype=np.int32)
+    gs2[0::2] = gs_np // 2
+    gs2[1::2] = gs_np - gs_np // 2
+    dA2 = ops.tgmm_forward(x, dout, torch.from_numpy(gs2).to(DEV))
+    summed = dA2[0::2].float() + dA2[1::2].float()
+    err = (summed - dA.float()).abs()
+    tol = 2.0 ** -6 * torch.maximum(dA2[0::2].float().abs(), dA2[1::2].float().abs()) + 1e-3
+    assert bool((err <= tol).all()), f"drhs not additive over a row split: worst {float((err / tol).max()):.2f}x"
+
+
+def test_deepseek_shape_properties():
+    """The largest configuration (m 32768, k 7168, n 2048, 256 experts, heavy-tailed sizes with
+    empty experts; 7.5 GB of weights and as much of drhs): sampled rows / blocks against the
+    oracle, zero blocks for empty experts, zero tail, and the device status word."""
+    s = workloads.DEEPSEEK_V3
+    gs_np = workloads.group_sizes_deepseek(0)
+    gs_np[int(np.argmax(gs_np))] -= 100  # leave a tail of unowned rows
+    x, A, dout = workloads.make_inputs(s, DEV, seed=0)
+    gs = torch.from_numpy(gs_np).to(DEV)
+    ws = ops._workspace(s.m, s.g, DEV)
+    y = ops.gmm_forward(x, A, gs, workspace=ws)
+    assert ops.device_status(ws) == 0
+    total = int(gs_np.sum())
+    assert float(y[total:].float().abs().max()) == 0.0
+    offs = np.concatenate([[0], np.cumsum(gs_np)])
+    rng = np.random.default_rng(2)
+    rows = np.sort(rng.choice(total, size=48, replace=False))
+    for r in rows:
+        gi = int(np.searchsorted(offs, r, side="right") - 1)
+        want = (x[r].float().cpu() @ A[gi].float().cpu()).to(torch.bfloat16)
+        _assert_close(y[r].cpu(), want, f"deepseek fwd row {r}")
+    dx = ops.gmm_forward(dout, A, gs, trans_rhs=True, workspace=ws)
+    for r in rows[:16]:
+        gi = int(np.searchsorted(offs, r, side="right") - 1)
+        want = (dout[r].float().cpu() @ A[gi].float().cpu().T).to(torch.bfloat16)
+        _assert_close(dx[r].cpu(), want, f"deepseek dlhs row {r}")
+    del y, dx, A
+    torch.cuda.empty_cache()
+    dA = ops.tgmm_forward(x, dout, gs, workspace=ws)
+    assert ops.device_status(ws) == 0
+    empty = np.nonzero(gs_np == 0)[0]
+    assert len(empty) > 0
+    for gi in empty[:8]:
+        assert float(dA[int(gi)].float().abs().max()) == 0.0
+    big = np.argsort(gs_np)[-3:]
+    for gi in list(big) + list(np.nonzero(gs_np == gs_np[gs_np > 0].min())[0][:2]):
+        lo, hi = int(offs[gi]), int(offs[gi + 1])
+        for kr in rng.choice(s.k, size=3, replace=False):
+            want = (x[lo:hi, kr].float().cpu() @ dout[lo:hi].float().cpu()).to(torch.bfloat16)
+            _assert_close(dA[int(gi), kr].cpu(), want, f"deepseek drhs block {gi} row {kr}")
+
+
 # ------------------------------------------------------------------ against the reference's own outputs
 from tests import golden_io  # noqa: E402
 
