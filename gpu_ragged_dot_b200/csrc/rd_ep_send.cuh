@@ -6,10 +6,13 @@
 // mbarrier: one thread keeps several KB in flight per warp without registers) and shared -> peer
 // memory with plain 16-byte stores (posted writes over NVLink).  Every warp works on its own:
 // own slots, own barriers, its share of the phase's rows (taken from the send list the assign
-// kernel wrote), so there is no hand-over between warps.  When a warp has issued all its stores
-// of a phase it fences them at system scope and counts itself in; the last warp of the last
-// sender CTA stores the epoch into the destination's ready flag for this source, which is what
-// the destination's GEMM loader waits for (wait_flag_ge).
+// kernel wrote), so there is no hand-over between warps.  The copying warps never fence: when
+// one has issued all its stores of a phase it arrives on that phase's CTA barrier and goes on
+// with the next phase.  Warp 0 of the CTA copies nothing; per phase it waits for the others'
+// arrivals, fences at system scope (the fence is cumulative: it covers the stores of the warps
+// whose arrival it has observed) and counts the CTA in; the last CTA stores the epoch into the
+// destination's ready flag for this source, which is what the destination's GEMM loader waits
+// for (wait_flag_ge).
 //
 // Only local memory is read by the bulk copies; peer memory is only written, with plain stores.
 #pragma once
@@ -42,28 +45,53 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 }
 
 // Runs on every thread of a sender CTA.  smem: 1024-byte aligned shared window of at least
-// warps * (kEpSlots * kEpChunkBytes + 64) bytes.
+// warps * (kEpSlots * kEpChunkBytes + 64) + 8 * world bytes.
 __device__ __noinline__ void ep_sender_role(const EpSendArgs a, int epoch, int sender, uint32_t smem,
                                             volatile int* abort_flag, int32_t* status) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_warps = blockDim.x >> 5;
+  const uint64_t t_start = global_timer_ns();
   if (threadIdx.x == 0) *abort_flag = 0;
   const uint32_t slots = smem + warp * (kEpSlots * kEpChunkBytes);
   const uint32_t bars = smem + n_warps * (kEpSlots * kEpChunkBytes) + warp * 64;
+  const uint32_t phase_bars = smem + n_warps * (kEpSlots * kEpChunkBytes + 64);  // one per phase
   if (lane == 0) {
     for (int s = 0; s < kEpSlots; ++s) mbar_init(bars + 8 * s, 1);
+    if (warp == 0)
+      for (int p = 0; p < a.world; ++p) mbar_init(phase_bars + 8 * p, n_warps - 1);
     fence_mbar_init();
   }
   __syncthreads();
 
   const int cpr = (a.row_bytes + kEpChunkBytes - 1) / kEpChunkBytes;  // chunks per row
-  const long long GW = static_cast<long long>(a.sender_ctas) * n_warps;  // warps sending
-  const long long gw = static_cast<long long>(sender) * n_warps + warp;
+  const int n_copy = n_warps - 1;                                        // warp 0 only signals
+  const long long GW = static_cast<long long>(a.sender_ctas) * n_copy;  // warps copying
+  const long long gw = static_cast<long long>(sender) * n_copy + (warp - 1);
   uint32_t parity = 0;  // bit s: parity of the next completion of slot s
   bool ok = true;
 
-  for (int p = 1; p < a.world && ok; ++p) {
+  if (warp == 0) {
+    // ---- signaller
+    for (int p = 1; p < a.world && ok; ++p) {
+      if (!mbar_wait(phase_bars + 8 * p, 0u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      __threadfence_system();
+      if (lane == 0) {
+        const int dest = (a.rank + p) % a.world;
+        const int done = atomicAdd(a.phase_done + p, 1) + 1;
+        if (done == a.sender_ctas) {
+          __threadfence_system();
+          int32_t* flag = reinterpret_cast<int32_t*>(a.peer_flags[dest]) + p;
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+        }
+      }
+      __syncwarp();
+    }
+  }
+  for (int p = 1; warp > 0 && p < a.world && ok; ++p) {
     const int dest = (a.rank + p) % a.world;
     uint8_t* dst_base = reinterpret_cast<uint8_t*>(a.peer_base[dest]);
     const int start = a.send_start[p];
@@ -138,22 +166,16 @@ __device__ __noinline__ void ep_sender_role(const EpSendArgs a, int epoch, int s
       __syncwarp();
     }
     if (!ok) break;
-    // This warp's rows of phase p are on their way: make them visible at the destination, then
-    // count in; the last warp raises the destination's flag for this source.
-    __threadfence_system();
+    // This warp's stores of phase p have been issued: tell the signaller and go on.
     __syncwarp();
-    if (lane == 0) {
-      const int done = atomicAdd(a.phase_done + p, 1) + 1;
-      if (done == static_cast<int>(GW)) {
-        __threadfence_system();
-        int32_t* flag = reinterpret_cast<int32_t*>(a.peer_flags[dest]) + p;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
-      }
-    }
+    if (lane == 0) mbar_arrive(phase_bars + 8 * p);
     __syncwarp();
   }
 
   __syncthreads();
+  // status[1]: time the slowest sender CTA needed for all its phases (microseconds)
+  if (threadIdx.x == 0)
+    atomicMax(status + 1, static_cast<int32_t>((global_timer_ns() - t_start) / 1000ull));
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicMax(status, 1);
     // bulk copies may still be in flight into this CTA's shared memory

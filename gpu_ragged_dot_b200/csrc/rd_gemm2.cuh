@@ -151,6 +151,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t it = 0;
       bool ok = true;
       int ready_slot = -1;  // last ready flag this producer has seen set
+      uint64_t waited_ns = 0;
+      const uint64_t t_start = kEp ? global_timer_ns() : 0;
       for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
         const int halves = halves_of(t);
@@ -158,10 +160,12 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (kEp && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
           if (slot != ready_slot) {
+            const uint64_t w0 = global_timer_ns();
             if (!wait_flag_ge(p.ready_flags + slot, p.ready_epoch, abort_ptr)) {
               ok = false;
               break;
             }
+            waited_ns += global_timer_ns() - w0;
             ready_slot = slot;
           }
         }
@@ -197,6 +201,12 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         }
+      }
+      if (kEp) {
+        // status[2]: longest total wait of a loader for remote rows; status[3]: longest loader
+        // lifetime (microseconds).  Read back by the expert-parallel harness.
+        atomicMax(p.status + 2, static_cast<int32_t>(waited_ns / 1000ull));
+        atomicMax(p.status + 3, static_cast<int32_t>((global_timer_ns() - t_start) / 1000ull));
       }
     }
   } else if (warp == 1) {

@@ -77,7 +77,13 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
   if (tid == 0) {
     carry_rows = 0;
     carry_tiles = 0;
-    if (status) status[0] = 0;
+    if (status) {
+      status[0] = 0;
+      // words 1..3: timing counters of the expert-parallel kernels (microseconds; see rd_ep_send.cuh)
+      status[1] = 0;
+      status[2] = 0;
+      status[3] = 0;
+    }
   }
   __syncthreads();
 

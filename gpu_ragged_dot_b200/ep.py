@@ -99,10 +99,10 @@ class ExpertParallelRaggedDot:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        # fused mode: CTAs of the GEMM grid that send instead of multiplying.  One sender CTA moves
-        # about 26-39 GB/s over NVLink (as with NCCL, it takes a few dozen CTAs to fill the links):
-        # 16 are enough for the 134 MB a rank sends at W = 2, more ranks send more (235 MB at W = 8).
-        self.sender_ctas = sender_ctas or (16 if self.world <= 2 else 24)
+        # fused mode: CTAs of the GEMM grid that send instead of multiplying.  Measured: 16 sender
+        # CTAs move 600 GB/s per GPU at 2 and at 8 ranks; 8 are too few (220 GB/s), 24 are slower
+        # again at 8 ranks (480 GB/s) and take more SMs from the GEMM.
+        self.sender_ctas = sender_ctas or 16
         assert num_experts % self.world == 0
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
         self.k, self.n, self.device = k, n, device
