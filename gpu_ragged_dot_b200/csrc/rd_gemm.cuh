@@ -361,8 +361,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ MMA issuer
     // In a pair only the leader issues MMAs.  The peer's warp 1 has nothing to do except for
     // the tgmm stages whose tail rows it must clear in its own shared memory.
-    const uint32_t idesc =
+    const uint32_t idesc_full =
         make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
+    // A gmm row tile with at most 64 rows (the short last tile of a group, a small expert) is
+    // multiplied with M = 64: half the tensor-core time for a tile that is mostly padding.
+    // Its accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory.
+    const uint32_t idesc_half = make_idesc_f16(p.ab_format, 0, kBKMajor ? 0 : 1, 64, BN);
     // Stage-0 operand descriptors; later stages / k-steps only add to the 16-byte-unit address.
     constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;       // A: MN-major (tgmm) or K-major
     constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;    // B: K-major or MN-major
@@ -382,6 +386,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
       const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
       const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+      const uint32_t idesc = (!kTgmm && !kPair && t.rows <= 64) ? idesc_half : idesc_full;
 
       if (kPair && !leader) {
         // ---- peer CTA: only the tail stage of a tgmm tile needs this warp
@@ -530,6 +535,14 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         slab_by_tma = true;  // rows >= k are outside the map and dropped by the store
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
         zero_only = t.rows <= 0;
+      } else if (!kPair && t.rows <= 64) {
+        // M = 64 tile: row 16 * quarter + lane sits in lane `lane` (< 16) of this warp's quarter
+        const int r64 = quarter * 16 + lane;
+        out_row0 = t.row0 + quarter * 16;
+        row_ok = lane < 16 && r64 < t.rows;
+        warp_has_rows = quarter * 16 < t.rows;
+        slab_by_tma = false;
+        row_off = static_cast<size_t>(t.row0 + r64) * static_cast<size_t>(p.n);
       } else {
         out_row0 = t.row0 + quarter * 32;
         row_ok = r_in_tile < t.rows;
