@@ -632,6 +632,17 @@ def run_expert_parallel(args):
         clocks = sampler.stop()
         ms = e0.elapsed_time(e1) / args.steps
         parts = layer.timers_ms(args.steps)
+        if mode in ("overlap", "fused"):
+            # a bounded wait that expired inside a kernel (status word != 0) makes the timing meaningless
+            from gpu_ragged_dot_b200 import ops as _ops
+            bad = torch.tensor([float(_ops.device_status(layer._ov["ws"]) != 0)], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if float(bad) != 0:
+                if rank == 0:
+                    sys.stderr.write(f"bench: dispatch mode {mode} dropped: a device-side wait expired\n")
+                del layer
+                torch.cuda.empty_cache()
+                continue
         t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"], parts.get("own_rows", 0.0)],
                          dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
