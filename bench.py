@@ -514,6 +514,12 @@ def run_other_workloads(dev, peaks):
         _time_ms(lambda: ops.gmm_forward(dout, A, gs, trans_rhs=True, out=dx, workspace=ws), 8), fl, b_gmm)
     out[s.name + "_drhs"] = entry(_time_ms(lambda: ops.tgmm_forward(x, dout, gs, out=dA, workspace=ws), 8), fl, b_tgmm)
     out[s.name + "_fwd"]["nonempty_groups"] = gplus
+    # drhs writes 7.5 GB and reads 0.6 GB: it is bound by the WRITE bandwidth, which on these parts
+    # is well below the read+write copy figure.  A memset of the same output measured here is its ceiling.
+    ms_set = _time_ms(lambda: dA.zero_(), 5)
+    out[s.name + "_drhs"]["memset_of_the_output_ms"] = ms_set
+    out[s.name + "_drhs"]["write_GBps_of_memset"] = dA.numel() * 2 / (ms_set * 1e-3) / 1e9
+    out[s.name + "_drhs"]["time_vs_memset_of_the_output"] = out[s.name + "_drhs"]["ms"] / ms_set
     return out
 
 
