@@ -524,9 +524,13 @@ def run_other_workloads(dev, peaks):
 
 
 def run_e2e(args, shape, dev, rd, x, A, dout, gs, kernels):
-    """Same step through the public API with host buffers: pinned H2D of x, A, group_sizes and
-    dout, ragged_dot + backward on the device, D2H of y, dlhs and drhs -- all inside the timed
-    region."""
+    """Same step with HOST buffers, everything inside the timed region: pinned H2D of x, A,
+    group_sizes and dout, ragged_dot + backward on the device, D2H of y, dlhs and drhs.
+
+    `value` goes through `HostRaggedDot` (the host-buffer entry of the package: expert chunks are
+    copied in, multiplied and copied out on three streams, so both directions of the PCIe link and
+    the GPU work at once).  `one_stream_ms` is the plain way beside it: `ragged_dot` + autograd
+    on device tensors with the copies around it on one stream."""
     full = len(kernels) == 3
     hx, hA, hd = (t.cpu().pin_memory() for t in (x, A, dout))
     hgs = gs.cpu().pin_memory()
@@ -535,7 +539,7 @@ def run_e2e(args, shape, dev, rd, x, A, dout, gs, kernels):
     hdA = torch.empty_like(hA).pin_memory()
     steps = max(2, min(args.steps, 5))
 
-    def step():
+    def step_one_stream():
         dx_ = hx.to(dev, non_blocking=True)
         dA_ = hA.to(dev, non_blocking=True)
         dg_ = hgs.to(dev, non_blocking=True)
@@ -550,23 +554,40 @@ def run_e2e(args, shape, dev, rd, x, A, dout, gs, kernels):
             hdA.copy_(dA_.grad, non_blocking=True)
         hy.copy_(yv.detach(), non_blocking=True)
 
-    for _ in range(2):
-        step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    pipe = rd.HostRaggedDot(shape.m, shape.k, shape.n, shape.g, device=dev, backward=full)
+
+    def step_pipelined():
+        if full:
+            pipe(hx, hA, hgs, hd, y=hy, dlhs=hdx, drhs=hdA)
+        else:
+            pipe(hx, hA, hgs, y=hy)
+
+    def timed(step, reps):
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ms_serial = timed(step_one_stream, steps)
+    torch.cuda.empty_cache()
+    ms = timed(step_pipelined, steps)
     nbytes = lambda t: t.numel() * t.element_size()
     h2d = nbytes(hx) + nbytes(hA) + nbytes(hgs) + (nbytes(hd) if full else 0)
     d2h = nbytes(hy) + ((nbytes(hdx) + nbytes(hdA)) if full else 0)
     flops = 2.0 * shape.m * shape.k * shape.n * (3 if full else 1)
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "gpu_ragged_dot_b200.ragged_dot + autograd backward, pinned host buffers"}
+            "h2d_GBps": h2d / (ms * 1e-3) / 1e9, "d2h_GBps": d2h / (ms * 1e-3) / 1e9,
+            "api": "gpu_ragged_dot_b200.HostRaggedDot (pinned host buffers; chunks of experts copied in, "
+                   "multiplied by rd_gmm/rd_tgmm and copied out on three streams)",
+            "one_stream_ms": ms_serial, "one_stream_value": flops / (ms_serial * 1e-3) / 1e12,
+            "one_stream_api": "gpu_ragged_dot_b200.ragged_dot + autograd backward, copies on the same stream"}
 
 
 def run_cpu_baseline(shape, kernels):

@@ -1,6 +1,7 @@
 """B200-native (sm_100a) ragged dot: drop-in for rdyro/gpu_ragged_dot's ``ragged_dot`` /
 ``trans_ragged_dot`` backed by hand-written CUDA (TMA + tcgen05) behind a C ABI."""
 
+from .host_pipeline import HostRaggedDot  # noqa: F401
 from .ops import (  # noqa: F401
     CHUNK_M,
     DEFAULT_BLOCK_K,
@@ -19,4 +20,4 @@ from .ops import (  # noqa: F401
     trans_ragged_dot,
 )
 
-__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted"]
+__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted", "HostRaggedDot"]
