@@ -171,14 +171,22 @@ __device__ __forceinline__ bool tail_needs_clearing(int group_rows) {
 template <int kBoxes>
 __device__ __forceinline__ void clear_tail_rows(uint32_t stage_addr, int live, int lane) {
   const int n_mma = (live + kUmmaK - 1) / kUmmaK;
-  const int dead = n_mma * kUmmaK - live;
+  const int dead = n_mma * kUmmaK - live;  // 0..15 rows
   if (dead <= 0) return;
-  const int chunks = kBoxes * dead * 8;  // 16-byte chunks
-  for (int c = lane; c < chunks; c += 32) {
-    const int box = c / (dead * 8);
-    const int rem = c - box * (dead * 8);
-    const uint32_t addr = stage_addr + box * kBoxBytes + (live * 128) + rem * 16;
-    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+  // Row r of a box is the 128 bytes at box + r * 128 (the swizzle only permutes 16-byte chunks
+  // inside a row), so the dead rows of a box are one contiguous range of at most 1920 bytes:
+  // four 512-byte warp stores per box, no index arithmetic in the loop.
+  const int bytes = dead * 128;
+  const uint32_t first = stage_addr + live * 128 + lane * 16;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i * 512 + lane * 16 < bytes) {
+#pragma unroll
+      for (int box = 0; box < kBoxes; ++box) {
+        const uint32_t addr = first + box * kBoxBytes + i * 512;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+      }
+    }
   }
   fence_proxy_async_smem();
 }

@@ -345,9 +345,12 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       const int n_chunks = warp_has_rows ? imin(BN / 64, (p.n - n0 + 63) / 64) : 0;
       const uint32_t acc_empty_bar = smem_u32(&bar_acc_empty[half]);
-#pragma unroll 1
-      for (int c = 0; c < n_chunks; ++c) {
-        const int col = n0 + c * 64;
+      // First the whole accumulator slab leaves TMEM (packed to 16 bits, 32 registers per 64
+      // columns) and the half is handed back to the MMA warp; only chunk 0 is stored on the way,
+      // so that its TMA store runs under the remaining loads.  The other chunks are stored after
+      // the hand-back: the waits for the staging buffer no longer hold up the next tile's MMAs.
+      uint4 o[BN / 64][8];
+      auto load_chunk = [&](int c) {
         uint32_t v[64];
         if (!zero_only) {
           const uint32_t taddr =
@@ -359,19 +362,16 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < 64; ++j) v[j] = 0u;
         }
-        if (c == n_chunks - 1) {  // the accumulator is in registers: hand it back
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar);
-        }
-        uint4 o[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          o[q].x = pack2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), p.ab_format);
-          o[q].y = pack2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), p.ab_format);
-          o[q].z = pack2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), p.ab_format);
-          o[q].w = pack2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), p.ab_format);
+          o[c][q].x = pack2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), p.ab_format);
+          o[c][q].y = pack2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), p.ab_format);
+          o[c][q].z = pack2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), p.ab_format);
+          o[c][q].w = pack2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), p.ab_format);
         }
+      };
+      auto store_chunk = [&](int c) {
+        const int col = n0 + c * 64;
         if (slab_by_tma) {
           if (lane == 0) bulk_wait_group_read<0>();  // the previous box has left this buffer
           __syncwarp();
@@ -379,8 +379,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const uint32_t a = row_addr + (((q ^ (lane & 7)) & 7) << 4);  // 128-byte swizzle
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[q].x),
-                         "r"(o[q].y), "r"(o[q].z), "r"(o[q].w)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[c][q].x),
+                         "r"(o[c][q].y), "r"(o[c][q].z), "r"(o[c][q].w)
                          : "memory");
           }
           fence_proxy_async_smem();
@@ -397,9 +397,25 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint16_t* dst = out16 + row_off + col;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            if (col + q * 8 < p.n) *reinterpret_cast<uint4*>(dst + q * 8) = o[q];
+            if (col + q * 8 < p.n) *reinterpret_cast<uint4*>(dst + q * 8) = o[c][q];
           }
         }
+      };
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c) {
+        if (c < n_chunks) {
+          load_chunk(c);
+          if (c == 0) store_chunk(0);
+        }
+      }
+      if (n_chunks > 0) {  // the accumulator is in registers: hand it back
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar);
+      }
+#pragma unroll
+      for (int c = 1; c < BN / 64; ++c) {
+        if (c < n_chunks) store_chunk(c);
       }
       if (n_chunks == 0) {
         tc_fence_before_sync();
