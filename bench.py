@@ -783,7 +783,9 @@ def run_expert_parallel(args):
                                   "flag_gated_ragged_dot_from_plan_end": g_ms} if m_ == "overlap" else
                                  {"count_allgather_plan_assign": p_ms, "own_rows_copied_from_plan_end": own_ms,
                                   "fused_send_and_ragged_dot_from_plan_end": g_ms}),
-                "exchange_GBps_per_gpu": row_bytes_out / (x_ms * 1e-3) / 1e9,
+                # fused: the exchange has no span of its own; rate over the whole send + GEMM kernel
+                ("exchange_GBps_per_gpu_over_the_fused_kernel" if m_ == "fused" else "exchange_GBps_per_gpu"):
+                    row_bytes_out / ((g_ms if m_ == "fused" else x_ms) * 1e-3) / 1e9,
             }
         line = {
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
