@@ -31,7 +31,22 @@ import torch
 
 from . import ops
 
-__all__ = ["HostRaggedDot"]
+__all__ = ["HostRaggedDot", "plan_chunks"]
+
+
+def plan_chunks(sizes: List[int], experts_per_chunk: int) -> List[Tuple[int, int, int, int]]:
+    """Cut ``g = len(sizes)`` experts into consecutive chunks of ``experts_per_chunk`` (the last one
+    may be shorter): (first expert, end expert, first row, end row) per chunk, in order.  The row
+    ranges tile ``[0, sum(sizes))`` without gaps because the rows are sorted by expert."""
+    if experts_per_chunk < 1:
+        raise ValueError("experts_per_chunk must be at least 1")
+    out, row = [], 0
+    for e0 in range(0, len(sizes), experts_per_chunk):
+        e1 = min(len(sizes), e0 + experts_per_chunk)
+        rows = sum(sizes[e0:e1])
+        out.append((e0, e1, row, row + rows))
+        row += rows
+    return out
 
 
 class HostRaggedDot:
@@ -74,14 +89,7 @@ class HostRaggedDot:
 
     # ------------------------------------------------------------------ helpers
     def chunks(self, sizes: List[int]) -> List[Tuple[int, int, int, int]]:
-        """(first expert, end expert, first row, end row) of every chunk, in order."""
-        out, row = [], 0
-        for e0 in range(0, self.g, self.experts_per_chunk):
-            e1 = min(self.g, e0 + self.experts_per_chunk)
-            rows = sum(sizes[e0:e1])
-            out.append((e0, e1, row, row + rows))
-            row += rows
-        return out
+        return plan_chunks(sizes, self.experts_per_chunk)
 
     def _check_host(self, t: torch.Tensor, shape, name: str, dtype=None) -> None:
         if t.is_cuda:

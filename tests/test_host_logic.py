@@ -79,3 +79,18 @@ def test_cpu_tensors_are_refused():
     with pytest.raises(NotImplementedError):
         rd.gmm(x, A, gs, compute_dtype=torch.float32)
     assert ops._torch_dtype("float32") is torch.float32
+
+
+def test_host_pipeline_chunk_plan():
+    """Chunks of experts for the host-buffer pipeline: consecutive, covering every expert once, row
+    ranges back to back, empty experts and empty chunks included."""
+    from gpu_ragged_dot_b200.host_pipeline import plan_chunks
+
+    sizes = [5, 0, 12, 3, 0, 0, 9, 1]
+    assert plan_chunks(sizes, 1) == [(i, i + 1, sum(sizes[:i]), sum(sizes[:i + 1])) for i in range(8)]
+    assert plan_chunks(sizes, 3) == [(0, 3, 0, 17), (3, 6, 17, 20), (6, 8, 20, 30)]
+    assert plan_chunks(sizes, 100) == [(0, 8, 0, 30)]
+    assert plan_chunks([0, 0, 0], 2) == [(0, 2, 0, 0), (2, 3, 0, 0)]
+    assert plan_chunks([], 4) == []
+    with pytest.raises(ValueError):
+        plan_chunks(sizes, 0)
