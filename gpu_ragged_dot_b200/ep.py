@@ -108,6 +108,7 @@ class ExpertParallelRaggedDot:
         self.k, self.n, self.device = k, n, device
         self.weights = workloads.normal_tensor((self.local_experts, k, n), k ** -0.5, seed, device, dtype)
         self._events = []
+        self._host = None
 
     def reset_timers(self):
         self._events = []
@@ -368,3 +369,60 @@ class ExpertParallelRaggedDot:
             ev[3].record()
             self._events.append(ev)
         return y, plan
+
+    # ------------------------------------------------------------------ host-resident tokens
+    def forward_host(self, x_host: torch.Tensor, routing_host: torch.Tensor, y_host: torch.Tensor) -> int:
+        """One step for a caller whose tokens, routing and result live in pinned host memory.
+
+        The copy-in goes to one of two device slots on a copy stream, so the tokens of step i+1
+        cross PCIe while step i is exchanged, multiplied and copied out (on a third stream); the
+        step itself is ``forward`` on the current stream.  Copies ``min(len(y_host), rows of y)``
+        rows of the result into ``y_host`` and returns that count.  ``wait_host_outputs`` orders
+        the current stream after the last copy-out."""
+        for name, t in (("x_host", x_host), ("routing_host", routing_host), ("y_host", y_host)):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError(f"{name} must be a pinned host tensor")
+        if routing_host.dtype != torch.int32:
+            raise ValueError("routing_host must be int32")
+        dev = self.device
+        if self._host is None:
+            self._host = {
+                "x": [torch.empty(x_host.shape, dtype=x_host.dtype, device=dev) for _ in range(2)],
+                "r": [torch.empty(routing_host.shape, dtype=torch.int32, device=dev) for _ in range(2)],
+                "s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
+                "read": [None, None],  # the step that last read slot i has finished
+                "out": None,           # the last copy-out has finished
+                "step": 0,
+            }
+        h = self._host
+        slot = h["step"] & 1
+        h["step"] += 1
+        s_in, s_out = h["s_in"], h["s_out"]
+        cur = torch.cuda.current_stream(dev)
+        arrived = torch.cuda.Event()
+        with torch.cuda.stream(s_in):
+            if h["read"][slot] is not None:
+                s_in.wait_event(h["read"][slot])
+            h["x"][slot].copy_(x_host, non_blocking=True)
+            h["r"][slot].copy_(routing_host, non_blocking=True)
+            arrived.record(s_in)
+        cur.wait_event(arrived)
+        if h["out"] is not None:  # the result buffer of the previous step is still being copied out
+            cur.wait_event(h["out"])
+        y = self.forward(h["x"][slot], h["r"][slot])[0]
+        done = torch.cuda.Event()
+        done.record(cur)
+        h["read"][slot] = done
+        rows = min(y_host.shape[0], y.shape[0])
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            y_host[:rows].copy_(y[:rows], non_blocking=True)
+            y.record_stream(s_out)
+            h["out"] = torch.cuda.Event()
+            h["out"].record(s_out)
+        return rows
+
+    def wait_host_outputs(self) -> None:
+        """Make the current stream wait for the last ``forward_host`` copy-out."""
+        if self._host is not None and self._host["out"] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._host["out"])

@@ -52,6 +52,30 @@ def _worker(rank, world, port, out_dir):
             res["p2p"] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu()}
         res["weights"] = layer.weights.cpu()
         del layer
+    # Host-resident tokens: forward_host (copy-in of step i+1 under step i, copy-out on a third
+    # stream) must deliver what forward delivers for the same inputs, step after step.
+    host_ok = {}
+    for mode in ("nccl", "fused"):
+        layer = ep.ExpertParallelRaggedDot(E, k, n, dev, seed=2000 + rank, dispatch=mode)
+        hr = routing.to(torch.int32).cpu().pin_memory()
+        ok = True
+        for step in range(3):
+            xs = (x.float() * (1.0 + step)).to(torch.bfloat16)
+            out = layer.forward(xs, routing)
+            total = out[0].shape[0] if mode == "nccl" else int(out[3].cpu())
+            want = out[0][:total].float().cpu()
+            hy = torch.zeros((out[0].shape[0], n), dtype=torch.bfloat16).pin_memory()
+            rows = layer.forward_host(xs.cpu().pin_memory(), hr, hy)
+            layer.wait_host_outputs()
+            torch.cuda.synchronize()
+            got = hy[:total].float()
+            if mode == "nccl":  # rows arrive in a fixed order
+                ok = ok and rows >= total and torch.equal(got, want)
+            else:               # positions inside a segment depend on arrival order: compare as sets
+                ok = ok and rows >= total and torch.equal(got.sum(1).sort().values, want.sum(1).sort().values)
+        host_ok[mode] = bool(ok)
+        del layer
+    res["host_ok"] = host_ok
     torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -67,6 +91,7 @@ def test_expert_parallel_two_gpus(tmp_path):
     E, top_k = 16, 4
     local = E // world
     for d in range(world):
+        assert res[d]["host_ok"] == {"nccl": True, "fused": True}
         w = res[d]["weights"].float()
         seg_ref = []
         for s in range(world):
