@@ -165,8 +165,12 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
+    # All the host threads this process may use (torchrun presets OMP_NUM_THREADS=1 for its ranks).
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    if max(world, args.gpus) > 1:
+        return run_reference_expert_parallel(args, max(world, args.gpus), threads)
     shape = workloads.MIXTRAL
-    threads = torch.get_num_threads()
     gemms = 3 if args.only is None else 1
     # Calibrate on 128 rows, then size the per-step sample so warmup+steps stay near 2 minutes.
     x, A, dout, gs = cpu_oracle_sample(shape, 128, threads)
@@ -203,6 +207,62 @@ def run_reference(args):
         "data": "synthetic",
         "config": {"workload": shape.name + "_fwd_bwd", "m": shape.m, "k": shape.k, "n": shape.n,
                    "g": shape.g, "reference": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_expert_parallel(args, world, threads):
+    """Reference arm of the N > 1 workload (expert-parallel forward): the same routing, permutation
+    by expert and ragged_dot over all 64 experts, on the host cores of rank 0.  There is no
+    exchange on one host; each step is a bounded sample of the job's tokens."""
+    from gpu_ragged_dot_b200 import workloads
+    from oracle import ragged_dot_oracle as oracle
+
+    shape = workloads.EP_PREFILL
+    tokens_job, top_k, experts = 8192 * world, 4, shape.g
+    A = workloads.normal_tensor((experts, shape.k, shape.n), shape.k ** -0.5, 12, "cpu")
+
+    def make(tokens):
+        x = workloads.normal_tensor((tokens, shape.k), 1.0, 11, "cpu")
+        routing = torch.from_numpy(workloads.topk_routing(tokens, experts, top_k, seed=3000)).to(torch.int64)
+        return x, routing
+
+    def step(x, routing):
+        flat = routing.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        gs = torch.bincount(flat, minlength=experts).to(torch.int32)
+        rows = x.index_select(0, order // top_k)
+        return oracle.ragged_dot(rows, A, gs, native_16bit=True)
+
+    x, routing = make(256)
+    step(x, routing)
+    t0 = time.perf_counter()
+    step(x, routing)
+    t_probe = time.perf_counter() - t0
+    budget = 120.0 / max(args.steps + args.warmup, 1)
+    tokens = int(min(tokens_job, max(256, 256 * budget / max(t_probe, 1e-3))))
+    tokens = max(256, (tokens // 256) * 256)
+    x, routing = make(tokens)
+    for _ in range(args.warmup):
+        step(x, routing)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(x, routing)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = 2.0 * tokens * top_k * shape.k * shape.n / dt / 1e12
+    sample = (f"{tokens} of the job's {tokens_job} tokens x top-{top_k} per step: sort by expert, gather rows, "
+              f"ragged_dot over all {experts} experts' weights; torch CPU bf16 matmul (oneDNN, fp32 accumulate) per group")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"expert_parallel_fwd_{shape.name}_w{world}", "tokens_per_gpu": 8192,
+                   "top_k": top_k, "experts": experts, "k": shape.k, "n": shape.n,
+                   "reference": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed), one host"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
