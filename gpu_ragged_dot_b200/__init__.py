@@ -9,15 +9,18 @@ from .ops import (  # noqa: F401
     DEFAULT_BLOCK_N,
     BlockSizes,
     GMMGroupLookupMetadata,
+    RaggedDotDimensionNumbers,
     RaggedDotSizes,
     gmm,
     gmm_forward,
     make_group_metadata,
     ragged_dot,
+    ragged_dot_general,
     ragged_dot_permuted,
     tgmm,
     tgmm_forward,
     trans_ragged_dot,
 )
 
-__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted", "HostRaggedDot"]
+__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted", "HostRaggedDot",
+           "ragged_dot_general", "RaggedDotDimensionNumbers"]

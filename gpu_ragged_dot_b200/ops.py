@@ -21,7 +21,7 @@ Differences from the reference, all deliberate:
 from __future__ import annotations
 
 import ctypes
-from typing import NamedTuple, Optional
+from typing import NamedTuple, Optional, Sequence
 
 import torch
 
@@ -33,6 +33,8 @@ __all__ = [
     "tgmm",
     "ragged_dot",
     "trans_ragged_dot",
+    "ragged_dot_general",
+    "RaggedDotDimensionNumbers",
     "make_group_metadata",
     "GMMGroupLookupMetadata",
     "RaggedDotSizes",
@@ -778,6 +780,47 @@ def tgmm(
 
 ragged_dot = gmm
 trans_ragged_dot = tgmm
+
+
+class RaggedDotDimensionNumbers(NamedTuple):
+    """Same fields as ``jax.lax.RaggedDotDimensionNumbers``, the argument of the op the reference
+    is tested against (tests.py:31-36): ``dot_dimension_numbers`` is
+    ``((lhs_contracting, rhs_contracting), (lhs_batch, rhs_batch))``."""
+
+    dot_dimension_numbers: tuple
+    lhs_ragged_dimensions: Sequence[int]
+    rhs_group_dimensions: Sequence[int]
+
+
+def ragged_dot_general(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor,
+                       ragged_dot_dimension_numbers: RaggedDotDimensionNumbers, **kwargs) -> torch.Tensor:
+    """The two modes of ``jax.lax.ragged_dot_general`` that the reference implements, chosen by
+    dimension numbers as its tests spell them (tests.py:31-48):
+
+    * ragged non-contracting dimension -- lhs ``[m, k]`` ragged in dim 0, rhs ``[g, k, n]`` (or
+      ``[g, n, k]`` when the rhs contracting dimension is 2) with group dimension 0 -> ``gmm``;
+    * ragged contracting dimension -- lhs ``[m, k]`` and rhs ``[m, n]`` contracted over dim 0, which
+      is the ragged one, no rhs group dimension -> ``tgmm``, result ``[g, k, n]``.
+
+    Batch dimensions and the ragged-batch mode are not built and raise ``NotImplementedError``.
+    ``kwargs`` are passed on (``block_*`` hints and so on)."""
+    dn = ragged_dot_dimension_numbers
+    (lhs_c, rhs_c), (lhs_b, rhs_b) = dn.dot_dimension_numbers
+    lhs_c, rhs_c = [int(d) for d in lhs_c], [int(d) for d in rhs_c]
+    ragged = [int(d) for d in dn.lhs_ragged_dimensions]
+    groups = [int(d) for d in dn.rhs_group_dimensions]
+    if len(lhs_b) or len(rhs_b):
+        raise NotImplementedError("ragged_dot_general: batch dimensions are not supported")
+    if lhs.dim() != 2 or ragged != [0] or len(lhs_c) != 1 or len(rhs_c) != 1:
+        raise NotImplementedError(
+            "ragged_dot_general: lhs must be [m, k] (or [m, n]) with ragged dimension 0 and one "
+            f"contracting dimension, got {lhs.dim()=} {ragged=} {lhs_c=} {rhs_c=}")
+    if groups == [0] and lhs_c == [1] and rhs.dim() == 3 and rhs_c[0] in (1, 2):
+        return gmm(lhs, rhs, group_sizes, trans_rhs=(rhs_c[0] == 2), **kwargs)
+    if groups == [] and lhs_c == [0] and rhs_c == [0] and rhs.dim() == 2:
+        return tgmm(lhs, rhs, group_sizes, **kwargs)
+    raise NotImplementedError(
+        f"ragged_dot_general: unsupported dimension numbers {dn} for shapes {tuple(lhs.shape)}, {tuple(rhs.shape)}")
 
 
 def device_status(workspace: torch.Tensor) -> int:

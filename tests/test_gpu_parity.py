@@ -767,3 +767,25 @@ def test_float32_vjp_and_tile_widths():
     dx_ref, dA_ref = oracle.ragged_dot_vjp(x, A, gs, dout)
     assert float(oracle.rel_l2_err(xd.grad.cpu(), dx_ref, axis=-1, mask=rows).max()) < 2e-3
     assert float(oracle.rel_l2_err(Ad.grad.cpu(), dA_ref, axis=(-1, -2), mask=gs != 0).max()) < 2e-3
+
+
+def test_ragged_dot_general_matches_oracle():
+    """ragged_dot_general with the dimension numbers of the reference's own oracle calls
+    (tests.py:31-48): both modes, and the rhs-transposed form of the first."""
+    m, k, n, g = 300, 136, 200, 5
+    rng = np.random.default_rng(21)
+    bf = lambda a: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16)  # noqa: E731
+    x, A, y = bf(rng.standard_normal((m, k))), bf(rng.standard_normal((g, k, n)) / np.sqrt(k)), bf(rng.standard_normal((m, n)))
+    gs = torch.tensor([100, 0, 57, 120, 3], dtype=torch.int32)
+    DN = rd.RaggedDotDimensionNumbers
+    got = rd.ragged_dot_general(x.to(DEV), A.to(DEV), gs.to(DEV), DN((([1], [1]), ([], [])), [0], [0]))
+    want = oracle.ragged_dot(x, A, gs)
+    ok, worst = oracle.allclose_report(got.cpu(), want, 2e-2, 2e-2)
+    assert ok, worst
+    At = A.transpose(1, 2).contiguous()
+    got = rd.ragged_dot_general(x.to(DEV), At.to(DEV), gs.to(DEV), DN((([1], [2]), ([], [])), [0], [0]))
+    ok, worst = oracle.allclose_report(got.cpu(), want, 2e-2, 2e-2)
+    assert ok, worst
+    got = rd.ragged_dot_general(x.to(DEV), y.to(DEV), gs.to(DEV), DN((([0], [0]), ([], [])), [0], []))
+    ok, worst = oracle.allclose_report(got.cpu(), oracle.trans_ragged_dot(x, y, gs), 2e-2, 2e-2)
+    assert ok, worst

@@ -94,3 +94,22 @@ def test_host_pipeline_chunk_plan():
     assert plan_chunks([], 4) == []
     with pytest.raises(ValueError):
         plan_chunks(sizes, 0)
+
+
+def test_ragged_dot_general_dimension_numbers():
+    """Dimension numbers the op does not cover are refused before any device work; the two it
+    covers reach gmm / tgmm (which then refuse CPU tensors: there is no CPU path)."""
+    x, A, y = torch.zeros(8, 4), torch.zeros(2, 4, 6), torch.zeros(8, 6)
+    gs = torch.tensor([3, 5], dtype=torch.int32)
+    DN = rd.RaggedDotDimensionNumbers
+    gmm_dn = DN((([1], [1]), ([], [])), [0], [0])       # tests.py:31-33 of the reference
+    tgmm_dn = DN((([0], [0]), ([], [])), [0], [])       # tests.py:34-36
+    for dn, rhs in ((gmm_dn, A), (tgmm_dn, y), (DN((([1], [2]), ([], [])), [0], [0]), A.transpose(1, 2))):
+        with pytest.raises(RuntimeError, match="no CPU fallback"):
+            rd.ragged_dot_general(x, rhs, gs, dn)
+    for dn, rhs in ((DN((([1], [1]), ([0], [0])), [0], [0]), A),   # batch dimensions
+                    (DN((([1], [1]), ([], [])), [1], [0]), A),     # ragged in the contracting dim of a 3-D rhs
+                    (DN((([0], [0]), ([], [])), [0], [0]), y),     # group dimension on a 2-D rhs
+                    (gmm_dn, y)):                                  # gmm numbers, 2-D rhs
+        with pytest.raises(NotImplementedError):
+            rd.ragged_dot_general(x, rhs, gs, dn)
