@@ -150,6 +150,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      const uint64_t keep = l2_policy_evict_last();
       int ready_slot = -1;  // last ready flag this producer has seen set
       uint64_t waited_ns = 0;
       const uint64_t t_start = kEp ? global_timer_ns() : 0;
@@ -183,12 +184,12 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (kTgmm) {
             const int r = t.row0 + kb * kTileK;
             for (int h = 0; h < halves; ++h) {
-              tma_load_2d(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r);
-              tma_load_2d(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r);
+              tma_load_2d_hint(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r, keep);
+              tma_load_2d_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r, keep);
             }
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * kBoxBytes, &tmap_b, full, t.n0 + j * 64, r);
+              tma_load_2d_hint(sb + j * kBoxBytes, &tmap_b, full, t.n0 + j * 64, r, keep);
           } else {
             for (int h = 0; h < halves; ++h)
               tma_load_2d(sa + h * kHalfABytes, &tmap_a, full, kb * kTileK, t.row0 + h * kTileM);
@@ -311,6 +312,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t buf = stage_base + kStages * kG2StageBytes + (warp - 2) * kOutBoxBytes;
     uint32_t uses = 0;
     bool ok = true;
+    const uint64_t stream_out = l2_policy_evict_first();
     uint16_t* out16 = reinterpret_cast<uint16_t*>(p.out);
     for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
@@ -387,7 +389,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
           if (lane == 0) {
             if (kTgmm) {
-              tma_store_3d(&tmap_out, buf, col, out_row0, t.group);
+              tma_store_3d_hint(&tmap_out, buf, col, out_row0, t.group, stream_out);
             } else {
               tma_store_2d(&tmap_out, buf, col, out_row0);
             }
