@@ -64,6 +64,8 @@ class ClockSampler:
         self.index = index
         self.period = period_s
         self.samples = []
+        self.power_w = []
+        self.power_limit_w = None
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -78,6 +80,10 @@ class ClockSampler:
             self._nvml = pynvml
             self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            try:
+                self.power_limit_w = pynvml.nvmlDeviceGetEnforcedPowerLimit(self._h) / 1000.0
+            except Exception:
+                self.power_limit_w = None
         except Exception:
             self._nvml = None
             return self
@@ -101,6 +107,7 @@ class ClockSampler:
                 for k, bit in names.items():
                     if mask & bit:
                         self.reasons.add(k)
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
             except Exception:
                 pass
             time.sleep(self.period)
@@ -114,6 +121,11 @@ class ClockSampler:
             "sm_max_mhz": self.max_mhz,
             "reasons": sorted(self.reasons),
             "samples": len(self.samples),
+            # board power beside the clock: these kernels pull the board to its power limit within
+            # milliseconds, and the clock drops with it before NVML's reason bits show the cap
+            "power_w": statistics.median(self.power_w) if self.power_w else None,
+            "power_max_w": max(self.power_w) if self.power_w else None,
+            "power_limit_w": self.power_limit_w,
         }
 
 
