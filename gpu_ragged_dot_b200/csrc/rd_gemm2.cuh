@@ -28,6 +28,10 @@ constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps;
 constexpr int kG2Stages = 3;
 constexpr int kG2TileN = 256;
 constexpr int kG2TileRows = 2 * kTileM;
+#ifndef RD_G2_TGMM_BAND
+#define RD_G2_TGMM_BAND 8
+#endif
+constexpr int kG2TgmmBand = RD_G2_TGMM_BAND;  // column tiles per band of the tgmm tile order
 constexpr uint32_t kG2ABytes = 2 * kTileM * kTileK * 2;   // two 128-row halves
 constexpr uint32_t kG2BBytes = kG2TileN * kTileK * 2;
 constexpr uint32_t kG2StageBytes = kG2ABytes + kG2BBytes;  // 64 KB
@@ -57,8 +61,15 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int 
   const int per_group = p.k_tiles * p.n_tiles;
   const int gi = tile / per_group;
   const int rem = tile - gi * per_group;
-  const int kt = rem / p.n_tiles;
-  const int nt = rem - kt * p.n_tiles;
+  // Column tiles are taken in bands of kG2TgmmBand: consecutive tiles (= CTAs running at the same
+  // time) walk all k tiles of one band before the next band, so a wave of CTAs shares about
+  // k_tiles + band operand panels instead of n_tiles + a few.
+  const int band_tiles = p.k_tiles * kG2TgmmBand;
+  const int band = rem / band_tiles;
+  const int in_band = rem - band * band_tiles;
+  const int width = imin(kG2TgmmBand, p.n_tiles - band * kG2TgmmBand);
+  const int kt = in_band / width;
+  const int nt = band * kG2TgmmBand + (in_band - kt * width);
   TileCoord t;
   t.group = gi;
   t.weight = gi;
