@@ -36,7 +36,7 @@ if ROOT not in sys.path:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel on this workload, from
 # the ncu captures summarised in profiles/ragged_gemm_mixtral_m8192_k4096_n14336_g8.md.
 DRAM_TRAFFIC_BYTES_PER_LAUNCH = {"fwd": 1.140598e9 + 229.923328e6, "dlhs": 1.588072e9 + 60.262912e6,
-                                 "drhs": 735.026432e6 + 894.027776e6}
+                                 "drhs": 332.787968e6 + 884.06144e6}
 
 METRIC = "ragged_dot fwd+bwd TFLOP/s (2*m*k*n useful flops per GEMM)"
 UNIT = "TFLOP/s"
