@@ -8,8 +8,9 @@ One JSON line on stdout (rank 0).  N = 1: one step is ragged_dot forward + its f
 (dlhs through the transposed grouped GEMM, drhs through tgmm) on the Mixtral-8x7B-shaped
 workload, m=8192, k=4096, n=14336, g=8, bf16 with fp32 accumulation; `value` counts useful
 flops, 2*m*k*n per GEMM.  N > 1 (torchrun): the expert-parallel workload -- per GPU 8192
-tokens x top-4 routing over 64 experts sharded 64/N per GPU, NCCL all-to-all of the rows, then
-the local ragged_dot.
+tokens x top-4 routing over 64 experts sharded 64/N per GPU, the rows exchanged over NVLink, the
+local ragged_dot, and its backward (dlhs on the owner + the return exchange, drhs per local
+expert): forward + backward, the same three GEMMs per row as at N = 1.
 
 `--impl reference` times the CPU oracle (oracle/ragged_dot_oracle.py, the restatement of the
 reference semantics; jax is not installed, so jax.lax.ragged_dot on XLA-CPU cannot run) on a
@@ -33,10 +34,20 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel on this workload, from
-# the ncu captures summarised in profiles/ragged_gemm_mixtral_m8192_k4096_n14336_g8.md.
-DRAM_TRAFFIC_BYTES_PER_LAUNCH = {"fwd": 1.140598e9 + 229.923328e6, "dlhs": 1.588072e9 + 60.262912e6,
-                                 "drhs": 332.787968e6 + 884.06144e6}
+
+
+def dram_traffic_per_launch():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of each kernel on the Mixtral
+    workload, from the profiler capture whose figures are kept in a small JSON file beside its
+    summary; None for a kernel that file does not list."""
+    path = os.path.join(ROOT, "profiles", "ragged_gemm_mixtral_dram_traffic.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(v["dram_read_bytes"]) + float(v["dram_write_bytes"]) for k, v in d["kernels"].items()}
+    except Exception:
+        return {}
+
 
 METRIC = "ragged_dot fwd+bwd TFLOP/s (2*m*k*n useful flops per GEMM)"
 UNIT = "TFLOP/s"
@@ -147,28 +158,44 @@ def dist_env():
 
 
 # ---------------------------------------------------------------------------- reference arm (CPU)
+def mixtral_config(shape, only, rows_per_step):
+    """`config` of the N = 1 line, identical for both arms when both run the whole workload."""
+    return {
+        "workload": shape.name + ("_fwd_bwd" if only is None else "_" + only),
+        "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
+        "group_sizes": "fwd: multinomial(Dirichlet(2)); bwd: same, each group at a random offset mod 128",
+        "rows_per_step": rows_per_step,
+        "l2": "inputs larger than L2 (weights %d MB per GEMM)" % (shape.g * shape.k * shape.n * 2 // 1000000),
+    }
+
+
 def cpu_oracle_sample(shape, rows, threads, seed=0):
-    """Inputs for a CPU run on the first `rows` rows of the workload (group sizes scaled)."""
+    """Inputs for a CPU run on the first `rows` rows of the workload: the forward's and the
+    backward's group sizes of our arm, scaled when rows < m."""
     from gpu_ragged_dot_b200 import workloads
 
-    gs_full = workloads.group_sizes_mixtral_ragged(seed).astype(np.int64)
-    gs = (gs_full * rows) // shape.m
-    gs[-1] += rows - gs.sum()
+    def scaled(gs_full):
+        gs = (gs_full.astype(np.int64) * rows) // shape.m
+        gs[-1] += rows - gs.sum()
+        return torch.from_numpy(gs.astype(np.int32))
+
+    gs_fwd, gs_bwd = scaled(workloads.group_sizes_mixtral(seed)), scaled(workloads.group_sizes_mixtral_ragged(seed))
     x = workloads.normal_tensor((rows, shape.k), 1.0, 11, "cpu")
     A = workloads.normal_tensor((shape.g, shape.k, shape.n), shape.k ** -0.5, 12, "cpu")
     dout = workloads.normal_tensor((rows, shape.n), 1.0, 13, "cpu")
-    return x, A, dout, torch.from_numpy(gs.astype(np.int32))
+    return x, A, dout, (gs_fwd, gs_bwd)
 
 
 def cpu_oracle_step(x, A, dout, gs, only=None):
     from oracle import ragged_dot_oracle as oracle
 
+    gs_fwd, gs_bwd = gs if isinstance(gs, tuple) else (gs, gs)
     if only in (None, "fwd"):
-        oracle.ragged_dot(x, A, gs, native_16bit=True)
+        oracle.ragged_dot(x, A, gs_fwd, native_16bit=True)
     if only in (None, "dlhs"):
-        oracle.ragged_dot(dout, A, gs, trans_rhs=True, native_16bit=True)
+        oracle.ragged_dot(dout, A, gs_bwd, trans_rhs=True, native_16bit=True)
     if only in (None, "drhs"):
-        oracle.trans_ragged_dot(x, dout, gs, native_16bit=True)
+        oracle.trans_ragged_dot(x, dout, gs_bwd, native_16bit=True)
 
 
 def run_reference(args):
@@ -184,14 +211,17 @@ def run_reference(args):
         return run_reference_expert_parallel(args, max(world, args.gpus), threads)
     shape = workloads.MIXTRAL
     gemms = 3 if args.only is None else 1
-    # Calibrate on 128 rows, then size the per-step sample so warmup+steps stay near 2 minutes.
-    x, A, dout, gs = cpu_oracle_sample(shape, 128, threads)
+    # The whole workload (all 8192 rows) per step whenever warm-up + steps fit about two and a half
+    # minutes; otherwise the largest multiple of 128 rows that does.  The probe runs twice: the
+    # first call pays for oneDNN's set-up and the first touch of 940 MB of weights.
+    x, A, dout, gs = cpu_oracle_sample(shape, 1024, threads)
+    cpu_oracle_step(x, A, dout, gs, args.only)
     t0 = time.perf_counter()
     cpu_oracle_step(x, A, dout, gs, args.only)
     t_probe = time.perf_counter() - t0
-    budget = 120.0 / max(args.steps + args.warmup, 1)
-    rows = int(min(shape.m, max(128, 128 * budget / max(t_probe, 1e-3))))
-    rows = max(128, (rows // 128) * 128)
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    rows = int(min(shape.m, max(128, 1024 * budget / max(t_probe, 1e-3))))
+    rows = shape.m if rows >= shape.m else max(128, (rows // 128) * 128)
     x, A, dout, gs = cpu_oracle_sample(shape, rows, threads)
     for _ in range(args.warmup):
         cpu_oracle_step(x, A, dout, gs, args.only)
@@ -201,7 +231,8 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / max(args.steps, 1)
     flops = 2.0 * rows * shape.k * shape.n * gemms
     value = flops / dt / 1e12
-    sample = (f"rows 0..{rows - 1} of {shape.m} (group sizes scaled), all {shape.g} experts' weights, "
+    sample = (("the whole workload: " if rows == shape.m else "") +
+              f"rows 0..{rows - 1} of {shape.m} (group sizes {'as in our arm' if rows == shape.m else 'scaled'}), all {shape.g} experts' weights, "
               f"{'fwd+dlhs+drhs' if args.only is None else args.only} per step; torch CPU bf16 matmul (oneDNN, fp32 accumulate) per group")
     line = {
         "impl": "reference",
@@ -217,8 +248,8 @@ def run_reference(args):
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": shape.name + "_fwd_bwd", "m": shape.m, "k": shape.k, "n": shape.n,
-                   "g": shape.g, "reference": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed)"},
+        "config": mixtral_config(shape, args.only, rows),
+        "method": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed); wall clock around the steps",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -227,54 +258,72 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def ep_config(shape, world, tokens, top_k, experts, tokens_per_step):
+    """`config` of the N > 1 line, identical for both arms when the CPU arm runs every token."""
+    return {"workload": f"expert_parallel_fwd_bwd_{shape.name}_w{world}", "tokens_per_gpu": tokens,
+            "top_k": top_k, "experts": experts, "experts_per_gpu": experts // world, "k": shape.k, "n": shape.n,
+            "tokens_per_step": tokens_per_step,
+            "l2": "inputs larger than L2 (268 MB of rows per GPU)"}
+
+
 def run_reference_expert_parallel(args, world, threads):
-    """Reference arm of the N > 1 workload (expert-parallel forward): the same routing, permutation
-    by expert and ragged_dot over all 64 experts, on the host cores of rank 0.  There is no
-    exchange on one host; each step is a bounded sample of the job's tokens."""
+    """Reference arm of the N > 1 workload (expert-parallel forward + backward): the same routing,
+    permutation by expert, ragged_dot over all 64 experts, and its VJP as the reference wires it
+    (dlhs through the transposed product, summed over a token's copies; drhs through tgmm), on
+    the host cores of rank 0.  There is no exchange on one host.  A step covers every token of the
+    job when warm-up + steps fit about two and a half minutes, else a bounded sample of them."""
     from gpu_ragged_dot_b200 import workloads
     from oracle import ragged_dot_oracle as oracle
 
     shape = workloads.EP_PREFILL
-    tokens_job, top_k, experts = 8192 * world, 4, shape.g
+    tokens_gpu, top_k, experts = 8192, 4, shape.g
+    tokens_job = tokens_gpu * world
     A = workloads.normal_tensor((experts, shape.k, shape.n), shape.k ** -0.5, 12, "cpu")
 
     def make(tokens):
         x = workloads.normal_tensor((tokens, shape.k), 1.0, 11, "cpu")
         routing = torch.from_numpy(workloads.topk_routing(tokens, experts, top_k, seed=3000)).to(torch.int64)
-        return x, routing
+        dy = workloads.normal_tensor((tokens * top_k, shape.n), 1.0, 13, "cpu")
+        return x, routing, dy
 
-    def step(x, routing):
+    def step(x, routing, dy):
         flat = routing.reshape(-1)
         order = torch.argsort(flat, stable=True)
         gs = torch.bincount(flat, minlength=experts).to(torch.int32)
-        rows = x.index_select(0, order // top_k)
-        return oracle.ragged_dot(rows, A, gs, native_16bit=True)
+        token_of_row = order // top_k
+        rows = x.index_select(0, token_of_row)
+        y = oracle.ragged_dot(rows, A, gs, native_16bit=True)
+        d_rows = oracle.ragged_dot(dy, A, gs, trans_rhs=True, native_16bit=True)
+        dx = torch.zeros((x.shape[0], shape.k), dtype=torch.float32).index_add_(0, token_of_row, d_rows.float())
+        dA = oracle.trans_ragged_dot(rows, dy, gs, native_16bit=True)
+        return y, dx.to(torch.bfloat16), dA
 
-    x, routing = make(256)
-    step(x, routing)
+    probe = make(2048)
+    step(*probe)
     t0 = time.perf_counter()
-    step(x, routing)
+    step(*probe)
     t_probe = time.perf_counter() - t0
-    budget = 120.0 / max(args.steps + args.warmup, 1)
-    tokens = int(min(tokens_job, max(256, 256 * budget / max(t_probe, 1e-3))))
-    tokens = max(256, (tokens // 256) * 256)
-    x, routing = make(tokens)
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    tokens = int(min(tokens_job, max(256, 2048 * budget / max(t_probe, 1e-3))))
+    tokens = tokens_job if tokens >= tokens_job else max(256, (tokens // 256) * 256)
+    data = make(tokens)
     for _ in range(args.warmup):
-        step(x, routing)
+        step(*data)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        step(x, routing)
+        step(*data)
     dt = (time.perf_counter() - t0) / max(args.steps, 1)
-    value = 2.0 * tokens * top_k * shape.k * shape.n / dt / 1e12
-    sample = (f"{tokens} of the job's {tokens_job} tokens x top-{top_k} per step: sort by expert, gather rows, "
-              f"ragged_dot over all {experts} experts' weights; torch CPU bf16 matmul (oneDNN, fp32 accumulate) per group")
+    value = 3 * 2.0 * tokens * top_k * shape.k * shape.n / dt / 1e12
+    sample = (("every token of the job: " if tokens == tokens_job else "") +
+              f"{tokens} of the job's {tokens_job} tokens x top-{top_k} per step: sort by expert, gather rows, "
+              f"ragged_dot over all {experts} experts' weights, dlhs + top-k combine, drhs; torch CPU bf16 matmul "
+              "(oneDNN, fp32 accumulate) per group")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"expert_parallel_fwd_{shape.name}_w{world}", "tokens_per_gpu": 8192,
-                   "top_k": top_k, "experts": experts, "k": shape.k, "n": shape.n,
-                   "reference": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed), one host"},
+        "config": ep_config(shape, world, tokens_gpu, top_k, experts, tokens),
+        "method": "CPU restatement of jax.lax.ragged_dot semantics (jax not installed), one host; wall clock",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -359,7 +408,7 @@ def run_single(args):
         tf = gemm_flops / (ms * 1e-3) / 1e12
         per_kernel[name] = {"ms": ms, "tflops": tf, "frac_of_measured_burst": tf / peaks["bf16_tflops"],
                             "frac_of_measured_sustained": tf / peaks["bf16_tflops_sustained"]}
-    traffic = DRAM_TRAFFIC_BYTES_PER_LAUNCH if args.workload == "mixtral" else {}
+    traffic = dram_traffic_per_launch() if args.workload == "mixtral" else {}
     gplus_f, gplus_b = int((gs_fwd_np > 0).sum()), int((gs_bwd_np > 0).sum())
     alg_bytes = {
         "fwd": 2.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
@@ -412,15 +461,14 @@ def run_single(args):
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": {
+        "config": (mixtral_config(shape, args.only, shape.m) if args.workload == "mixtral" else {
             "workload": shape.name + ("_fwd_bwd" if args.only is None else "_" + args.only),
             "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
-            "group_sizes": {"mixtral": "fwd: multinomial(Dirichlet(2)); bwd: same, each group at a random offset mod 128",
-                            "decode": "64 tokens x uniform top-4 of 64 experts",
+            "group_sizes": {"decode": "64 tokens x uniform top-4 of 64 experts",
                             "deepseek": "multinomial(Dirichlet(0.3)), ~20% empty"}[args.workload],
             "l2": "inputs larger than L2 (weights %d MB per GEMM)" % (shape.g * shape.k * shape.n * 2 // 1000000),
-            "timing": "CUDA events on the launch stream; per-kernel events inside the timed region",
-        },
+        }),
+        "method": "CUDA events on the launch stream; per-kernel events inside the timed region",
         "clocks": clocks,
         "gpu_launches": 2 * len(kernels) * args.steps,
         "roofline": roofline,
@@ -668,6 +716,7 @@ def run_cpu_baseline(shape, kernels):
     x, A, dout, gs = cpu_oracle_sample(shape, rows, threads)
     only = None if len(kernels) == 3 else kernels[0]
     cpu_oracle_step(x[:128], A, dout[:128], torch.tensor([16] * shape.g, dtype=torch.int32), only)  # warm-up
+    cpu_oracle_step(x, A, dout, gs, only)
     t0 = time.perf_counter()
     reps = 0
     while reps < 3 and time.perf_counter() - t0 < 20.0:
@@ -682,14 +731,84 @@ def run_cpu_baseline(shape, kernels):
 
 
 # ---------------------------------------------------------------------------- our arm, N > 1
-def run_expert_parallel(args):
-    """N > 1: expert parallel forward.  Three dispatch modes are timed on the same inputs ("overlap":
-    ring-phased peer stores running under the flag-gated local GEMM), among them:
-    "nccl" (sort + gather + NCCL all-to-all with host-known split sizes) and "p2p" (device-side
-    plan + rows stored straight into the owners' receive buffers through peer memory, no host
-    round trip).  `value` is the faster one; both are reported."""
+EP_MODES = ("nccl", "p2p", "fused")
+EP_COLLECTIVE = {
+    "nccl": "NCCL all-to-all (rows, both directions) + all-to-all (counts)",
+    "p2p": "NCCL all-gather (counts) + peer stores over NVLink + symmetric-memory barrier; gradient rows pulled "
+           "back with peer loads",
+    "fused": "NCCL all-gather (counts) + ONE kernel whose sender CTAs store rows to the peers over NVLink (ring "
+             "phases) while its other CTAs multiply the rows that have arrived (ready flags); gradient rows pulled "
+             "back with peer loads after a symmetric-memory barrier",
+}
+# our kernels per step (forward + backward), collectives and torch's own kernels not counted
+EP_LAUNCHES = {"nccl": 1 + 2 + 2 + 2, "p2p": 4 + 2 + 2 + 2 + 1, "fused": 6 + 2 + 2 + 1}
+
+
+def ep_parity_check(layer, mode, out, dy, dx, dW, routing, world, dev, sample_tokens=48):
+    """Outside the timed region: does this rank's result agree with an independent computation?
+    Every segment of the receive buffer is copied into an ordinary tensor and multiplied with torch
+    in fp32 on this GPU: y and the gradient rows (dlhs) of ALL received rows and the dW of every
+    local expert must agree within rtol/atol 2e-2.  The return exchange is checked on the first
+    `sample_tokens` tokens: their top_k gradient rows are fetched from the owners' buffers with
+    peer memcpys and summed in fp32 in slot order, which dx must equal bit for bit.  Returns a
+    dict, all-reduced over the ranks (worst case)."""
     import torch.distributed as dist
-    from gpu_ragged_dot_b200 import _lib, ep, workloads
+
+    El, W = layer.local_experts, world
+    sv = layer._saved
+    seg = sv["plan"].segment_sizes if mode == "nccl" else sv["seg"]
+    recv, y = sv["recv"], out[0]
+    d_rows = None if mode == "nccl" else layer._grad["buf"]
+    offs = np.concatenate([[0], np.cumsum(seg.cpu().tolist())])
+    ratio = lambda got, want: float(((got.float() - want).abs() / (2e-2 + 2e-2 * want.abs())).max()) if want.numel() else 0.0
+    worst = [0.0, 0.0, 0.0, 0.0]  # y, dlhs, dW, dx mismatches
+    for j in range(El):
+        wj = layer.weights[j].float()
+        want_dW = torch.zeros((layer.k, layer.n), dtype=torch.float32, device=dev)
+        for q in range(W):
+            lo, hi = int(offs[q * El + j]), int(offs[q * El + j + 1])
+            rows = recv[lo:hi].clone().float()
+            g_rows = dy[lo:hi].float()
+            want_dW += rows.T @ g_rows
+            worst[0] = max(worst[0], ratio(y[lo:hi], (rows @ wj).to(torch.bfloat16).float()))
+            if d_rows is not None:
+                worst[1] = max(worst[1], ratio(d_rows[lo:hi], (g_rows @ wj.T).to(torch.bfloat16).float()))
+        worst[2] = max(worst[2], ratio(dW[j], want_dW.to(torch.bfloat16).float()))
+    dx_checked = 0
+    if mode != "nccl":
+        hdl, cap = layer._grad["hdl"], layer._grad["capacity"]
+        peers = [layer._grad["buf"] if (hdl is None or r == layer.rank) else
+                 hdl.get_buffer(r, (cap, layer.k), layer.dtype) for r in range(W)]
+        r_cpu = sv["routing"].cpu()
+        p_cpu = sv["dest_pos"].reshape(r_cpu.shape).cpu()
+        top_k = r_cpu.shape[1]
+        for t in range(min(sample_tokens, r_cpu.shape[0])):
+            acc = torch.zeros(layer.k, dtype=torch.float32, device=dev)
+            for s_ in range(top_k):
+                e, pos = int(r_cpu[t, s_]), int(p_cpu[t, s_])
+                row = torch.empty((1, layer.k), dtype=layer.dtype, device=dev)
+                row.copy_(peers[e // El][pos:pos + 1])  # a peer-to-peer memcpy of one row
+                acc += row[0].float()
+            worst[3] += float(not torch.equal(acc.to(layer.dtype).view(torch.int16), dx[t].view(torch.int16)))
+            dx_checked += 1
+    w = torch.tensor(worst, dtype=torch.float64, device=dev)
+    dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    res = {"y_worst_ratio": float(w[0]), "dlhs_worst_ratio": float(w[1]) if d_rows is not None else None,
+           "dW_worst_ratio": float(w[2]), "dx_tokens_checked_per_rank": dx_checked,
+           "dx_mismatching_tokens": int(w[3]) if dx_checked else None,
+           "tolerance": "|a-b| <= 2e-2 + 2e-2|b| against torch fp32 on the same GPU; dx bit-exact on the sample"}
+    res["ok"] = bool(float(w[0]) <= 1.0 and float(w[1]) <= 1.0 and float(w[2]) <= 1.0 and float(w[3]) == 0.0)
+    return res
+
+
+def run_expert_parallel(args):
+    """N > 1: expert-parallel forward + backward.  Three dispatch modes are timed on the same
+    inputs: "nccl" (sort + gather + NCCL all-to-all with host-known split sizes; the baseline),
+    "p2p" (device-side plan + rows stored straight into the owners' receive buffers through peer
+    memory, no host round trip) and "fused" (the exchange inside the GEMM launch).  `value` is the
+    fastest; all are reported, each with a parity check made outside the timed region."""
+    import torch.distributed as dist
+    from gpu_ragged_dot_b200 import _lib, ep, ops, workloads
 
     _lib.load()
     rank, world, local = dist_env()
@@ -701,13 +820,17 @@ def run_expert_parallel(args):
     x_tokens = workloads.normal_tensor((tokens, shape.k), 1.0, 1000 + rank, dev)
     routing = torch.from_numpy(workloads.topk_routing(tokens, experts, top_k, seed=3000 + rank)).to(dev)
     peaks = measured_peaks()
-    results = {}
+    results, parity, local_only = {}, {}, None
     clocks = None
-    for mode in ("nccl", "p2p", "overlap", "fused"):
+    warm = max(args.warmup, 3)
+    for mode in EP_MODES:
         try:
             layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode)
-            for _ in range(max(args.warmup, 3)):
-                layer.forward(x_tokens, routing)
+            out = layer.forward(x_tokens, routing)
+            dy = workloads.normal_tensor(tuple(out[0].shape), 1.0, 4000 + rank, dev)
+            for _ in range(warm):
+                out = layer.forward(x_tokens, routing)
+                dx, dW = layer.backward(dy)
             torch.cuda.synchronize()
             ok = torch.ones(1, device=dev)
         except Exception as e:  # e.g. no peer access for symmetric memory
@@ -717,6 +840,7 @@ def run_expert_parallel(args):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if float(ok) == 0:
             continue
+        parity[mode] = ep_parity_check(layer, mode, out, dy, dx, dW, routing, world, dev)
         dist.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(physical_gpu_index(local)).start()
@@ -725,31 +849,44 @@ def run_expert_parallel(args):
         e0.record()
         for _ in range(args.steps):
             layer.forward(x_tokens, routing, timed=True)
+            layer.backward(dy, timed=True)
         e1.record()
         torch.cuda.synchronize()
         dist.barrier()
         clocks = sampler.stop()
         ms = e0.elapsed_time(e1) / args.steps
         parts = layer.timers_ms(args.steps)
-        if mode in ("overlap", "fused"):
-            # a bounded wait that expired inside a kernel (status word != 0) makes the timing meaningless
-            from gpu_ragged_dot_b200 import ops as _ops
-            bad = torch.tensor([float(_ops.device_status(layer._ov["ws"]) != 0)], device=dev)
-            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
-            if float(bad) != 0:
-                if rank == 0:
-                    sys.stderr.write(f"bench: dispatch mode {mode} dropped: a device-side wait expired\n")
-                del layer
-                torch.cuda.empty_cache()
-                continue
-        t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"], parts.get("own_rows", 0.0)],
+        bparts = layer.backward_timers_ms(args.steps)
+        bad = torch.tensor([float(layer.device_status() != 0)], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if float(bad) != 0:
+            raise RuntimeError(f"dispatch mode {mode}: a device-side wait expired inside the timed region")
+        t = torch.tensor([ms, parts["gemm"], parts["a2a"], parts["permute"], parts.get("own_rows", 0.0),
+                          bparts["dlhs_gemm"], bparts["drhs_tgmm"], bparts["return_exchange_and_combine"]],
                          dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         results[mode] = t.tolist()
-        del layer
+        if mode == "fused":
+            # The same per-GPU work with nothing to exchange: the three GEMMs over the rows that are in
+            # the receive buffer, on this GPU alone (what a step would cost if the exchange were free).
+            sv, cfg = layer._saved, _lib.TileCfg(0, 0, 0, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+            ybuf, dbuf = layer._ring["y"], layer._grad["buf"]
+            ws1, ws2 = layer._grad["ws"], layer._grad["ws_tgmm"]
+
+            def local_step():
+                ops.gmm_forward(sv["recv"], layer.weights, sv["seg"], group_to_weight=sv["seg2e"], cfg=cfg,
+                                out=ybuf, workspace=ws1)
+                ops.gmm_forward(dy, layer.weights, sv["seg"], trans_rhs=True, group_to_weight=sv["seg2e"], cfg=cfg,
+                                out=dbuf, workspace=ws1)
+                ops.tgmm_forward(sv["recv"], dy, sv["seg"], seg_count=world, workspace=ws2)
+
+            lt = torch.tensor([_time_ms(local_step, max(args.steps, 5))], dtype=torch.float64, device=dev)
+            dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+            local_only = float(lt[0])
+        del layer, out, dy, dx, dW
         torch.cuda.empty_cache()
     # Decode-shaped case of the same expert layout: 64 tokens x top-4 per GPU (m = 256 rows per rank),
-    # weight-bandwidth bound on every rank.  Timed with the two host-sync-free modes.
+    # weight-bandwidth bound on every rank.  Forward only, timed with the two host-sync-free modes.
     decode = {}
     d_tokens = 64
     xd = workloads.normal_tensor((d_tokens, shape.k), 1.0, 5000 + rank, dev)
@@ -758,7 +895,7 @@ def run_expert_parallel(args):
         try:
             layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode,
                                                capacity_rows=d_tokens * top_k * world)
-            for _ in range(max(args.warmup, 3)):
+            for _ in range(warm):
                 out = layer.forward(xd, rd_)
             torch.cuda.synchronize()
             ok = torch.ones(1, device=dev)
@@ -779,8 +916,8 @@ def run_expert_parallel(args):
         e1.record()
         torch.cuda.synchronize()
         dist.barrier()
-        local = experts // world
-        touched = int((seg.view(world, local).sum(0) > 0).sum())  # local experts with at least one row
+        n_local = experts // world
+        touched = int((seg.view(world, n_local).sum(0) > 0).sum())  # local experts with at least one row
         t = torch.tensor([e0.elapsed_time(e1) / args.steps, float(touched)], dtype=torch.float64, device=dev)
         tmax = t.clone()
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -790,22 +927,31 @@ def run_expert_parallel(args):
                         "experts_touched": int(t[1])}
         del layer
         torch.cuda.empty_cache()
-    # End to end at N GPUs: every step copies this rank's tokens and routing from pinned host memory,
-    # runs the fastest mode's public forward() and reads the local result rows back to the host.
+    # End to end at N GPUs: every step copies this rank's tokens, routing and the cotangent of the
+    # rows it receives from pinned host memory, runs forward + backward of the fastest mode through
+    # the public host-buffer calls and reads y, dx and dW back to the host.
     e2e = None
     if results:
-        best_t = torch.tensor([results.get(m, [1e30])[0] for m in ("nccl", "p2p", "overlap", "fused")],
-                              dtype=torch.float64, device=dev)
+        best_t = torch.tensor([results.get(m, [1e30])[0] for m in EP_MODES], dtype=torch.float64, device=dev)
         dist.broadcast(best_t, src=0)
-        mode = ("nccl", "p2p", "overlap", "fused")[int(torch.argmin(best_t))]
+        mode = EP_MODES[int(torch.argmin(best_t))]
         layer = ep.ExpertParallelRaggedDot(experts, shape.k, shape.n, dev, seed=2000 + rank, dispatch=mode)
         hx = x_tokens.cpu().pin_memory()
         hr = routing.to(torch.int32).cpu().pin_memory()
-        rows_back = tokens * top_k
-        hy = torch.empty((rows_back, shape.n), dtype=torch.bfloat16).pin_memory()
+        hrows = torch.zeros(1, dtype=torch.int32).pin_memory()
+        cap_rows = tokens * top_k * (world if mode != "nccl" else 1)
+        out = layer.forward(x_tokens, routing)  # untimed: how many rows does this rank receive?
+        torch.cuda.synchronize()
+        rows_valid = int(out[0].shape[0]) if mode == "nccl" else int(out[3].cpu())
+        del out
+        hy = torch.empty((rows_valid, shape.n), dtype=torch.bfloat16).pin_memory()
+        hdy = workloads.normal_tensor((rows_valid, shape.n), 1.0, 4000 + rank, "cpu").pin_memory()
+        hdx = torch.empty((tokens, shape.k), dtype=torch.bfloat16).pin_memory()
+        hdW = torch.empty((experts // world, shape.k, shape.n), dtype=torch.bfloat16).pin_memory()
 
-        def step():  # copy-in of the next step runs under this step's exchange, GEMM and copy-out
-            layer.forward_host(hx, hr, hy)
+        def step():  # copy-in of the next step runs under this step's exchange, GEMMs and copy-out
+            layer.forward_host(hx, hr, hy, rows_host=hrows)
+            layer.backward_host(hdy, rows_valid, hdx, hdW)
 
         for _ in range(2):
             step()
@@ -820,77 +966,74 @@ def run_expert_parallel(args):
         e1.record()
         torch.cuda.synchronize()
         dist.barrier()
+        assert int(hrows[0]) == rows_valid
         t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nb = torch.tensor([hx.numel() * 2 + hr.numel() * 4 + hdy.numel() * 2,
+                           hy.numel() * 2 + hdx.numel() * 2 + hdW.numel() * 2 + 4], dtype=torch.float64, device=dev)
+        dist.all_reduce(nb)
         e2e_ms = float(t[0])
-        e2e = {"value": 2.0 * tokens * top_k * world * shape.k * shape.n / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+        e2e = {"value": 3 * 2.0 * tokens * top_k * world * shape.k * shape.n / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                "ms_per_step": e2e_ms, "steps": e2e_steps, "dispatch": mode,
-               "h2d_bytes_per_step": world * (hx.numel() * 2 + hr.numel() * 4),
-               "d2h_bytes_per_step": world * hy.numel() * 2,
-               "api": "ExpertParallelRaggedDot.forward_host per rank, pinned host buffers (copy-in of step i+1 under step i)"}
+               "h2d_bytes_per_step": float(nb[0]), "d2h_bytes_per_step": float(nb[1]),
+               "api": "ExpertParallelRaggedDot.forward_host + backward_host per rank, pinned host buffers: tokens, "
+                      "routing and the cotangent of the rows the rank receives go in, y (the rows received; their "
+                      "number is fixed by the inputs and was read once before timing), dx and dW come out"}
         del layer
         torch.cuda.empty_cache()
     if rank == 0 and results:
         best = min(results, key=lambda m: results[m][0])
-        ms, gemm_ms, a2a_ms, first_ms, _ = results[best]
+        ms = results[best][0]
         rows_global = tokens * top_k * world
-        flops = 2.0 * rows_global * shape.k * shape.n
-        gemm_tf = 2.0 * tokens * top_k * shape.k * shape.n / (gemm_ms * 1e-3) / 1e12
+        flops = 3 * 2.0 * rows_global * shape.k * shape.n
+        gemm_flops_gpu = 2.0 * tokens * top_k * shape.k * shape.n
         row_bytes_out = tokens * top_k * shape.k * 2 * (world - 1) / world
         modes = {}
-        for m_, (t_ms, g_ms, x_ms, p_ms, own_ms) in results.items():
+        for m_, (t_ms, g_ms, x_ms, p_ms, own_ms, dl_ms, dr_ms, ret_ms) in results.items():
+            fwd = ({"sort_plan_gather": p_ms, "all_to_all": x_ms, "local_ragged_dot": g_ms} if m_ == "nccl" else
+                   {"count_allgather_plan": p_ms, "peer_store_dispatch_and_barrier": x_ms,
+                    "local_ragged_dot": g_ms} if m_ == "p2p" else
+                   {"count_allgather_plan_assign": p_ms, "own_rows_copied_from_plan_end": own_ms,
+                    "fused_send_and_ragged_dot_from_plan_end": g_ms})
             modes[m_] = {
                 "ms_per_step": t_ms, "tflops": flops / (t_ms * 1e-3) / 1e12,
-                "breakdown_ms": ({"sort_plan_gather": p_ms, "all_to_all": x_ms, "local_ragged_dot": g_ms}
-                                 if m_ == "nccl" else
-                                 {"count_allgather_plan": p_ms, "peer_store_dispatch_and_barrier": x_ms,
-                                  "local_ragged_dot": g_ms} if m_ == "p2p" else
-                                 {"count_allgather_plan": p_ms, "peer_store_phases_from_plan_end": x_ms,
-                                  "own_rows_copied_from_plan_end": own_ms,
-                                  "flag_gated_ragged_dot_from_plan_end": g_ms} if m_ == "overlap" else
-                                 {"count_allgather_plan_assign": p_ms, "own_rows_copied_from_plan_end": own_ms,
-                                  "fused_send_and_ragged_dot_from_plan_end": g_ms}),
+                "forward_breakdown_ms": fwd,
+                "backward_breakdown_ms": {"dlhs_gemm_on_the_owner": dl_ms, "drhs_tgmm_per_local_expert": dr_ms,
+                                          "return_exchange_and_topk_combine": ret_ms},
                 # fused: the exchange has no span of its own; rate over the whole send + GEMM kernel
                 ("exchange_GBps_per_gpu_over_the_fused_kernel" if m_ == "fused" else "exchange_GBps_per_gpu"):
                     row_bytes_out / ((g_ms if m_ == "fused" else x_ms) * 1e-3) / 1e9,
+                "return_exchange_GBps_per_gpu": row_bytes_out / (ret_ms * 1e-3) / 1e9,
+                "parity_check": parity.get(m_),
             }
+        # Target of one step per GPU: the three GEMMs at the measured tensor peak, or the two exchanges
+        # at the measured peer-copy bandwidth (770 GB/s per direction per GPU), whichever is slower.
+        target_ms = max(3 * gemm_flops_gpu / (peaks["bf16_tflops"] * 1e9), 2 * row_bytes_out / 770e9 * 1e3)
         line = {
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"expert_parallel_fwd_{shape.name}_w{world}", "tokens_per_gpu": tokens,
-                       "top_k": top_k, "experts": experts, "experts_per_gpu": experts // world,
-                       "k": shape.k, "n": shape.n, "dispatch": best,
-                       "collective": {"nccl": "NCCL all-to-all (rows) + all-to-all (counts)",
-                                      "p2p": "NCCL all-gather (counts) + peer stores over NVLink + symmetric-memory barrier",
-                                      "overlap": "NCCL all-gather (counts) + ring-phased peer stores over NVLink overlapped "
-                                                 "with the local GEMM, which waits per source on ready flags",
-                                      "fused": "NCCL all-gather (counts) + ONE kernel whose sender CTAs store rows to the "
-                                               "peers over NVLink (ring phases) while its other CTAs multiply the rows "
-                                               "that have arrived (ready flags)"}[best],
-                       "l2": "inputs larger than L2 (268 MB of rows per GPU)"},
+            "config": ep_config(shape, world, tokens, top_k, experts, tokens * world),
+            "method": "CUDA events on the launch stream, barrier + synchronize on both sides, max over ranks",
+            "dispatch": best, "collective": EP_COLLECTIVE[best],
             "clocks": clocks,
-            "gpu_launches": {"nccl": 3, "p2p": 5, "overlap": 4 + world, "fused": 6}[best] * args.steps,
-            "roofline": ({"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> (local experts)",
-                          "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                          "frac": gemm_tf / peaks["bf16_tflops"], "traffic": None,
-                          "peak_source": peaks["source"]} if best not in ("overlap", "fused") else
-                         # fused exchange + GEMM: target = slower of flops / GEMM peak and NVLink bytes / 770 GB/s
-                         # (measured peer-copy bandwidth per direction per GPU); achieved is over the span from
-                         # the end of the plan to the end of the GEMM, waits on remote rows included.
-                         {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> gated by ready flags, " +
-                                                      ("sender CTAs in the same launch" if best == "fused"
-                                                       else "ep_dispatch_phase_kernel on a side stream"),
-                          "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                          "target_ms": max(2.0 * tokens * top_k * shape.k * shape.n / (peaks["bf16_tflops"] * 1e9),
-                                           row_bytes_out / 770e9 * 1e3),
-                          "frac": max(2.0 * tokens * top_k * shape.k * shape.n / (peaks["bf16_tflops"] * 1e9),
-                                      row_bytes_out / 770e9 * 1e3) / gemm_ms,
-                          "traffic": None, "peak_source": peaks["source"] + "; NVLink 770 GB/s per direction"}),
+            "gpu_launches": EP_LAUNCHES[best] * args.steps,
+            "parity_check": parity.get(best),
+            "local_only_ms": local_only,
+            "local_only_note": "the same three GEMMs per GPU over the received rows with nothing exchanged: "
+                               "step efficiency on one workload = local_only_ms / ms_per_step",
+            "roofline": {"bound": "tensor", "kernel": "ragged_gemm2_kernel<gmm> (flag-gated, sender CTAs in the "
+                                                      "launch) + <gmm, trans_rhs> + <tgmm, strided segments>",
+                         "achieved": 3 * gemm_flops_gpu / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": target_ms / ms, "target_ms": target_ms, "traffic": None,
+                         "note": "per GPU over the whole step; frac = max(3 GEMMs at the measured tensor peak, two "
+                                 "exchanges at 770 GB/s) / measured step",
+                         "peak_source": peaks["source"] + "; NVLink 770 GB/s per direction"},
             "dispatch_modes": modes,
             "decode_case": {"tokens_per_gpu": d_tokens, "top_k": top_k, "rows_per_gpu": d_tokens * top_k,
-                            "note": "exchange + local ragged_dot per step; latency-bound (a few small kernels and "
-                                    "one all-gather), weights read once per touched expert", "modes": decode},
+                            "note": "forward only: exchange + local ragged_dot per step; latency-bound (a few small "
+                                    "kernels and one all-gather), weights read once per touched expert",
+                            "modes": decode},
             "e2e": e2e,
         }
         print(json.dumps(line), flush=True)

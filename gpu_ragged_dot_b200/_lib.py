@@ -32,7 +32,7 @@ class TileCfg(ctypes.Structure):
     """Mirror of ``rd_tile_cfg``."""
 
     _fields_ = [("tile_n", ctypes.c_int32), ("max_ctas", ctypes.c_int32), ("cta_group", ctypes.c_int32),
-                ("tile_m", ctypes.c_int32), ("flags", ctypes.c_int32)]
+                ("tile_m", ctypes.c_int32), ("flags", ctypes.c_int32), ("wait_limit_ms", ctypes.c_int32)]
 
 
 class EpSend(ctypes.Structure):
@@ -65,6 +65,14 @@ SIGNATURES = {
         + [_c_int] * 5
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
+    "rd_tgmm_strided": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 6
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
+    "rd_ep_combine_pull": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                    _c_int, _c_int, _c_void_p, _c_void_p]),
     "rd_gmm_indexed": (
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
@@ -82,11 +90,6 @@ SIGNATURES = {
         [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
         + [_c_int] * 6
         + [ctypes.POINTER(TileCfg), _c_void_p, _c_int, _c_int, ctypes.POINTER(EpSend), _c_void_p],
-    ),
-    "rd_ep_dispatch_phase": (
-        _c_int,
-        [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
-         _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     ),
     "rd_gmm_indexed_when_ready": (
         _c_int,

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -130,9 +131,8 @@ void launch_internal_metadata(const int32_t* group_sizes, const int32_t* group_t
 }
 
 // ------------------------------------------------------------------ tile selection
-// The committed replacement for the reference's run-time tune-jax search.  Measured on B200
-// (profiles/): the 256-wide tile wins at every benchmark shape, compute-bound or
-// bandwidth-bound (decode m=256: 93 % of copy bandwidth at 256, 67 % at 128, 39 % at 64), so
+// The committed replacement for the reference's run-time tune-jax search.  Measured on B200:
+// the 256-wide tile wins at every benchmark shape, compute-bound or bandwidth-bound (decode m=256: 93 % of copy bandwidth at 256, 67 % at 128, 39 % at 64), so
 // narrower tiles are only used when n itself is narrow.
 int choose_tile_n(long long /*row_tiles*/, int n, int /*sms*/) {
   if (n <= 64) return 64;
@@ -254,6 +254,20 @@ bool choose_two_half(bool tgmm, long long m, int k, int g, int bn) {
 bool choose_pair(bool tgmm, long long tiles256, int bn, int sms) {
   if (!tgmm || bn != 256) return false;
   return tiles256 >= 2LL * (sms / 2);
+}
+
+// Limit of every bounded wait inside a kernel, in microseconds: rd_tile_cfg.wait_limit_ms if
+// set, else the environment variable RD_WAIT_LIMIT_MS (read once), else two seconds.
+uint32_t wait_limit_us(const rd_tile_cfg* cfg) {
+  static const long env_ms = [] {
+    const char* v = getenv("RD_WAIT_LIMIT_MS");
+    const long ms = v ? strtol(v, nullptr, 10) : 0;
+    return ms > 0 ? ms : 0;
+  }();
+  long ms = (cfg && cfg->wait_limit_ms > 0) ? cfg->wait_limit_ms : env_ms;
+  if (ms <= 0) return rd::kDefaultWaitLimitUs;
+  if (ms > 4000000) ms = 4000000;
+  return static_cast<uint32_t>(ms) * 1000u;
 }
 
 int pick_ctas(const rd_tile_cfg* cfg) {
@@ -409,6 +423,7 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   args.k_tiles = 0;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.wait_limit_us = wait_limit_us(cfg);
   args.zero_tail = (cfg && (cfg->flags & RD_CFG_NO_ZERO_TAIL)) ? 0 : 1;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
@@ -562,31 +577,30 @@ int rd_ep_send_list(const void* x, int top_k, int row_bytes, const int32_t* send
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
-int rd_ep_dispatch_phase(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
-                         int num_experts, int world, int rank, int phase, const int32_t* dest_offset,
-                         int32_t* fill, void* dest_base, int capacity_rows, int32_t* dest_pos,
-                         int32_t* phase_done, int32_t* dest_ready_flag, int epoch, int max_blocks,
-                         void* stream) {
-  if (tokens < 0 || top_k <= 0 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 ||
-      num_experts <= 0 || num_experts % world != 0 || capacity_rows < 0 || rank < 0 ||
-      rank >= world || phase < 0 || phase >= world)
+int rd_ep_combine_pull(const int32_t* routing, const int32_t* dest_pos, int tokens, int top_k,
+                       int row_bytes, int num_experts, int world, const uint64_t* peer_base,
+                       int capacity_rows, int dtype, void* out, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
+  if (tokens < 0 || top_k <= 0 || top_k > 8 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 ||
+      num_experts <= 0 || num_experts % world != 0 || capacity_rows < 0)
     return RD_ERR_BAD_SHAPE;
-  if (!aligned16(dest_base) || !dest_offset || !fill || !dest_pos || !phase_done || !dest_ready_flag ||
-      (tokens > 0 && (!aligned16(x) || !routing)))
-    return RD_ERR_BAD_POINTER;
-  const long long entries = static_cast<long long>(tokens) * top_k;
+  if (tokens == 0) return RD_OK;
+  if (!routing || !dest_pos || !peer_base || !aligned16(out)) return RD_ERR_BAD_POINTER;
   const int warps_per_block = rd::kEpThreads / 32;
-  long long blocks = (entries + warps_per_block - 1) / warps_per_block;
-  // The phases run next to the local GEMM's persistent CTAs: by default two blocks per SM, so
-  // that both kinds of block stay resident together.
-  const int cap = max_blocks > 0 ? max_blocks : sm_count() * 2;
+  int blocks = (tokens + warps_per_block - 1) / warps_per_block;
+  const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;  // the flag is written even when there is nothing to send
-  rd::ep_dispatch_phase_kernel<<<static_cast<int>(blocks), rd::kEpThreads, 0,
-                                 static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x), routing, tokens, top_k, row_bytes / 16, num_experts,
-      num_experts / world, (rank + phase) % world, dest_offset, fill, static_cast<uint4*>(dest_base),
-      capacity_rows, dest_pos, phase_done + phase, dest_ready_flag, epoch, phase == 0 ? 1 : 0);
+  const int vecs = row_bytes / 16, local = num_experts / world;
+  uint4* o = static_cast<uint4*>(out);
+#define RD_COMBINE(BF, TK)                                                                          \
+  rd::ep_combine_pull_kernel<BF, TK><<<blocks, rd::kEpThreads, 0, stream>>>(                        \
+      routing, dest_pos, tokens, top_k, vecs, num_experts, local, peer_base, capacity_rows, o)
+  const bool bf = dtype == RD_DTYPE_BF16;
+  if (top_k <= 2) { if (bf) RD_COMBINE(true, 2); else RD_COMBINE(false, 2); }
+  else if (top_k <= 4) { if (bf) RD_COMBINE(true, 4); else RD_COMBINE(false, 4); }
+  else { if (bf) RD_COMBINE(true, 8); else RD_COMBINE(false, 8); }
+#undef RD_COMBINE
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -624,10 +638,14 @@ int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k,
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
-int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
-            void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
-            const rd_tile_cfg* cfg, void* stream_v) {
+// Shared body of rd_tgmm / rd_tgmm_strided: `g` output blocks, block i contracting over the rows
+// of groups i, i + g, ..., i + (seg_count - 1) * g of group_sizes (seg_count * g entries).
+static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+                     void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int seg_count,
+                     int dtype, const rd_tile_cfg* cfg, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (seg_count < 1 || (seg_count > 1 && g > 0 && seg_count > 0x7fffffff / g)) return RD_ERR_BAD_SHAPE;
+  const int g_fine = g * seg_count;
   if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16 && dtype != RD_DTYPE_F32) return RD_ERR_BAD_DTYPE;
   const bool f32 = dtype == RD_DTYPE_F32;
   const int esize = f32 ? 4 : 2;
@@ -642,7 +660,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   }
   if (!aligned16(x) || !aligned16(dout) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
   Workspace w;
-  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  int rc = bind_workspace(workspace, workspace_bytes, m, g_fine, &w);
   if (rc != RD_OK) return rc;
 
   const int sms = sm_count();
@@ -656,9 +674,13 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
   if (tile_m == 256 && (bn != 256 || cta_group == 2)) return RD_ERR_BAD_CONFIG;
   if (f32) {  // the float32 (TF32) kernels exist as single-CTA 128-row tiles only
-    if (cta_group == 2 || tile_m == 256) return RD_ERR_BAD_CONFIG;
+    if (cta_group == 2 || tile_m == 256 || seg_count > 1) return RD_ERR_BAD_CONFIG;
     cta_group = 1;
     tile_m = 128;
+  }
+  if (seg_count > 1) {  // strided segments: one CTA per tile
+    if (cta_group == 2) return RD_ERR_BAD_CONFIG;
+    cta_group = 1;
   }
   // Preference order when nothing is forced: 256-row tiles on one CTA, then a CTA pair, then
   // plain 128-row tiles.
@@ -678,7 +700,7 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   // of the call, a runtime launch binds the device's primary context to the calling thread,
   // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
   // arrive here without one).
-  launch_internal_metadata(group_sizes, nullptr, g, m, rd::kTileM, w, stream);
+  launch_internal_metadata(group_sizes, nullptr, g_fine, m, rd::kTileM, w, stream);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   CUtensorMap ta, tb;
@@ -708,8 +730,11 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   args.m = m; args.k = k; args.n = n; args.g = g;
   args.n_tiles = (n + bn - 1) / bn;
   args.k_tiles = static_cast<int>(k_tiles);
+  args.seg_count = seg_count;
+  args.seg_stride = g;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.wait_limit_us = wait_limit_us(cfg);
   args.zero_tail = 0;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
@@ -729,6 +754,19 @@ int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* o
   if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);
   if (bn == 128) return launch_gemm<128, false, true, 1>(ta, tb, tout, args, ctas, stream);
   return launch_gemm<64, false, true, 1>(ta, tb, tout, args, ctas, stream);
+}
+
+int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+            void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
+            const rd_tile_cfg* cfg, void* stream) {
+  return tgmm_impl(x, dout, group_sizes, out, workspace, workspace_bytes, m, k, n, g, 1, dtype, cfg, stream);
+}
+
+int rd_tgmm_strided(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+                    void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int seg_count,
+                    int dtype, const rd_tile_cfg* cfg, void* stream) {
+  return tgmm_impl(x, dout, group_sizes, out, workspace, workspace_bytes, m, k, n, g, seg_count, dtype, cfg,
+                   stream);
 }
 
 int rd_gmm_permuted(const void* x, int x_rows, const int32_t* in_rows, const void* A, int num_weights,
@@ -794,6 +832,7 @@ int rd_gmm_permuted(const void* x, int x_rows, const int32_t* in_rows, const voi
   args.k_tiles = 0;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.wait_limit_us = wait_limit_us(cfg);
   args.zero_tail = (cfg && (cfg->flags & RD_CFG_NO_ZERO_TAIL)) ? 0 : 1;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
@@ -868,6 +907,7 @@ int rd_tgmm_permuted(const void* x, int x_rows, const int32_t* x_row_index, cons
   args.k_tiles = (k + rd::kTileM - 1) / rd::kTileM;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
+  args.wait_limit_us = wait_limit_us(cfg);
   args.zero_tail = 0;
   args.group_sizes = group_sizes;
   args.group_offsets = w.group_offsets();
@@ -1000,12 +1040,3 @@ extern "C" int rd_gmm_static_scratch(const void* x, const void* A, const int32_t
   return rd_gmm(x, A, group_sizes, y, scratch, kStaticScratchBytes, m, k, n, g, trans_rhs, dtype, cfg,
                 stream);
 }
-
-#ifdef RD_TRACE
-// Debug builds only: copy CTA 0's timeline stamps (8192 x u64) to the host.
-extern "C" int rd_debug_trace(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_rd_trace, sizeof(unsigned long long) * 8192) == cudaSuccess
-             ? RD_OK
-             : RD_ERR_LAUNCH;
-}
-#endif

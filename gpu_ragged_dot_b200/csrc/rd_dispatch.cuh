@@ -17,6 +17,8 @@
 // so results can be brought back.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -45,7 +47,7 @@ ep_count_kernel(const int32_t* __restrict__ routing, int entries, int num_expert
 //   fill[e]               reset to 0 (arrival counters used by the dispatch kernel)
 //   totals[0]             rows I receive in all
 //
-// ring != 0 selects the layout of the overlapped exchange: on rank d the segments are ordered by
+// ring != 0 selects the layout of the fused exchange (rd_gmm_ep_fused): on rank d the segments are ordered by
 // "position" q = (d - source) mod W, i.e. d's own rows first, then those of d-1, d-2, ...; a
 // source sends to d in phase q of its dispatch, so positions fill in the order the local GEMM
 // reads them.  phase_done[W] (may be null) are the per-phase block counters, reset here.
@@ -139,65 +141,6 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ rout
   __threadfence_system();  // rows must be visible to their owners before the ranks synchronise
 }
 
-// One phase of the overlapped exchange: copies the (token, slot) pairs whose expert lives on
-// rank `dest` = (rank + phase) mod W, and when the last block has finished (its stores fenced
-// at system scope) writes `epoch` into ready_flag, the word ready[phase] of dest's flag array:
-// "the rows of position `phase` have landed".  Phases run one after the other on one stream,
-// and in phase p all ranks together form a permutation (r -> r+p), so every NVLink port
-// carries one flow at a time and dest's positions complete in the order its GEMM reads them.
-__global__ void __launch_bounds__(kEpThreads)
-ep_dispatch_phase_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ routing,
-                         int tokens, int top_k, int vecs_per_row, int num_experts,
-                         int experts_per_rank, int dest, const int32_t* __restrict__ dest_offset,
-                         int32_t* __restrict__ fill, uint4* __restrict__ dest_base,
-                         int capacity_rows, int32_t* __restrict__ dest_pos,
-                         int32_t* __restrict__ phase_done, int32_t* ready_flag, int epoch,
-                         int report_invalid) {
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = kEpThreads / 32;
-  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const int warp_stride = gridDim.x * warps_per_block;
-  const int entries = tokens * top_k;
-  const int e_lo = dest * experts_per_rank, e_hi = e_lo + experts_per_rank;
-  for (int i = warp_global; i < entries; i += warp_stride) {
-    const int e = routing[i];
-    if (e < e_lo || e >= e_hi) {
-      // An expert id outside [0, E) belongs to no phase: one phase (report_invalid) marks it.
-      if (report_invalid && (e < 0 || e >= num_experts) && lane == 0) dest_pos[i] = -1;
-      continue;
-    }
-    int pos = 0;
-    if (lane == 0) pos = dest_offset[e] + atomicAdd(&fill[e], 1);
-    pos = __shfl_sync(0xffffffffu, pos, 0);
-    if (pos >= capacity_rows) pos = -1;
-    if (lane == 0) dest_pos[i] = pos;
-    if (pos < 0) continue;
-    const uint4* src = x + static_cast<size_t>(i / top_k) * vecs_per_row;
-    uint4* dst = dest_base + static_cast<size_t>(pos) * vecs_per_row;
-    int v = lane;
-    for (; v + 96 < vecs_per_row; v += 128) {
-      const uint4 a = src[v], b = src[v + 32], c = src[v + 64], d = src[v + 96];
-      dst[v] = a;
-      dst[v + 32] = b;
-      dst[v + 64] = c;
-      dst[v + 96] = d;
-    }
-    for (; v < vecs_per_row; v += 32) dst[v] = src[v];
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int done = atomicAdd(phase_done, 1) + 1;
-    if (done == static_cast<int>(gridDim.x)) {
-      // Every block has fenced its stores before its increment; order this thread's flag store
-      // after having seen them all.
-      __threadfence_system();
-      *reinterpret_cast<volatile int32_t*>(ready_flag) = epoch;
-      __threadfence_system();
-    }
-  }
-}
-
 // Fused exchange, step 1: one thread per (token, slot) entry, one pass per block.  Assigns the
 // row its position at the expert's owner (dest_pos, as ep_dispatch_kernel does) and appends the
 // entry to the send list of its phase p = (owner - rank) mod W.  Both counters are aggregated
@@ -284,6 +227,90 @@ ep_send_list_kernel(const uint4* __restrict__ x, int top_k, int vecs_per_row,
       __threadfence_system();
       *reinterpret_cast<volatile int32_t*>(ready_flag) = epoch;
       __threadfence_system();
+    }
+  }
+}
+
+// Reverse exchange of the expert-parallel backward pass, fused with the top-k combine: the
+// gradient of token t is the sum, over its top_k routed copies, of the gradient rows the owners
+// computed at the positions the forward dispatch recorded (dest_pos).  One warp per token pulls
+// the top_k rows from the owners' buffers (peer loads over NVLink, or local memory), adds them in
+// fp32 and writes one 16-bit row.  peer_base[r]: rank r's gradient buffer as seen from this GPU.
+// The caller orders this kernel after every owner's dlhs GEMM (a cross-rank barrier).
+template <bool kBf16>
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (kBf16) {
+      acc[2 * i] += __uint_as_float(w[i] << 16);
+      acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      const float2 f = __half22float2(h);
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  }
+}
+
+template <bool kBf16, int kTopK>
+__global__ void __launch_bounds__(kEpThreads)
+ep_combine_pull_kernel(const int32_t* __restrict__ routing, const int32_t* __restrict__ dest_pos, int tokens,
+                       int top_k, int vecs_per_row, int num_experts, int experts_per_rank,
+                       const uint64_t* __restrict__ peer_base, int capacity_rows, uint4* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kEpThreads / 32;
+  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * warps_per_block;
+  for (int t = warp_global; t < tokens; t += warp_stride) {
+    const uint4* src[kTopK];
+#pragma unroll
+    for (int s = 0; s < kTopK; ++s) {
+      src[s] = nullptr;
+      if (s < top_k) {
+        const int e = routing[t * top_k + s];
+        const int pos = dest_pos[t * top_k + s];
+        if (e >= 0 && e < num_experts && pos >= 0 && pos < capacity_rows)
+          src[s] = reinterpret_cast<const uint4*>(peer_base[e / experts_per_rank]) +
+                   static_cast<size_t>(pos) * vecs_per_row;
+      }
+    }
+    uint4* dst = out + static_cast<size_t>(t) * vecs_per_row;
+    for (int v = lane; v < vecs_per_row; v += 64) {
+      const bool second = v + 32 < vecs_per_row;
+      uint4 a[kTopK], b[kTopK];
+#pragma unroll
+      for (int s = 0; s < kTopK; ++s) {  // all loads first: 2 * top_k 16-byte loads in flight per lane
+        a[s] = b[s] = make_uint4(0u, 0u, 0u, 0u);
+        if (src[s] != nullptr) {
+          a[s] = src[s][v];
+          if (second) b[s] = src[s][v + 32];
+        }
+      }
+      float fa[8] = {0, 0, 0, 0, 0, 0, 0, 0}, fb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int s = 0; s < kTopK; ++s) {
+        add8<kBf16>(fa, a[s]);
+        add8<kBf16>(fb, b[s]);
+      }
+      auto pack = [](const float (&f)[8]) {
+        uint4 o;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (kBf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        return o;
+      };
+      dst[v] = pack(fa);
+      if (second) dst[v + 32] = pack(fb);
     }
   }
 }

@@ -47,12 +47,16 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 // Runs on every thread of a sender CTA.  smem: 1024-byte aligned shared window of at least
 // warps * (kEpSlots * kEpChunkBytes + 64) + 8 * world bytes.
 __device__ __noinline__ void ep_sender_role(const EpSendArgs a, int epoch, int sender, uint32_t smem,
-                                            volatile int* abort_flag, int32_t* status) {
+                                            volatile WaitCtl* abort_flag, uint32_t wait_limit_us,
+                                            int32_t* status) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_warps = blockDim.x >> 5;
   const uint64_t t_start = global_timer_ns();
-  if (threadIdx.x == 0) *abort_flag = 0;
+  if (threadIdx.x == 0) {
+    abort_flag->abort = 0;
+    abort_flag->limit_us = wait_limit_us;
+  }
   const uint32_t slots = smem + warp * (kEpSlots * kEpChunkBytes);
   const uint32_t bars = smem + n_warps * (kEpSlots * kEpChunkBytes) + warp * 64;
   const uint32_t phase_bars = smem + n_warps * (kEpSlots * kEpChunkBytes + 64);  // one per phase
@@ -176,7 +180,7 @@ __device__ __noinline__ void ep_sender_role(const EpSendArgs a, int epoch, int s
   // status[1]: time the slowest sender CTA needed for all its phases (microseconds)
   if (threadIdx.x == 0)
     atomicMax(status + 1, static_cast<int32_t>((global_timer_ns() - t_start) / 1000ull));
-  if (*abort_flag) {
+  if (abort_flag->abort) {
     if (threadIdx.x == 0) atomicMax(status, 1);
     // bulk copies may still be in flight into this CTA's shared memory
     const uint64_t t0 = global_timer_ns();

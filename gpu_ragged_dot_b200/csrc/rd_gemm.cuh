@@ -41,22 +41,6 @@
 #include "rd_metadata.cuh"
 #include "rd_ptx.cuh"
 
-// Optional timeline instrumentation (build with -DRD_TRACE): CTA 0 records globaltimer stamps
-// of its pipeline events into a device array read back by rd_debug_trace().
-#ifdef RD_TRACE
-__device__ unsigned long long g_rd_trace[8192];
-#define RD_TRACE_EVENT(role, idx, ev)                                                         \
-  do {                                                                                        \
-    if (blockIdx.x == 0 && (idx) < 64) {                                                      \
-      g_rd_trace[(((role) * 64 + (idx)) * 8 + (ev))] = rd::global_timer_ns();                 \
-    }                                                                                         \
-  } while (0)
-#else
-#define RD_TRACE_EVENT(role, idx, ev) \
-  do {                                \
-  } while (0)
-#endif
-
 namespace rd {
 
 constexpr int kTileM = 128;  // UMMA M per CTA == output rows per CTA tile
@@ -75,10 +59,15 @@ enum DeviceStatus : int32_t {
 struct GemmArgs {
   int m, k, n, g;   // gmm: x[m,k] . W[g] -> y[m,n]      tgmm: x[m,k], dout[m,n] -> out[g,k,n]
   int n_tiles;      // ceil(n / BN)
+  // tgmm over strided segments (seg_count > 1): output block i contracts over the rows of the
+  // groups i, i + seg_stride, ..., i + (seg_count - 1) * seg_stride of group_sizes, one after
+  // the other; g is then the number of output blocks.  seg_count <= 1: block i = group i.
+  int seg_count, seg_stride;
   int k_tiles;      // tgmm: tiles along the output's k axis (128 * kCtas rows each); gmm: unused
   int max_m_tiles;  // static upper bound on live row tiles (gmm)
   int ab_format;    // 0 = fp16, 1 = bf16
   int zero_tail;    // gmm: write zeros to the rows past sum(group_sizes)
+  uint32_t wait_limit_us;  // how long a bounded wait inside the kernel may last (microseconds)
   const int32_t* group_sizes;
   const int32_t* group_offsets;
   const TileRecord* tile_rec;  // gmm: one record per live row tile (of 128 * kCtas rows)
@@ -166,6 +155,57 @@ __device__ __forceinline__ bool tail_needs_clearing(int group_rows) {
   return live != 0 && (live % kUmmaK) != 0;
 }
 
+// tgmm: the 64-row blocks one output block contracts over.  A block never crosses the end of a
+// segment (a group of group_sizes); its rows past the segment's end are cleared or skipped by
+// the MMA warp.  Plain tgmm has one segment per output block, the rows of group t.group.
+struct RowBlocks {
+  int q;     // segments opened so far
+  int row;   // first row of the next block
+  int left;  // rows of the current segment from `row` on
+};
+
+__device__ __forceinline__ void segment_rows(const GemmArgs& p, int group, int& row0, int& rows) {
+  row0 = p.group_offsets[group];
+  rows = imax(imin(imax(p.group_sizes[group], 0), p.m - row0), 0);
+}
+
+__device__ __forceinline__ int tgmm_block_count(const GemmArgs& p, const TileCoord& t) {
+  if (p.seg_count <= 1) return (t.rows + kTileK - 1) / kTileK;
+  int blocks = 0;
+  for (int q = 0; q < p.seg_count; ++q) {
+    int row0, rows;
+    segment_rows(p, t.group + q * p.seg_stride, row0, rows);
+    blocks += (rows + kTileK - 1) / kTileK;
+  }
+  return blocks;
+}
+
+__device__ __forceinline__ RowBlocks first_block(const TileCoord& t) {
+  RowBlocks it;
+  it.q = 1;
+  it.row = t.row0;
+  it.left = t.rows;
+  return it;
+}
+
+// First row and live rows (1..64) of the next block.  Call at most tgmm_block_count() times.
+__device__ __forceinline__ void next_block(const GemmArgs& p, const TileCoord& t, RowBlocks& it, int& row,
+                                           int& live) {
+  while (it.left <= 0 && it.q < p.seg_count) {
+    segment_rows(p, t.group + it.q * p.seg_stride, it.row, it.left);
+    ++it.q;
+  }
+  row = it.row;
+  live = imin(it.left, kTileK);
+  it.row += kTileK;
+  it.left -= kTileK;
+}
+
+// Does a block with `live` rows need rows cleared before its MMAs?
+__device__ __forceinline__ bool block_needs_clearing(int live) {
+  return live < kTileK && (live % kUmmaK) != 0;
+}
+
 // Zero rows [live, end of the last 16-deep MMA) of every [64 rows][128 B] box of one stage and
 // make the writes visible to the tensor core (async proxy).  Whole warp.
 template <int kBoxes>
@@ -241,7 +281,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];  // leader only when paired
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ WaitCtl wait_ctl;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -255,14 +295,15 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // The senders are the FIRST CTAs of the grid, so they are resident before any CTA that may wait
   // for another GPU's senders.
   if (static_cast<int>(blockIdx.x) < sender_ctas) {
-    ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &abort_flag,
+    ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &wait_ctl, p.wait_limit_us,
                    p.status);
     return;
   }
   const int cta_index = static_cast<int>(blockIdx.x) - sender_ctas;  // among the multiplying CTAs
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
+    wait_ctl.abort = 0;
+    wait_ctl.limit_us = p.wait_limit_us;
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_out);
@@ -286,7 +327,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (kPair) cluster_sync();  // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  volatile int* abort_ptr = &abort_flag;
+  volatile WaitCtl* abort_ptr = &wait_ctl;
 
   int num_tiles;
   if (kTgmm) {
@@ -308,7 +349,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
                                   : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
         const int nb = t.n0 + cta_rank * kBCols;  // first B column this CTA loads
-        const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+        RowBlocks blocks = first_block(t);
         if (!kTgmm && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
           if (slot != ready_slot) {
@@ -319,7 +361,6 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ready_slot = slot;
           }
         }
-        RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 0);
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -327,8 +368,6 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
-          if (kb == 0) RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 1);
-          if (kb == kb_count - 1) RD_TRACE_EVENT(0, (tile - tile_start) / tile_step, 2);
           uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t sa = stage_base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
@@ -345,7 +384,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             remote_bar = true;
           }
           if (kTgmm) {
-            const int r = t.row0 + kb * kTileK;
+            int r, live;
+            next_block(p, t, blocks, r, live);
             load_2d(remote_bar, sa, &tmap_a, full, t.k0, r);
             load_2d(remote_bar, sa + kBoxBytes, &tmap_a, full, t.k0 + 64, r);
 #pragma unroll
@@ -392,8 +432,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
       const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
                                 : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
-      const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
-      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+      const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);  // pairs only
+      RowBlocks blocks = first_block(t);
       const uint32_t idesc = (!kTgmm && !kPair && t.rows <= 64) ? idesc_half : idesc_full;
 
       if (kPair && !leader) {
@@ -420,12 +461,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // ---- single CTA, or the leader of a pair
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
-      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 0);
       if (!mbar_wait<kPair>(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
         ok = false;
         break;
       }
-      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 1);
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       uint32_t s = it % kStages;
@@ -435,15 +474,17 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = false;
           break;
         }
-        if (lane == 0 && kb == 0) RD_TRACE_EVENT(1, local_tile, 2);
-        if (lane == 0 && kb == kb_count - 1) RD_TRACE_EVENT(1, local_tile, 3);
         const uint32_t sa = stage_base + s * kStageBytes;
         // tgmm: contraction depth that is really there in this stage (the group's last rows);
         // whole 16-deep MMAs past it are skipped.  gmm always issues all four: columns past k
         // are zero-filled by TMA in both operands.
-        const int live = kTgmm ? t.rows - kb * kTileK : kTileK;
+        int live = kTileK;
+        if (kTgmm) {
+          int r;
+          next_block(p, t, blocks, r, live);
+        }
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && tail_stage && kb == kb_count - 1) {
+        if (kTgmm && (kPair ? (tail_stage && kb == kb_count - 1) : block_needs_clearing(live))) {
           // Rows past the end of the group belong to the next group (or to nobody): clear them,
           // up to the end of the last MMA that is issued, in every box of this stage, so they
           // add nothing to the reduction.  (In gmm the columns past k are zero-filled by TMA.)
@@ -490,7 +531,6 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
       }
       if (!ok) break;
-      if (lane == 0) RD_TRACE_EVENT(1, local_tile, 4);
       if (lane == 0) {
         const uint32_t bar = smem_u32(&bar_acc_full[acc]);
         if (kb_count > 0) {
@@ -521,12 +561,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = t.n0;
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_ph = (local_tile >> 1) & 1u;
-      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 0);
       if (!mbar_wait<kPair>(smem_u32(&bar_acc_full[acc]), acc_ph, abort_ptr)) {
         ok = false;
         break;
       }
-      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 1);
       tc_fence_after_sync();
 
       bool row_ok;         // this thread's output row exists
@@ -542,7 +580,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         warp_has_rows = out_row0 < p.k;
         slab_by_tma = true;  // rows >= k are outside the map and dropped by the store
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
-        zero_only = t.rows <= 0;
+        zero_only = tgmm_block_count(p, t) == 0;
       } else if (!kPair && t.rows <= 64) {
         // M = 64 tile: row 16 * quarter + lane sits in lane `lane` (< 16) of this warp's quarter
         const int r64 = quarter * 16 + lane;
@@ -629,7 +667,6 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
-      if (warp == 2 && lane == 0) RD_TRACE_EVENT(2, local_tile, 2);
       if (n_chunks == 0) {
         tc_fence_before_sync();
         __syncwarp();
@@ -662,7 +699,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ------------------------------------------------------------ tear-down
   __syncthreads();
-  if (abort_flag) {
+  if (wait_ctl.abort) {
     if (threadIdx.x == 0) atomicMax(p.status, static_cast<int32_t>(kStatusWaitExpired));
     // Give copies and MMAs that are still in flight time to land before smem/TMEM go away.
     const uint64_t t0 = global_timer_ns();

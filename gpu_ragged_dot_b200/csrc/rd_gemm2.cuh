@@ -28,10 +28,7 @@ constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps;
 constexpr int kG2Stages = 3;
 constexpr int kG2TileN = 256;
 constexpr int kG2TileRows = 2 * kTileM;
-#ifndef RD_G2_TGMM_BAND
-#define RD_G2_TGMM_BAND 8
-#endif
-constexpr int kG2TgmmBand = RD_G2_TGMM_BAND;  // column tiles per band of the tgmm tile order
+constexpr int kG2TgmmBand = 8;  // column tiles per band of the tgmm tile order
 constexpr uint32_t kG2ABytes = 2 * kTileM * kTileK * 2;   // two 128-row halves
 constexpr uint32_t kG2BBytes = kG2TileN * kTileK * 2;
 constexpr uint32_t kG2StageBytes = kG2ABytes + kG2BBytes;  // 64 KB
@@ -100,7 +97,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_acc_full[2];   // per half
   __shared__ __align__(8) uint64_t bar_acc_empty[2];  // per half
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ WaitCtl wait_ctl;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -114,14 +111,15 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (kEp) {
     sender_ctas = p.send.world > 0 ? p.send.sender_ctas : 0;
     if (static_cast<int>(blockIdx.x) < sender_ctas) {
-      ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &abort_flag,
+      ep_sender_role(p.send, p.ready_epoch, static_cast<int>(blockIdx.x), stage_base, &wait_ctl, p.wait_limit_us,
                      p.status);
       return;
     }
   }
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
+    wait_ctl.abort = 0;
+    wait_ctl.limit_us = p.wait_limit_us;
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_out);
@@ -143,7 +141,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  volatile int* abort_ptr = &abort_flag;
+  volatile WaitCtl* abort_ptr = &wait_ctl;
 
   const int num_tiles =
       kTgmm ? p.g * p.k_tiles * p.n_tiles : imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
@@ -168,7 +166,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
         const int halves = halves_of(t);
-        const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
+        const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+        RowBlocks blocks = first_block(t);
         if (kEp && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
           if (slot != ready_slot) {
@@ -193,7 +192,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sb = sa + kG2ABytes;
           mbar_arrive_expect_tx(full, halves * kHalfABytes + kG2BBytes);
           if (kTgmm) {
-            const int r = t.row0 + kb * kTileK;
+            int r, live;
+            next_block(p, t, blocks, r, live);
             for (int h = 0; h < halves; ++h) {
               tma_load_2d_hint(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r, keep);
               tma_load_2d_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r, keep);
@@ -239,8 +239,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
       const int halves = halves_of(t);
-      const int kb_count = kTgmm ? (t.rows + kTileK - 1) / kTileK : k_blocks_gmm;
-      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+      const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+      RowBlocks blocks = first_block(t);
 
       if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
 #pragma unroll
@@ -266,9 +266,13 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           break;
         }
         const uint32_t sa = stage_base + s * kG2StageBytes;
-        const int live = kTgmm ? t.rows - kb * kTileK : kTileK;
+        int live = kTileK;
+        if (kTgmm) {
+          int r;
+          next_block(p, t, blocks, r, live);
+        }
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && tail_stage && kb == kb_count - 1) {
+        if (kTgmm && block_needs_clearing(live)) {
           clear_tail_rows<kG2StageBytes / kBoxBytes>(sa, live, lane);
           __syncwarp();
         }
@@ -347,7 +351,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         warp_has_rows = out_row0 < p.k;
         slab_by_tma = true;
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
-        zero_only = t.rows <= 0;
+        zero_only = tgmm_block_count(p, t) == 0;
       } else {
         out_row0 = t.row0 + slab0;
         row_ok = r_in_tile < t.rows;
@@ -456,7 +460,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ------------------------------------------------------------ tear-down
   __syncthreads();
-  if (abort_flag) {
+  if (wait_ctl.abort) {
     if (threadIdx.x == 0) atomicMax(p.status, static_cast<int32_t>(kStatusWaitExpired));
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);

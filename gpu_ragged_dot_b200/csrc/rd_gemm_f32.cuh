@@ -84,14 +84,15 @@ ragged_gemm_f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ WaitCtl wait_ctl;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
+    wait_ctl.abort = 0;
+    wait_ctl.limit_us = p.wait_limit_us;
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_out);
@@ -113,7 +114,7 @@ ragged_gemm_f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  volatile int* abort_ptr = &abort_flag;
+  volatile WaitCtl* abort_ptr = &wait_ctl;
 
   const int num_tiles =
       kTgmm ? p.g * p.k_tiles * p.n_tiles : imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
@@ -354,7 +355,7 @@ ragged_gemm_f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ------------------------------------------------------------ tear-down
   __syncthreads();
-  if (abort_flag) {
+  if (wait_ctl.abort) {
     if (threadIdx.x == 0) atomicMax(p.status, static_cast<int32_t>(kStatusWaitExpired));
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);

@@ -88,6 +88,10 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
   __syncthreads();
 
   // Pass 1: blocked exclusive scan of rows and of tiles, kMetaThreads groups at a time.
+  // For the GEMM kernels (tile_rec given) a group only counts the rows that exist below m, so a
+  // caller whose group_sizes add up to more than m still gets every tile of the rows that are
+  // there; the reference-shaped arrays alone follow the reference's formula (no clamp).
+  const bool clamp_to_m = tile_rec != nullptr;
   for (int base = 0; base < g; base += kMetaThreads) {
     const int i = base + tid;
     int rows = 0;
@@ -95,24 +99,31 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
       rows = group_sizes[i];
       rows = rows < 0 ? 0 : rows;
     }
-    const int tiles = (rows + tile_m - 1) / tile_m;
     int inc_rows = warp_inclusive_scan(rows, lane);
-    int inc_tiles = warp_inclusive_scan(tiles, lane);
-    if (lane == 31) {
-      warp_rows[warp] = inc_rows;
-      warp_tiles[warp] = inc_tiles;
-    }
+    if (lane == 31) warp_rows[warp] = inc_rows;
     __syncthreads();
     if (warp == 0) {
       int wr = warp_rows[lane];
-      int wt = warp_tiles[lane];
       int ir = warp_inclusive_scan(wr, lane);
-      int it = warp_inclusive_scan(wt, lane);
       warp_rows[lane] = ir - wr;  // exclusive prefix over warps
-      warp_tiles[lane] = it - wt;
     }
     __syncthreads();
     const int ex_rows = carry_rows + warp_rows[warp] + inc_rows - rows;
+    int live_rows = rows;
+    if (clamp_to_m) {
+      const int left = m - ex_rows;
+      live_rows = left <= 0 ? 0 : (rows < left ? rows : left);
+    }
+    const int tiles = (live_rows + tile_m - 1) / tile_m;
+    int inc_tiles = warp_inclusive_scan(tiles, lane);
+    if (lane == 31) warp_tiles[warp] = inc_tiles;
+    __syncthreads();
+    if (warp == 0) {
+      int wt = warp_tiles[lane];
+      int it = warp_inclusive_scan(wt, lane);
+      warp_tiles[lane] = it - wt;
+    }
+    __syncthreads();
     const int ex_tiles = carry_tiles + warp_tiles[warp] + inc_tiles - tiles;
     if (i < g) {
       if (group_offsets) group_offsets[i] = ex_rows;
@@ -172,7 +183,9 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
       r.group = gi;
       r.weight = group_to_weight ? group_to_weight[gi] : gi;
       r.group_offset = group_offsets[gi];
-      r.group_size = rows < 0 ? 0 : rows;
+      rows = rows < 0 ? 0 : rows;
+      const int left = m - r.group_offset;
+      r.group_size = left <= 0 ? 0 : (rows < left ? rows : left);
       r.tile_base = tile_prefix[gi];
       r.tiles = tile_prefix[gi + 1] - r.tile_base;
       r.idx = idx;

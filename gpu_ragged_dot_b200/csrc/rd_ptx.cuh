@@ -118,28 +118,33 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
-// Bounded wait.  Gives up after `RD_WAIT_LIMIT_NS` of wall time (or as soon as another
-// thread of the CTA has raised *abort_flag), raises *abort_flag and returns false; the
-// caller must then leave its loop and fall through to the kernel's common tear-down.
-#ifndef RD_WAIT_LIMIT_NS
-#define RD_WAIT_LIMIT_NS 2000000000ull
-#endif
+// Bounded waits.  Every spin in these kernels (on an mbarrier, on a flag another GPU raises)
+// gives up after `limit_us` microseconds of wall time, or as soon as another thread of the CTA has
+// given up: it raises `abort`, returns false, and the caller leaves its loop and falls through
+// to the kernel's common tear-down, which records the expiry in the workspace status word.
+// The limit is a launch argument (GemmArgs::wait_limit_us, default kDefaultWaitLimitUs).
+struct WaitCtl {
+  int abort;
+  uint32_t limit_us;
+};
+constexpr uint32_t kDefaultWaitLimitUs = 2000000u;
 
 template <bool kClusterScope = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitCtl* ctl) {
   for (int i = 0; i < 256; ++i) {
     bool ok = kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
     if (ok) return true;
   }
   const uint64_t t0 = global_timer_ns();
+  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
   for (;;) {
     for (int i = 0; i < 64; ++i) {
       bool ok = kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
       if (ok) return true;
     }
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > RD_WAIT_LIMIT_NS) {
-      *abort_flag = 1;
+    if (ctl->abort) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
+      ctl->abort = 1;
       return false;
     }
   }
@@ -148,15 +153,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // Bounded wait until the 32-bit word at `flag` (written by a kernel on this or another GPU, at
 // system scope, after the data it guards) is >= `value`.  The proxy fence orders the TMA loads
 // that follow after the acquire.  Same expiry rule as mbar_wait.
-__device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int value, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int value, volatile WaitCtl* ctl) {
   const uint64_t t0 = global_timer_ns();
+  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
   for (;;) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v >= value) break;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > RD_WAIT_LIMIT_NS) {
-      *abort_flag = 1;
+    if (ctl->abort) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
+      ctl->abort = 1;
       return false;
     }
     __nanosleep(256);

@@ -25,6 +25,7 @@ namespace {
 int DtypeCode(ffi::DataType t) {
   if (t == ffi::DataType::BF16) return RD_DTYPE_BF16;
   if (t == ffi::DataType::F16) return RD_DTYPE_F16;
+  if (t == ffi::DataType::F32) return RD_DTYPE_F32;  // multiplied as TF32, float32 result
   return -1;
 }
 
@@ -45,7 +46,7 @@ ffi::Error GmmImpl(cudaStream_t stream, ffi::AnyBuffer x, ffi::AnyBuffer a,
     return ffi::Error(ffi::ErrorCode::kInvalidArgument, "rd_gmm: expected x[m,k], A[g,.,.], gs[g]");
   const int m = static_cast<int>(xd[0]), k = static_cast<int>(xd[1]), g = static_cast<int>(ad[0]);
   const int n = static_cast<int>(trans_rhs ? ad[1] : ad[2]);
-  rd_tile_cfg cfg{tile_n, 0, 0, 0, 0};
+  rd_tile_cfg cfg{tile_n, 0, 0, 0, 0, 0};
   return ToError(rd_gmm(x.untyped_data(), a.untyped_data(), group_sizes.typed_data(),
                         y->untyped_data(), workspace->untyped_data(), workspace->size_bytes(), m, k, n,
                         g, trans_rhs ? 1 : 0, DtypeCode(x.element_type()), tile_n ? &cfg : nullptr,
@@ -62,7 +63,7 @@ ffi::Error TgmmImpl(cudaStream_t stream, ffi::AnyBuffer x, ffi::AnyBuffer dout,
     return ffi::Error(ffi::ErrorCode::kInvalidArgument, "rd_tgmm: expected x[m,k], dout[m,n]");
   const int m = static_cast<int>(xd[0]), k = static_cast<int>(xd[1]), n = static_cast<int>(dd[1]);
   const int g = static_cast<int>(group_sizes.dimensions()[0]);
-  rd_tile_cfg cfg{tile_n, 0, 0, 0, 0};
+  rd_tile_cfg cfg{tile_n, 0, 0, 0, 0, 0};
   return ToError(rd_tgmm(x.untyped_data(), dout.untyped_data(), group_sizes.typed_data(),
                          out->untyped_data(), workspace->untyped_data(), workspace->size_bytes(), m, k,
                          n, g, DtypeCode(x.element_type()), tile_n ? &cfg : nullptr, stream),

@@ -16,12 +16,20 @@ Per step, on each rank (T tokens, top_k routing, E experts, El = E / W per rank)
 `plan_dispatch` and `exchange_rows` use only torch + torch.distributed and run on any backend
 (the CPU tests drive them over gloo); `ExpertParallelRaggedDot` adds the CUDA steps.
 
+The backward pass (``backward``) mirrors the reference's custom_vjp wiring (gpu_ragged_dot.py:399-402)
+on the sharded layout: dlhs = the transposed grouped GEMM over the received rows on the owner,
+brought back to the tokens' ranks by the reverse exchange (summed over the top_k copies of a
+token); drhs = tgmm over the received rows, summed per local expert over the source ranks.
+
 A second dispatch mode, ``dispatch="p2p"``, has no host round trip at all: the counts are
 all-gathered (NCCL, E int32 per rank), `rd_ep_plan` turns them into write offsets on the device,
 and `rd_ep_dispatch` stores every row directly into the owner's receive buffer through peer
 memory (torch symmetric memory supplies the peer addresses and the cross-rank barrier).  The
 receive buffer has a fixed capacity (every row of every rank could land on one rank), the
 local GEMM gets that capacity as its static row bound and the true segment sizes on the device.
+
+The third mode, ``dispatch="fused"``, runs the exchange inside the GEMM launch (sender CTAs of the
+same grid), see ``forward_fused``.
 """
 
 from __future__ import annotations
@@ -85,16 +93,13 @@ class ExpertParallelRaggedDot:
 
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
-                 dispatch: str = "nccl", capacity_rows: Optional[int] = None,
-                 own_blocks: int = 0, side_blocks: int = 0, sender_ctas: int = 0):
+                 dispatch: str = "nccl", capacity_rows: Optional[int] = None, sender_ctas: int = 0):
         from . import workloads
 
-        assert dispatch in ("nccl", "p2p", "overlap", "fused")
+        assert dispatch in ("nccl", "p2p", "fused")
         self.dispatch, self.capacity_rows, self._p2p = dispatch, capacity_rows, None
-        self._ov, self._epoch = None, 0
-        # overlap mode: grid caps of the phase kernels (0 = library default), phase 0 / the others
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
-        self.own_blocks, self.side_blocks = own_blocks or 8 * sms, side_blocks
+        self._ring, self._epoch = None, 0
+        self._saved = None  # what the last forward left for backward
         self.dtype = dtype
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -108,10 +113,23 @@ class ExpertParallelRaggedDot:
         self.k, self.n, self.device = k, n, device
         self.weights = workloads.normal_tensor((self.local_experts, k, n), k ** -0.5, seed, device, dtype)
         self._events = []
+        self._bwd_events = []
+        self._grad = None
         self._host = None
 
     def reset_timers(self):
         self._events = []
+        self._bwd_events = []
+
+    def device_status(self) -> int:
+        """Synchronises and returns the status word of the kernels of the last step (0 = ok; non-zero
+        means a bounded wait expired inside a kernel and the result has unwritten rows)."""
+        from . import ops
+
+        for st in (self._ring, self._grad):
+            if st is not None and ops.device_status(st["ws"]) != 0:
+                return ops.device_status(st["ws"])
+        return 0
 
     def timers_ms(self, steps: int):
         torch.cuda.synchronize(self.device)
@@ -119,9 +137,9 @@ class ExpertParallelRaggedDot:
         for e in self._events:
             tot["permute"] += e[0].elapsed_time(e[1])
             tot["a2a"] += e[1].elapsed_time(e[2])
-            # overlap mode: exchange and GEMM both start when the plan is done and run together
-            tot["gemm"] += (e[1] if self.dispatch in ("overlap", "fused") else e[2]).elapsed_time(e[3])
-        if self.dispatch in ("overlap", "fused"):  # when the GEMM could start: own rows copied
+            # fused mode: exchange and GEMM both start when the plan is done and run together
+            tot["gemm"] += (e[1] if self.dispatch == "fused" else e[2]).elapsed_time(e[3])
+        if self.dispatch == "fused":  # when the GEMM could start: own rows copied
             tot["own_rows"] = sum(e[1].elapsed_time(e[4]) for e in self._events)
         return {k: v / max(steps, 1) for k, v in tot.items()}
 
@@ -182,11 +200,13 @@ class ExpertParallelRaggedDot:
         if timed:
             ev[3].record()
             self._events.append(ev)
+        self._saved = {"recv": st["buf"], "seg": seg_sizes, "seg2e": st["seg2e"], "dest_pos": dest_pos,
+                       "routing": routing, "capacity": st["capacity"]}
         return y, seg_sizes, dest_pos, totals
 
-    # ------------------------------------------------------------------ overlapped exchange + GEMM
-    def _overlap_setup(self, capacity_rows: int):
-        """Receive buffer and ready flags in symmetric memory, persistent plan buffers, side stream."""
+    # ------------------------------------------------------------------ exchange inside the GEMM launch
+    def _ring_setup(self, capacity_rows: int):
+        """Receive buffer and ready flags in symmetric memory, persistent plan buffers."""
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
 
@@ -206,7 +226,7 @@ class ExpertParallelRaggedDot:
             hb = hf = None
             buf_ptrs, flag_ptrs = [buf.data_ptr()], [flags.data_ptr()]
         E, W = self.num_experts, self.world
-        self._ov = {
+        self._ring = {
             "buf": buf, "flags": flags, "handles": (hb, hf), "capacity": capacity_rows,
             "buf_ptrs": buf_ptrs, "flag_ptrs": flag_ptrs,
             "counts_all": torch.empty((W, E), dtype=torch.int32, device=dev),
@@ -216,87 +236,23 @@ class ExpertParallelRaggedDot:
             "y": torch.empty((capacity_rows, self.n), dtype=self.dtype, device=dev),
             "ws": ops._workspace(capacity_rows, E, dev),
             "seg2e": torch.arange(self.local_experts, dtype=torch.int32, device=dev).repeat(W),
-            "side": torch.cuda.Stream(device=dev, priority=-1),
-            "ev_plan": torch.cuda.Event(), "ev_done": torch.cuda.Event(),
         }
-
-    def forward_overlap(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
-        """Exchange and local ragged_dot running together: after the plan, the W dispatch phases go
-        out on a side stream (phase p sends to rank+p and raises flag p there) while the GEMM,
-        launched at once on the main stream, multiplies position q as soon as flag q is up.
-
-        Returns (y [capacity, n], segment_sizes [W*El] in position order, dest_pos [T, top_k], totals)."""
-        from . import _lib, ops
-
-        tokens, top_k = routing.shape
-        if self._ov is None:
-            self._overlap_setup(self.capacity_rows or tokens * top_k * self.world)
-        st = self._ov
-        self._epoch += 1
-        epoch, W = self._epoch, self.world
-        main = torch.cuda.current_stream(self.device)
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
-        if timed:
-            ev[0].record()
-        routing = routing.to(torch.int32).contiguous()
-        x_tokens = x_tokens.contiguous()
-        counts = ops.ep_count(routing, self.num_experts)
-        if W > 1:
-            # Also the "receive buffers are free again" barrier (see forward_p2p).
-            dist.all_gather_into_tensor(st["counts_all"].view(-1), counts, group=self.group)
-        else:
-            st["counts_all"].copy_(counts.view(1, -1))
-        plan = ops.ep_plan_ring(st["counts_all"], self.rank, st["plan"])
-        dest_pos = torch.empty(tokens * top_k, dtype=torch.int32, device=self.device)
-        if timed:
-            ev[1].record()
-        def phase(p):
-            d = (self.rank + p) % W
-            ops.ep_dispatch_phase(x_tokens, routing, self.num_experts, W, self.rank, p, plan,
-                                  st["buf_ptrs"][d], st["capacity"], dest_pos, st["flag_ptrs"][d] + 4 * p, epoch,
-                                  max_blocks=self.own_blocks if p == 0 else self.side_blocks)
-
-        # Phase 0 (this rank's own rows, a local copy) runs alone and first, on the main stream:
-        # the GEMM behind it never waits for a kernel of its own GPU, and the copy is not slowed
-        # down by the NVLink phases (measured: 0.15 ms next to them, 0.05 ms alone).
-        phase(0)
-        if timed:
-            ev.append(torch.cuda.Event(enable_timing=True))
-            ev[4].record()
-        st["ev_plan"].record(main)
-        side = st["side"]
-        side.wait_event(st["ev_plan"])
-        # Phases to the other ranks go out on the side stream while the GEMM runs; the local
-        # GEMM never waits for them -- it waits for the other GPUs' phases.
-        with torch.cuda.stream(side):
-            for p in range(1, W):
-                phase(p)
-            if timed:
-                ev[2].record(side)
-            st["ev_done"].record(side)
-        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
-        y = ops.gmm_forward(st["buf"], self.weights, plan["segment_sizes"], group_to_weight=st["seg2e"],
-                            cfg=cfg, out=st["y"], workspace=st["ws"],
-                            ready=(st["flags"], self.local_experts, epoch))
-        if timed:
-            ev[3].record()
-        # The step is over on this rank when its own sends are, too.
-        main.wait_event(st["ev_done"])
-        if timed:
-            self._events.append(ev)
-        return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
 
     def forward_fused(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
         """Exchange and local ragged_dot in ONE kernel launch: after count / all-gather / plan /
         assign and a copy of this rank's own rows, ``rd_gmm_ep_fused`` runs the flag-gated GEMM on
         most CTAs while ``sender_ctas`` CTAs of the same grid push the rows of phases 1..W-1 to
-        their owners and raise the owners' flags.  Same return values as ``forward_overlap``."""
+        their owners and raise the owners' flags.  The senders are CTAs of the same launch as the
+        CTAs that wait for other GPUs' senders, resident before them by construction, so no rank's
+        progress depends on a separately launched kernel finding room on a busy GPU.
+
+        Returns (y [capacity, n], segment_sizes [W*El] in position order, dest_pos [T, top_k], totals)."""
         from . import _lib, ops
 
         tokens, top_k = routing.shape
-        if self._ov is None:
-            self._overlap_setup(self.capacity_rows or tokens * top_k * self.world)
-        st = self._ov
+        if self._ring is None:
+            self._ring_setup(self.capacity_rows or tokens * top_k * self.world)
+        st = self._ring
         self._epoch += 1
         epoch, W = self._epoch, self.world
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if timed else None
@@ -341,16 +297,18 @@ class ExpertParallelRaggedDot:
         if timed:
             ev[3].record()
             self._events.append(ev)
+        self._saved = {"recv": st["buf"], "seg": plan["segment_sizes"], "seg2e": st["seg2e"],
+                       "dest_pos": dest_pos, "routing": routing, "capacity": st["capacity"]}
         return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
 
     def forward(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
         """Returns (y [rows_received, n], plan).  y's rows are ordered (source rank, local expert)."""
         from . import ops
 
+        if self._grad is not None and self.world > 1:
+            self._grad["pulled"] = True  # this step's count exchange orders the gradient buffers
         if self.dispatch == "p2p":
             return self.forward_p2p(x_tokens, routing, timed=timed)
-        if self.dispatch == "overlap":
-            return self.forward_overlap(x_tokens, routing, timed=timed)
         if self.dispatch == "fused":
             return self.forward_fused(x_tokens, routing, timed=timed)
 
@@ -368,22 +326,128 @@ class ExpertParallelRaggedDot:
         if timed:
             ev[3].record()
             self._events.append(ev)
+        self._saved = {"recv": received, "plan": plan, "tokens": x_tokens.shape[0]}
         return y, plan
 
+    # ------------------------------------------------------------------ backward
+    def _grad_setup(self, capacity_rows: int):
+        """Buffer of gradient rows (dlhs over the received layout) in symmetric memory, so the
+        ranks the rows came from can pull them back."""
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+
+        dev = self.device
+        buf = symm_mem.empty((capacity_rows, self.k), dtype=self.dtype, device=dev)
+        if self.world > 1:
+            hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+        else:
+            hdl, ptrs = None, [buf.data_ptr()]
+        self._grad = {"buf": buf, "hdl": hdl, "capacity": capacity_rows,
+                      "peer_base": torch.tensor(ptrs, dtype=torch.int64, device=dev),
+                      "ws": ops._workspace(capacity_rows, self.num_experts, dev),
+                      "ws_tgmm": ops._workspace(capacity_rows, self.num_experts, dev),
+                      "pulled": True}
+
+    def backward(self, dy: torch.Tensor, timed: bool = False):
+        """VJP of the last ``forward`` with the reference's wiring (gpu_ragged_dot.py:399-402) on the
+        sharded layout.  ``dy`` is the cotangent of the y that forward returned, same rows.
+
+        Returns (dx_tokens [T, k], dW [local experts, k, n]):
+          dlhs  rows = rd_gmm_indexed(dy, W, trans_rhs) over the received segments, on the owner;
+                they go back to the tokens' ranks and the top_k copies of a token are summed
+                (p2p / fused: ``rd_ep_combine_pull`` reads them from the owners' buffers after a
+                cross-rank barrier; nccl: the reverse all-to-all, then an index_add);
+          drhs  = rd_tgmm_strided over the received rows: local expert j sums its W segments.
+        Stream-ordered; in the p2p / fused modes nothing is read on the host."""
+        from . import _lib, ops
+
+        sv = self._saved
+        if sv is None:
+            raise RuntimeError("backward needs a forward first")
+        W, El = self.world, self.local_experts
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
+        if timed:
+            ev[0].record()
+        cfg = _lib.TileCfg(0, 0, 0, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        if self.dispatch == "nccl":
+            plan, recv = sv["plan"], sv["recv"]
+            dy = dy[: recv.shape[0]].contiguous()
+            d_recv = ops.gmm_forward(dy, self.weights, plan.segment_sizes, trans_rhs=True,
+                                     group_to_weight=plan.segment_to_expert, cfg=cfg)
+            if timed:
+                ev[1].record()
+            dW = ops.tgmm_forward(recv, dy, plan.segment_sizes, seg_count=W)
+            if timed:
+                ev[2].record()
+            d_sorted = torch.empty((sum(plan.send_splits), self.k), dtype=self.dtype, device=self.device)
+            if W > 1:
+                dist.all_to_all_single(d_sorted, d_recv, output_split_sizes=plan.send_splits,
+                                       input_split_sizes=plan.recv_splits, group=self.group)
+            else:
+                d_sorted.copy_(d_recv)
+            dx = torch.zeros((sv["tokens"], self.k), dtype=torch.float32, device=self.device)
+            dx.index_add_(0, plan.token_index.long(), d_sorted.float())
+            dx = dx.to(self.dtype)
+            if timed:
+                ev[3].record()
+                self._bwd_events.append(ev)
+            return dx, dW
+        cap = sv["capacity"]
+        if getattr(self, "_grad", None) is None:
+            self._grad_setup(cap)
+        gr = self._grad
+        assert dy.shape == (cap, self.n) and dy.is_contiguous()
+        if not gr["pulled"] and gr["hdl"] is not None:
+            gr["hdl"].barrier(channel=1)  # two backward calls in a row: the last pull has finished everywhere
+        ops.gmm_forward(dy, self.weights, sv["seg"], trans_rhs=True, group_to_weight=sv["seg2e"], cfg=cfg,
+                        out=gr["buf"], workspace=gr["ws"])
+        if timed:
+            ev[1].record()
+        # drhs is local work: it runs while the other ranks finish their dlhs
+        dW = ops.tgmm_forward(sv["recv"], dy, sv["seg"], seg_count=W, workspace=gr["ws_tgmm"])
+        if timed:
+            ev[2].record()
+        if gr["hdl"] is not None:
+            gr["hdl"].barrier(channel=0)  # every owner's gradient rows are complete
+        dx = ops.ep_combine_pull(sv["routing"], sv["dest_pos"], self.num_experts, W, gr["peer_base"], cap,
+                                 self.k, self.dtype)
+        gr["pulled"] = False
+        if timed:
+            ev[3].record()
+            self._bwd_events.append(ev)
+        return dx, dW
+
+    def backward_timers_ms(self, steps: int):
+        torch.cuda.synchronize(self.device)
+        names = ("dlhs_gemm", "drhs_tgmm", "return_exchange_and_combine")
+        tot = dict.fromkeys(names, 0.0)
+        for e in self._bwd_events:
+            for i, nm in enumerate(names):
+                tot[nm] += e[i].elapsed_time(e[i + 1])
+        return {k: v / max(steps, 1) for k, v in tot.items()}
+
     # ------------------------------------------------------------------ host-resident tokens
-    def forward_host(self, x_host: torch.Tensor, routing_host: torch.Tensor, y_host: torch.Tensor) -> int:
+    def forward_host(self, x_host: torch.Tensor, routing_host: torch.Tensor, y_host: torch.Tensor,
+                     rows_host: Optional[torch.Tensor] = None) -> int:
         """One step for a caller whose tokens, routing and result live in pinned host memory.
 
         The copy-in goes to one of two device slots on a copy stream, so the tokens of step i+1
         cross PCIe while step i is exchanged, multiplied and copied out (on a third stream); the
         step itself is ``forward`` on the current stream.  Copies ``min(len(y_host), rows of y)``
-        rows of the result into ``y_host`` and returns that count.  ``wait_host_outputs`` orders
-        the current stream after the last copy-out."""
+        rows of the result into ``y_host`` and returns that count, an upper bound: in the p2p and
+        fused modes y has the receive buffer's capacity and only the rows this rank received are
+        defined.  ``rows_host`` (pinned int32 [1]) receives that number of defined rows with the
+        result, i.e. it is valid once the copy-out has finished.  ``wait_host_outputs`` orders the
+        current stream after the last copy-out."""
         for name, t in (("x_host", x_host), ("routing_host", routing_host), ("y_host", y_host)):
             if t.is_cuda or not t.is_pinned():
                 raise ValueError(f"{name} must be a pinned host tensor")
         if routing_host.dtype != torch.int32:
             raise ValueError("routing_host must be int32")
+        if rows_host is not None and (rows_host.is_cuda or not rows_host.is_pinned()
+                                      or rows_host.dtype != torch.int32 or rows_host.numel() < 1):
+            raise ValueError("rows_host must be a pinned int32 host tensor with one element")
         dev = self.device
         if self._host is None:
             self._host = {
@@ -409,7 +473,8 @@ class ExpertParallelRaggedDot:
         cur.wait_event(arrived)
         if h["out"] is not None:  # the result buffer of the previous step is still being copied out
             cur.wait_event(h["out"])
-        y = self.forward(h["x"][slot], h["r"][slot])[0]
+        res = self.forward(h["x"][slot], h["r"][slot])
+        y = res[0]
         done = torch.cuda.Event()
         done.record(cur)
         h["read"][slot] = done
@@ -418,11 +483,55 @@ class ExpertParallelRaggedDot:
             s_out.wait_event(done)
             y_host[:rows].copy_(y[:rows], non_blocking=True)
             y.record_stream(s_out)
+            if rows_host is not None:
+                if self.dispatch == "nccl":
+                    rows_host[0] = res[1].rows_received
+                else:
+                    rows_host[:1].copy_(res[3][:1], non_blocking=True)
+                    res[3].record_stream(s_out)
             h["out"] = torch.cuda.Event()
             h["out"].record(s_out)
         return rows
 
+    def backward_host(self, dy_host: torch.Tensor, rows: int, dx_host: torch.Tensor, dW_host: torch.Tensor) -> None:
+        """``backward`` for a caller whose cotangent and gradients live in pinned host memory: the
+        first ``rows`` rows of ``dy_host`` (the rows this rank received in the last forward; see
+        ``forward_host``'s ``rows_host``) are copied in on the copy-in stream, the gradients leave on
+        the copy-out stream.  Rows of the device-side cotangent past ``rows`` are not read by the
+        kernels (they lie outside every segment)."""
+        for name, t in (("dy_host", dy_host), ("dx_host", dx_host), ("dW_host", dW_host)):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError(f"{name} must be a pinned host tensor")
+        if self._host is None or self._saved is None:
+            raise RuntimeError("backward_host needs a forward_host first")
+        h, dev = self._host, self.device
+        full_rows = self._saved["recv"].shape[0]
+        if h.get("dy") is None or h["dy"].shape[0] != full_rows:
+            h["dy"] = torch.empty((full_rows, self.n), dtype=self.dtype, device=dev)
+            h["dy_read"] = None
+        rows = min(int(rows), full_rows, dy_host.shape[0])
+        cur = torch.cuda.current_stream(dev)
+        arrived = torch.cuda.Event()
+        with torch.cuda.stream(h["s_in"]):
+            if h["dy_read"] is not None:
+                h["s_in"].wait_event(h["dy_read"])
+            h["dy"][:rows].copy_(dy_host[:rows], non_blocking=True)
+            arrived.record(h["s_in"])
+        cur.wait_event(arrived)
+        dx, dW = self.backward(h["dy"])
+        done = torch.cuda.Event()
+        done.record(cur)
+        h["dy_read"] = done
+        with torch.cuda.stream(h["s_out"]):
+            h["s_out"].wait_event(done)
+            dx_host.copy_(dx, non_blocking=True)
+            dW_host.copy_(dW, non_blocking=True)
+            dx.record_stream(h["s_out"])
+            dW.record_stream(h["s_out"])
+            h["out"] = torch.cuda.Event()
+            h["out"].record(h["s_out"])
+
     def wait_host_outputs(self) -> None:
-        """Make the current stream wait for the last ``forward_host`` copy-out."""
+        """Make the current stream wait for the last ``forward_host`` / ``backward_host`` copy-out."""
         if self._host is not None and self._host["out"] is not None:
             torch.cuda.current_stream(self.device).wait_event(self._host["out"])

@@ -11,7 +11,10 @@ Differences from the reference, all deliberate:
     (``tile_table.py``), which replaces the tune-jax search of tuning.py:49-58.
   * ``interpret=True`` raises: there is no CPU path.
   * float32 inputs are multiplied as TF32 on the tensor cores with fp32 accumulation and give
-    float32 results (the precision the reference's Triton ``tl.dot`` uses for float32).
+    float32 results (the precision the reference's Triton ``tl.dot`` uses for float32);
+    ``precision="highest"`` (an extra keyword) runs three TF32 passes for nearly fp32 accuracy.
+  * ``compute_dtype`` casts both operands before the product and the result comes back in
+    ``x.dtype``, as in the reference (gpu_ragged_dot.py:116,145,149); the two inputs may differ in type.
   * rows past ``sum(group_sizes)`` are always zero, also when every group is empty (the
     reference leaves them unwritten in that case, gpu_ragged_dot.py:155-157).
   * the VJP of ``tgmm`` is the mathematically correct one; the reference's
@@ -21,6 +24,7 @@ Differences from the reference, all deliberate:
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import NamedTuple, Optional, Sequence
 
 import torch
@@ -124,6 +128,20 @@ def _cfg_ptr(cfg: Optional[_lib.TileCfg]):
     return ctypes.byref(cfg) if cfg is not None else None
 
 
+def _check_status_enabled() -> bool:
+    return os.environ.get("RD_CHECK_STATUS", "0") not in ("", "0")
+
+
+def _maybe_check_status(workspace: torch.Tensor, where: str) -> None:
+    """With RD_CHECK_STATUS=1 every GEMM call synchronises its stream and raises if a bounded wait
+    expired inside the kernel (the output then has unwritten tiles).  Off by default: the check
+    costs a device synchronisation per call."""
+    if _check_status_enabled():
+        code = device_status(workspace)
+        if code != 0:
+            raise _lib.RaggedDotError(code, _lib.status_string(code), where)
+
+
 def make_group_metadata(group_sizes: torch.Tensor, m: int, chunk_m: int) -> GMMGroupLookupMetadata:
     """Device-side equivalent of ``_make_gmm_group_metadata`` (gpu_ragged_dot.py:70-90)."""
     lib = _lib.load()
@@ -218,6 +236,7 @@ def gmm_forward(
                 _stream_ptr(x.device),
             )
     _lib.check(rc, "rd_gmm")
+    _maybe_check_status(ws, "rd_gmm")
     if padded_n:
         y = y[:, :n].contiguous()
         if out is not None:
@@ -293,7 +312,7 @@ def ep_dispatch(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world:
 
 
 def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = None) -> dict:
-    """``rd_ep_plan_ring``: the plan of the overlapped exchange (receive buffer ordered by position
+    """``rd_ep_plan_ring``: the plan of the fused exchange (receive buffer ordered by position
     q = (rank - source) mod W).  Returns / refills a dict with dest_offset[E], segment_sizes[E],
     fill[E], totals[1], phase_done[W], send_start[W+1], list_fill[W]."""
     lib = _lib.load()
@@ -312,25 +331,6 @@ def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = Non
                                  bufs["send_start"].data_ptr(), bufs["list_fill"].data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "rd_ep_plan_ring")
     return bufs
-
-
-def ep_dispatch_phase(x: torch.Tensor, routing: torch.Tensor, num_experts: int, world: int, rank: int,
-                      phase: int, plan: dict, dest_base: int, capacity_rows: int, dest_pos: torch.Tensor,
-                      dest_ready_flag: int, epoch: int, max_blocks: int = 0) -> None:
-    """``rd_ep_dispatch_phase`` on the current stream: rows for rank (rank + phase) % world go to the
-    buffer at address ``dest_base``; ``dest_ready_flag`` is the address of word ``phase`` of that
-    rank's flag array."""
-    lib = _lib.load()
-    _require_cuda(x, "x")
-    assert x.is_contiguous() and routing.dtype == torch.int32 and routing.is_contiguous()
-    tokens, top_k = routing.shape
-    with torch.cuda.device(x.device):
-        rc = lib.rd_ep_dispatch_phase(
-            x.data_ptr(), routing.data_ptr(), tokens, top_k, x.shape[1] * x.element_size(), num_experts, world,
-            rank, phase, plan["dest_offset"].data_ptr(), plan["fill"].data_ptr(), dest_base, capacity_rows,
-            dest_pos.data_ptr(), plan["phase_done"].data_ptr(), dest_ready_flag, epoch, max_blocks,
-            _stream_ptr(x.device))
-    _lib.check(rc, "rd_ep_dispatch_phase")
 
 
 def ep_assign(routing: torch.Tensor, num_experts: int, world: int, rank: int, plan: dict, capacity_rows: int,
@@ -379,6 +379,7 @@ def gmm_ep_fused(recv: torch.Tensor, A: torch.Tensor, segment_sizes: torch.Tenso
             _cfg_ptr(cfg), flags.data_ptr(), int(groups_per_flag), int(epoch), ctypes.byref(send),
             _stream_ptr(recv.device))
     _lib.check(rc, "rd_gmm_ep_fused")
+    _maybe_check_status(workspace, "rd_gmm_ep_fused")
     return out
 
 
@@ -389,8 +390,12 @@ def tgmm_forward(
     cfg: Optional[_lib.TileCfg] = None,
     out: Optional[torch.Tensor] = None,
     workspace: Optional[torch.Tensor] = None,
+    seg_count: int = 1,
 ) -> torch.Tensor:
-    """One call of ``rd_tgmm``: out[g,k,n] = x_g^T . y_g over each group's rows."""
+    """One call of ``rd_tgmm``: out[g,k,n] = x_g^T . y_g over each group's rows.
+
+    With ``seg_count > 1`` it is ``rd_tgmm_strided``: ``group_sizes`` has ``g * seg_count`` entries
+    and block i sums the groups i, i + g, i + 2g, ... (the expert-parallel receive layout)."""
     lib = _lib.load()
     _require_cuda(x, "x")
     _require_cuda(y, "y")
@@ -399,7 +404,8 @@ def tgmm_forward(
     if x.dtype not in _DTYPE_CODE or y.dtype != x.dtype:
         raise NotImplementedError(f"inputs must both be float16, bfloat16 or float32, got {x.dtype} / {y.dtype}")
     (m, k), n = x.shape, y.shape[-1]
-    g = gs.numel()
+    assert seg_count >= 1 and gs.numel() % seg_count == 0
+    g = gs.numel() // seg_count
     mult = 16 // x.element_size()
     xp = _dense16(_pad_last(x, mult))
     yp = _dense16(_pad_last(y, mult))
@@ -410,21 +416,50 @@ def tgmm_forward(
         res = out
     else:
         res = torch.empty((g, kp, np_), dtype=x.dtype, device=x.device)
-    ws = workspace if workspace is not None else _workspace(m, g, x.device)
-    if cfg is None:
+    ws = workspace if workspace is not None else _workspace(m, gs.numel(), x.device)
+    if cfg is None and seg_count == 1:
         cfg = tile_table.lookup("tgmm", m, kp, np_, g)
     with torch.cuda.device(x.device):
-        rc = lib.rd_tgmm(
-            xp.data_ptr(), yp.data_ptr(), gs.data_ptr(), res.data_ptr(), ws.data_ptr(), ws.numel(),
-            m, kp, np_, g, _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
-        )
+        if seg_count == 1:
+            rc = lib.rd_tgmm(
+                xp.data_ptr(), yp.data_ptr(), gs.data_ptr(), res.data_ptr(), ws.data_ptr(), ws.numel(),
+                m, kp, np_, g, _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+            )
+        else:
+            rc = lib.rd_tgmm_strided(
+                xp.data_ptr(), yp.data_ptr(), gs.data_ptr(), res.data_ptr(), ws.data_ptr(), ws.numel(),
+                m, kp, np_, g, int(seg_count), _DTYPE_CODE[x.dtype], _cfg_ptr(cfg), _stream_ptr(x.device),
+            )
     _lib.check(rc, "rd_tgmm")
+    _maybe_check_status(ws, "rd_tgmm")
     if padded:
         res = res[:, :k, :n].contiguous()
         if out is not None:
             out.copy_(res)
             res = out
     return res
+
+
+def ep_combine_pull(routing: torch.Tensor, dest_pos: torch.Tensor, num_experts: int, world: int,
+                    peer_base: torch.Tensor, capacity_rows: int, k: int, dtype: torch.dtype,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``rd_ep_combine_pull``: out[t] = sum over the top_k slots of the gradient rows the owners
+    hold at ``dest_pos``; ``peer_base`` is an int64 device tensor of `world` buffer addresses."""
+    lib = _lib.load()
+    r = _as_i32(routing)
+    tokens, top_k = r.shape
+    pos = _as_i32(dest_pos.reshape(-1))
+    assert pos.numel() == tokens * top_k
+    assert peer_base.dtype == torch.int64 and peer_base.numel() == world and peer_base.is_cuda
+    if out is None:
+        out = torch.empty((tokens, k), dtype=dtype, device=r.device)
+    assert out.shape == (tokens, k) and out.dtype == dtype and out.is_contiguous()
+    with torch.cuda.device(r.device):
+        rc = lib.rd_ep_combine_pull(r.data_ptr(), pos.data_ptr(), tokens, top_k, k * out.element_size(),
+                                    num_experts, world, peer_base.data_ptr(), capacity_rows,
+                                    _DTYPE_CODE[dtype], out.data_ptr(), _stream_ptr(r.device))
+    _lib.check(rc, "rd_ep_combine_pull")
+    return out
 
 
 def gmm_permuted_forward(
@@ -665,72 +700,137 @@ def ragged_dot_permuted(x, A, group_sizes, in_rows=None, out_rows=None, y_rows=N
 
 
 def _check_static_args(x, interpret, compute_dtype, acc_dtype):
+    """Returns the torch dtype the product is computed in (None: the inputs' own)."""
     if interpret:
         raise NotImplementedError(
             "interpret=True is not supported: this build has no CPU path (CUDA sm_100a only)"
         )
-    if compute_dtype is not None and _torch_dtype(compute_dtype) != x.dtype:
-        raise NotImplementedError(
-            f"compute_dtype={compute_dtype} differs from the input dtype {x.dtype}; only None or the "
-            "input dtype is implemented"
-        )
     if acc_dtype is not None and _torch_dtype(acc_dtype) != torch.float32:
         raise NotImplementedError(f"acc_dtype={acc_dtype}: only float32 accumulation is implemented")
+    if compute_dtype is None:
+        return None
+    cd = _torch_dtype(compute_dtype)
+    if cd not in _DTYPE_CODE:
+        raise NotImplementedError(f"compute_dtype={compute_dtype}: float16, bfloat16 or float32")
+    return cd
+
+
+def _check_precision(precision):
+    if precision not in (None, "default", "highest"):
+        raise NotImplementedError(f"precision={precision!r}: None / 'default' (one TF32 pass for float32) or 'highest'")
 
 
 def _torch_dtype(d):
     if isinstance(d, torch.dtype):
         return d
     name = getattr(d, "name", None) or getattr(d, "__name__", None) or str(d)
-    table = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+    table = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
+             "float64": torch.float64}
     if name in table:
         return table[name]
     raise NotImplementedError(f"unknown dtype {d!r}")
 
 
+def _gmm_cast(x, A, group_sizes, trans_rhs, compute_dtype, precision):
+    """The reference's cast -> dot -> cast (gpu_ragged_dot.py:116,145,149): both operands go to
+    ``compute_dtype`` (default: x's type), the product is accumulated in fp32, the result comes
+    back in x's type."""
+    cd = compute_dtype or x.dtype
+    if cd == torch.float32 and precision == "highest":
+        y = _gmm_3xtf32(x.to(cd), A.to(cd), group_sizes, trans_rhs)
+    else:
+        y = gmm_forward(x.to(cd), A.to(cd), group_sizes, trans_rhs=trans_rhs)
+    return y.to(x.dtype)
+
+
+def _tgmm_cast(x, y, group_sizes, compute_dtype, precision):
+    cd = compute_dtype or x.dtype
+    if cd == torch.float32 and precision == "highest":
+        out = _tgmm_3xtf32(x.to(cd), y.to(cd), group_sizes)
+    else:
+        out = tgmm_forward(x.to(cd), y.to(cd), group_sizes)
+    return out.to(x.dtype)
+
+
+def _split_tf32(t: torch.Tensor):
+    """t = hi + lo exactly, hi holding the top 10 explicit mantissa bits rounded to nearest (a
+    value the tensor cores read without loss) and lo the remainder."""
+    bits = t.contiguous().view(torch.int32)
+    hi = ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
+    hi = torch.where(torch.isfinite(hi), hi, t)  # rounding up the largest finite values would overflow
+    return hi, t - hi
+
+
+def _gmm_3xtf32(x, A, group_sizes, trans_rhs):
+    """float32 product to nearly fp32 accuracy on the TF32 tensor cores: with x = xh + xl and
+    A = Ah + Al (TF32 head + remainder), x.A ~ xh.Ah + xh.Al + xl.Ah; the dropped xl.Al term is
+    2^-22 relative.  Three passes of the TF32 kernel, summed in fp32, small terms first."""
+    xh, xl = _split_tf32(x)
+    Ah, Al = _split_tf32(A)
+    ws = _workspace(x.shape[0], _as_i32(group_sizes).numel(), x.device)
+    y = gmm_forward(xl, Ah, group_sizes, trans_rhs=trans_rhs, workspace=ws)
+    y += gmm_forward(xh, Al, group_sizes, trans_rhs=trans_rhs, workspace=ws)
+    y += gmm_forward(xh, Ah, group_sizes, trans_rhs=trans_rhs, workspace=ws)
+    return y
+
+
+def _tgmm_3xtf32(x, y, group_sizes):
+    xh, xl = _split_tf32(x)
+    yh, yl = _split_tf32(y)
+    ws = _workspace(x.shape[0], _as_i32(group_sizes).numel(), x.device)
+    out = tgmm_forward(xl, yh, group_sizes, workspace=ws)
+    out += tgmm_forward(xh, yl, group_sizes, workspace=ws)
+    out += tgmm_forward(xh, yh, group_sizes, workspace=ws)
+    return out
+
+
 class _GmmFn(torch.autograd.Function):
-    """custom_vjp of gmm: gpu_ragged_dot.py:383-405."""
+    """custom_vjp of gmm: gpu_ragged_dot.py:383-405.  compute_dtype travels to the backward
+    products as in the reference (its ``kw`` dict, :395-401)."""
 
     @staticmethod
-    def forward(ctx, x, A, group_sizes, trans_rhs):
-        ctx.trans_rhs = trans_rhs
+    def forward(ctx, x, A, group_sizes, trans_rhs, compute_dtype, precision):
+        ctx.trans_rhs, ctx.compute_dtype, ctx.precision = trans_rhs, compute_dtype, precision
         ctx.save_for_backward(x, A, group_sizes)  # residuals (x, A, group_sizes), reference :227
-        return gmm_forward(x, A, group_sizes, trans_rhs=trans_rhs)
+        return _gmm_cast(x, A, group_sizes, trans_rhs, compute_dtype, precision)
 
     @staticmethod
     def backward(ctx, do):
         x, A, group_sizes = ctx.saved_tensors
+        cd, pr = ctx.compute_dtype, ctx.precision
         do = do.contiguous()
         dx = dA = None
         if ctx.needs_input_grad[0]:
-            dx = gmm_forward(do, A, group_sizes, trans_rhs=not ctx.trans_rhs)
+            dx = _gmm_cast(do, A, group_sizes, not ctx.trans_rhs, cd, pr).to(x.dtype)
         if ctx.needs_input_grad[1]:
             dA = (
-                tgmm_forward(x, do, group_sizes)
+                _tgmm_cast(x, do, group_sizes, cd, pr)
                 if not ctx.trans_rhs
-                else tgmm_forward(do, x, group_sizes)
-            )
-        return dx, dA, None, None
+                else _tgmm_cast(do, x, group_sizes, cd, pr)
+            ).to(A.dtype)
+        return dx, dA, None, None, None, None
 
 
 class _TgmmFn(torch.autograd.Function):
     """VJP of tgmm.  out[g] = x_g^T y_g  =>  dx_g = y_g dout[g]^T,  dy_g = x_g dout[g]."""
 
     @staticmethod
-    def forward(ctx, x, y, group_sizes):
+    def forward(ctx, x, y, group_sizes, compute_dtype, precision):
+        ctx.compute_dtype, ctx.precision = compute_dtype, precision
         ctx.save_for_backward(x, y, group_sizes)
-        return tgmm_forward(x, y, group_sizes)
+        return _tgmm_cast(x, y, group_sizes, compute_dtype, precision)
 
     @staticmethod
     def backward(ctx, do):
         x, y, group_sizes = ctx.saved_tensors
+        cd, pr = ctx.compute_dtype, ctx.precision
         do = do.contiguous()
         dx = dy = None
         if ctx.needs_input_grad[0]:
-            dx = gmm_forward(y, do, group_sizes, trans_rhs=True)
+            dx = _gmm_cast(y, do, group_sizes, True, cd, pr).to(x.dtype)
         if ctx.needs_input_grad[1]:
-            dy = gmm_forward(x, do, group_sizes, trans_rhs=False)
-        return dx, dy, None
+            dy = _gmm_cast(x, do, group_sizes, False, cd, pr).to(y.dtype)
+        return dx, dy, None, None, None
 
 
 def gmm(
@@ -747,13 +847,19 @@ def gmm(
     num_warps: Optional[int] = None,
     num_stages: Optional[int] = None,
     chunk_m: int = CHUNK_M,
+    *,
+    precision: Optional[str] = None,
 ) -> torch.Tensor:
     """Ragged dot corresponding to jax.lax.ragged_dot: (m, k) x (g, k, n) -> (m, n).
 
-    Signature of the reference's ``gmm`` (gpu_ragged_dot.py:362-376)."""
+    Signature of the reference's ``gmm`` (gpu_ragged_dot.py:362-376) plus ``precision``:
+    ``"highest"`` computes a float32 product to nearly fp32 accuracy (three TF32 passes); the
+    default is one TF32 pass, the precision the reference's kernel and jax.lax.ragged_dot have
+    for float32 on NVIDIA GPUs."""
     del block_m, block_k, block_n, num_warps, num_stages, chunk_m  # hints; the tile table decides
-    _check_static_args(x, interpret, compute_dtype, acc_dtype)
-    return _GmmFn.apply(x, A, group_sizes, bool(trans_rhs))
+    cd = _check_static_args(x, interpret, compute_dtype, acc_dtype)
+    _check_precision(precision)
+    return _GmmFn.apply(x, A, group_sizes, bool(trans_rhs), cd, precision)
 
 
 def tgmm(
@@ -769,13 +875,16 @@ def tgmm(
     num_warps: Optional[int] = None,
     num_stages: Optional[int] = None,
     chunk_m: int = CHUNK_M,
+    *,
+    precision: Optional[str] = None,
 ) -> torch.Tensor:
     """Transposed ragged dot: (m, k) x (m, n) -> (g, k, n).
 
-    Signature of the reference's ``tgmm`` (gpu_ragged_dot.py:411-424)."""
+    Signature of the reference's ``tgmm`` (gpu_ragged_dot.py:411-424) plus ``precision`` (see gmm)."""
     del block_m, block_k, block_n, num_warps, num_stages, chunk_m
-    _check_static_args(x, interpret, compute_dtype, acc_dtype)
-    return _TgmmFn.apply(x, y, group_sizes)
+    cd = _check_static_args(x, interpret, compute_dtype, acc_dtype)
+    _check_precision(precision)
+    return _TgmmFn.apply(x, y, group_sizes, cd, precision)
 
 
 ragged_dot = gmm

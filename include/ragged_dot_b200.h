@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define RD_VERSION 1
+#define RD_VERSION 2
 
 enum rd_error {
   RD_OK = 0,
@@ -61,7 +61,11 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1, RD_DTYPE_F32 = 2 };
  *   tile_m    : 128, or 256 = one CTA computes 256-row tiles as two 128-row halves sharing
  *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice.
  *   flags     : RD_CFG_NO_ZERO_TAIL = rd_gmm leaves the rows past sum(group_sizes) unwritten
- *               (for callers that pass an upper bound as m and never read those rows). */
+ *               (for callers that pass an upper bound as m and never read those rows).
+ *   wait_limit_ms : how long a wait inside a kernel (on a pipeline barrier, on a ready flag of
+ *               rd_gmm_indexed_when_ready) may last before the kernel gives up, records
+ *               RD_ERR_DEVICE_WAIT in the status word and returns; 0 = the environment variable
+ *               RD_WAIT_LIMIT_MS if set, else 2000. */
 #define RD_CFG_NO_ZERO_TAIL 1
 typedef struct rd_tile_cfg {
   int32_t tile_n;
@@ -69,6 +73,7 @@ typedef struct rd_tile_cfg {
   int32_t cta_group;
   int32_t tile_m;
   int32_t flags;
+  int32_t wait_limit_ms;
 } rd_tile_cfg;
 
 int rd_version(void);
@@ -132,34 +137,26 @@ int rd_ep_dispatch(const void* x, const int32_t* routing, int tokens, int top_k,
                    int num_experts, int world, const int32_t* dest_offset, int32_t* fill,
                    const uint64_t* peer_base, int capacity_rows, int32_t* dest_pos, void* stream);
 
-/* Expert-parallel dispatch overlapped with the local GEMM (same roles as the three functions
- * above, no counterpart in the reference).  The receive buffer of rank d is laid out by
- * "position" q = (d - source) mod world: d's own rows first, then those of d-1, d-2, ...
+/* Expert-parallel exchange running under the local GEMM (no counterpart in the reference).  The
+ * receive buffer of rank d is laid out by "position" q = (d - source) mod world: d's own rows
+ * first, then those of d-1, d-2, ...; a source sends to rank + p in phase p, so in every phase the
+ * ranks form a permutation and each NVLink port carries one flow.
  *   rd_ep_plan_ring       as rd_ep_plan for that layout (segment q*El + j = rows from source
  *                         (rank - q) mod world for local expert j); resets phase_done[world].
- *   rd_ep_dispatch_phase  phase p of the exchange, p = 0 .. world-1, launched in that order on one
- *                         stream: copies the rows routed to rank (rank + p) mod world into
- *                         dest_base (that rank's buffer as seen from this GPU) and, when its last
- *                         block is done, stores `epoch` to *dest_ready_flag, which must be word p of
- *                         that rank's flag array.  In phase p the ranks form the permutation
- *                         r -> r + p, so every NVLink port carries one flow at a time.
- *                         max_blocks caps the grid (0 = two blocks per SM).
  *   rd_gmm_indexed_when_ready  rd_gmm_indexed whose loader, before it reads the rows of group i,
  *                         waits (bounded: expiry gives RD_ERR_DEVICE_WAIT through the status word)
- *                         until ready_flags[i / groups_per_flag] >= epoch.  Launched right after
- *                         the plan, it multiplies position q while positions q+1.. are still
- *                         arriving.  Epochs must increase from call to call; flags start at 0.
- * The caller keeps one exchange in flight per buffer: a rank may start the next exchange only
- * when every rank has finished reading its buffer (e.g. the all-gather of the next counts, issued
- * after the GEMM in stream order).  Plain peer stores and loads of flags only. */
+ *                         until ready_flags[i / groups_per_flag] >= epoch.  It multiplies position
+ *                         q while positions q+1.. are still arriving.  Epochs must increase from
+ *                         call to call; flags start at 0.
+ * Whoever raises the flags must be certain to run while this kernel waits: kernels launched
+ * separately on the same GPU are NOT (a persistent grid that fills every SM can keep them from
+ * ever being placed), which is why the senders of rd_gmm_ep_fused below are CTAs of the same
+ * launch.  The caller keeps one exchange in flight per buffer: a rank may start the next exchange
+ * only when every rank has finished reading its buffer (e.g. the all-gather of the next counts,
+ * issued after the GEMM in stream order).  Plain peer stores and loads of flags only. */
 int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int rank,
                     int32_t* dest_offset, int32_t* segment_sizes, int32_t* fill, int32_t* totals,
                     int32_t* phase_done, int32_t* send_start, int32_t* list_fill, void* stream);
-int rd_ep_dispatch_phase(const void* x, const int32_t* routing, int tokens, int top_k, int row_bytes,
-                         int num_experts, int world, int rank, int phase, const int32_t* dest_offset,
-                         int32_t* fill, void* dest_base, int capacity_rows, int32_t* dest_pos,
-                         int32_t* phase_done, int32_t* dest_ready_flag, int epoch, int max_blocks,
-                         void* stream);
 int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
                               const int32_t* group_to_weight, void* y, void* workspace,
                               size_t workspace_bytes, int m, int k, int n, int g, int trans_rhs,
@@ -209,6 +206,29 @@ int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t
 int rd_tgmm(const void* x, const void* dout, const int32_t* group_sizes, void* out,
             void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int dtype,
             const rd_tile_cfg* cfg, void* stream);
+
+/* rd_tgmm over strided segments: group_sizes has g * seg_count entries and output block i
+ * (of g) is the sum over q < seg_count of x_s^T . dout_s for the rows of group s = i + q * g.
+ * No counterpart in the reference.  It is the drhs of the expert-parallel layout, where the
+ * rows received from seg_count source ranks form seg_count * g consecutive segments and segment
+ * (q, i) belongs to local expert i: the per-expert weight gradient sums over the sources without
+ * re-sorting the rows.  16-bit types; seg_count == 1 is rd_tgmm. */
+int rd_tgmm_strided(const void* x, const void* dout, const int32_t* group_sizes, void* out,
+                    void* workspace, size_t workspace_bytes, int m, int k, int n, int g, int seg_count,
+                    int dtype, const rd_tile_cfg* cfg, void* stream);
+
+/* Reverse exchange of the expert-parallel backward pass fused with the top-k combine (no
+ * counterpart in the reference): out[t, :] = sum over the top_k slots s of row
+ * dest_pos[t * top_k + s] of the buffer of the rank that owns expert routing[t * top_k + s].
+ * peer_base[r] (device array of `world` addresses) is rank r's [capacity_rows, row_bytes] buffer
+ * of gradient rows (its rd_gmm_indexed(dout, A, trans_rhs) result over the received layout) as
+ * seen from this GPU; rows are pulled with plain peer loads, summed in fp32 and written as one
+ * 16-bit row per token.  Slots with an expert outside [0, num_experts) or a position outside
+ * [0, capacity_rows) add nothing.  top_k <= 8.  The caller orders this call after every owner's
+ * GEMM (a cross-rank barrier) and keeps the buffers unchanged until every rank has pulled. */
+int rd_ep_combine_pull(const int32_t* routing, const int32_t* dest_pos, int tokens, int top_k,
+                       int row_bytes, int num_experts, int world, const uint64_t* peer_base,
+                       int capacity_rows, int dtype, void* out, void* stream);
 
 /* Grouped GEMMs with the row permutation of a mixture-of-experts layer fused in.  The
  * reference takes rows that are already sorted by group (gpu_ragged_dot.py:362-376) and leaves

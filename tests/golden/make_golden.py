@@ -327,12 +327,32 @@ METADATA_CASES = [
 ]
 
 GEMM_CASES = [
-    # name, m, k, n, g, fill_in, seed, random_inputs, block (m,k,n), chunk_m
-    ("odd_shapes", 171, 58, 77, 8, 0.7, 0, True, (16, 32, 64), 8),
-    ("aligned_g16", 128, 64, 64, 16, 1.0, 1, True, (64, 64, 64), 512),
-    ("half_filled", 256, 64, 128, 8, 0.5, 0, True, (32, 16, 32), 512),
-    ("all_ones", 171, 58, 77, 16, 0.7, 1, False, (64, 64, 16), 8),
+    # name, m, k, n, g, fill_in, seed, random_inputs, block (m,k,n), chunk_m, explicit group sizes
+    ("odd_shapes", 171, 58, 77, 8, 0.7, 0, True, (16, 32, 64), 8, None),
+    ("aligned_g16", 128, 64, 64, 16, 1.0, 1, True, (64, 64, 64), 512, None),
+    ("half_filled", 256, 64, 128, 8, 0.5, 0, True, (32, 16, 32), 512, None),
+    ("all_ones", 171, 58, 77, 16, 0.7, 1, False, (64, 64, 16), 8, None),
+    # groups of size zero at the start, in the middle, doubled and at the end: the reference's
+    # zero-tile branch (gpu_ragged_dot.py:277-281) and its skipped programs (:113-114) write these
+    ("empty_groups", 256, 64, 128, 8, 0.9, 2, True, (32, 32, 64), 64, [0, 57, 0, 0, 91, 1, 81, 0]),
+    # the small benchmark configuration: m 512, k 256, n 384, 8 groups, multinomial(Dirichlet(1))
+    # sizes with a forced empty group, A scaled by 1/sqrt(k).  Only the forward and the VJP of the
+    # plain layout are stored (the file is the largest fixture as it is).
+    ("baseline_small", 512, 256, 384, 8, 1.0, 3, True, (64, 64, 64), 512, "baseline_small"),
 ]
+
+
+def baseline_small_group_sizes():
+    """multinomial(512, Dirichlet(1)) over 8 groups with a forced empty group (seed 0): the same
+    draw as gpu_ragged_dot_b200.workloads.group_sizes_small, restated so that this script needs
+    nothing but NumPy and the reference."""
+    rng = np.random.default_rng(0)
+    gs = rng.multinomial(512, rng.dirichlet(np.ones(8))).astype(np.int32)
+    if not (gs == 0).any():
+        lo, hi = int(np.argmin(gs)), int(np.argmax(gs))
+        gs[hi] += gs[lo]
+        gs[lo] = 0
+    return gs
 
 
 def main():
@@ -353,18 +373,35 @@ def main():
     np.savez_compressed(os.path.join(HERE, "golden_metadata.npz"), **meta)
     print("metadata cases:", len(METADATA_CASES))
 
-    for name, m, k, n, g, fill, seed, rnd, (bm, bk, bn), chunk in GEMM_CASES:
+    for name, m, k, n, g, fill, seed, rnd, (bm, bk, bn), chunk, explicit in GEMM_CASES:
         rng = np.random.default_rng(1000 + seed)
+        small = explicit == "baseline_small"
         if rnd:
             x = rng.normal(size=(m, k)).astype(BF16)
-            A = rng.normal(size=(g, k, n)).astype(BF16)
+            A = (rng.normal(size=(g, k, n)) * (k ** -0.5 if small else 1.0)).astype(BF16)
             dout = rng.normal(size=(m, n)).astype(BF16)
         else:
             x, A, dout = (np.ones(s, dtype=BF16) for s in ((m, k), (g, k, n), (m, n)))
         target_m = max(min(round(m * fill), m), 0)
-        gs = group_sizes_like_reference_tests(seed + 17, g, target_m)
+        if small:
+            gs = baseline_small_group_sizes()
+        elif explicit is not None:
+            gs = np.array(explicit, dtype=np.int32)
+        else:
+            gs = group_sizes_like_reference_tests(seed + 17, g, target_m)
+        target_m = int(gs.sum())
         kw = dict(block_m=bm, block_k=bk, block_n=bn, chunk_m=chunk)
         y, _ = ref._gpu_gmm_fwd(x, A, gs, **kw)
+        if small:
+            bwd_args = (bm, bk, bn, False, False, None, np.float32, None, None, chunk)
+            dx, dA, _ = ref._gpu_gmm_bwd(*bwd_args, (x, A, gs), dout)
+            np.savez_compressed(
+                os.path.join(HERE, f"golden_gemm_{name}.npz"),
+                x=bits(x), A=bits(A), dout=bits(dout), group_sizes=gs,
+                params=np.array([m, k, n, g, bm, bk, bn, chunk, target_m], dtype=np.int32),
+                y=bits(y), dlhs=bits(dx), drhs=bits(dA))
+            print(f"{name}: gs={gs.tolist()} (forward + VJP only)")
+            continue
         At = np.ascontiguousarray(np.swapaxes(A, 1, 2))
         y_t, _ = ref._gpu_gmm_fwd(x, At, gs, trans_rhs=True, **kw)
         tg, _ = ref._gpu_tgmm_fwd(x, dout, gs, **kw)

@@ -18,7 +18,7 @@ def gemm_cases():
     out = []
     for path in sorted(glob.glob(os.path.join(GOLDEN_DIR, "golden_gemm_*.npz"))):
         z = np.load(path)
-        case = {k: bf16(z[k]) for k in BF16_KEYS}
+        case = {k: bf16(z[k]) for k in BF16_KEYS if k in z.files}  # the largest case stores a subset
         case["group_sizes"] = torch.from_numpy(z["group_sizes"].astype(np.int32))
         m, k, n, g, bm, bk, bn, chunk, target_m = (int(v) for v in z["params"])
         case.update(m=m, k=k, n=n, g=g, target_m=target_m, name=os.path.basename(path)[12:-4])

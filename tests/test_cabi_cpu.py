@@ -35,7 +35,7 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_version_and_status_strings(lib):
-    assert lib.rd_version() == 1
+    assert lib.rd_version() == 2
     assert _lib.status_string(0) == "ok"
     for code in range(1, 10):
         assert _lib.status_string(code) not in ("ok", "unknown status")
@@ -76,6 +76,23 @@ def test_argument_validation_happens_on_the_host(lib):
     assert tg(out=a16 + 8) == 3
     assert tg(ws_bytes=0) == 4
     assert tg(g=0) == 0
+    ts = lambda **kw: lib.rd_tgmm_strided(
+        a16, a16, a16, a16, a16, 1 << 20, 128, kw.get("k", 64), 64, kw.get("g", 2), kw.get("seg", 2),
+        kw.get("dtype", 1), cfg, None)
+    assert ts(seg=0) == 1
+    assert ts(k=60) == 1
+    assert ts(dtype=2, seg=2) == 5  # the float32 kernels have no strided form
+    assert ts(g=0) == 0
+    pull = lambda **kw: lib.rd_ep_combine_pull(
+        kw.get("routing", a16), a16, kw.get("tokens", 8), kw.get("top_k", 2), kw.get("row_bytes", 256),
+        kw.get("experts", 8), kw.get("world", 2), a16, 64, kw.get("dtype", 1), kw.get("out", a16), None)
+    assert pull(top_k=9) == 1
+    assert pull(row_bytes=250) == 1
+    assert pull(experts=7) == 1
+    assert pull(dtype=2) == 2
+    assert pull(routing=None) == 3
+    assert pull(out=a16 + 4) == 3
+    assert pull(tokens=0) == 0
     assert lib.rd_metadata(a16, -1, 16, 8, None, None, None, None, None) == 1
     assert lib.rd_metadata(a16, 4, 16, 0, None, None, None, None, None) == 1
     assert lib.rd_device_status(None, None) == 3

@@ -1,6 +1,8 @@
-"""Two-GPU expert-parallel check (skipped unless two CUDA devices are visible): the three
-dispatch modes -- NCCL all-to-all, peer stores + barrier, and the phased peer stores overlapped
-with the flag-gated local GEMM -- against a routing + GEMM oracle built from every rank's inputs.  Ranks are child processes, one per GPU; NVLS is switched off for the collectives."""
+"""Multi-GPU expert-parallel check at 2, 4 and 8 ranks (each skipped unless that many CUDA devices
+are visible): the three dispatch modes -- NCCL all-to-all, peer stores + barrier, and the exchange
+fused into the flag-gated GEMM launch -- forward and backward, against a routing + GEMM oracle
+built from every rank's inputs.  Ranks are child processes, one per GPU; NVLS is switched off for
+the collectives."""
 
 import os
 import socket
@@ -33,23 +35,25 @@ def _worker(rank, world, port, out_dir):
     x = workloads.normal_tensor((T, k), 1.0, 1000 + rank, dev)
     routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=3000 + rank)).to(dev)
     res = {"x": x.cpu(), "routing": routing.cpu()}
-    for mode in ("nccl", "p2p", "overlap", "fused"):
+    for mode in ("nccl", "p2p", "fused"):
         layer = ep.ExpertParallelRaggedDot(E, k, n, dev, seed=2000 + rank, dispatch=mode)
-        for step in range(3):  # several steps: the later ones reuse the receive buffer (and flags)
+        for step in range(3):  # several steps: the later ones reuse the buffers (and flags)
             out = layer.forward(x, routing)
+            # cotangent: a function of (rank, row) only, so that every mode's dy is reproducible
+            dy = workloads.normal_tensor(tuple(out[0].shape), 1.0, 7000 + rank, dev)
+            dx, dW = layer.backward(dy)
         torch.cuda.synchronize()
         if mode == "nccl":
             y, plan = out
             res["nccl"] = {"y": y.cpu(), "seg": plan.segment_sizes.cpu()}
-        elif mode in ("overlap", "fused"):
-            from gpu_ragged_dot_b200 import ops
+        elif mode == "fused":
             y, seg, dest_pos, totals = out
             res[mode] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu(),
-                              "status": ops.device_status(layer._ov["ws"]),
-                              "flags": layer._ov["flags"][:world].cpu()}
+                         "flags": layer._ring["flags"][:world].cpu()}
         else:
             y, seg, dest_pos, totals = out
             res["p2p"] = {"y": y[: int(totals.cpu())].cpu(), "seg": seg.cpu(), "pos": dest_pos.cpu()}
+        res[mode].update(status=layer.device_status(), dx=dx.cpu(), dW=dW.cpu(), dy=dy[: res[mode]["y"].shape[0]].cpu())
         res["weights"] = layer.weights.cpu()
         del layer
     # Host-resident tokens: forward_host (copy-in of step i+1 under step i, copy-out on a third
@@ -65,9 +69,11 @@ def _worker(rank, world, port, out_dir):
             total = out[0].shape[0] if mode == "nccl" else int(out[3].cpu())
             want = out[0][:total].float().cpu()
             hy = torch.zeros((out[0].shape[0], n), dtype=torch.bfloat16).pin_memory()
-            rows = layer.forward_host(xs.cpu().pin_memory(), hr, hy)
+            hrows = torch.zeros(1, dtype=torch.int32).pin_memory()
+            rows = layer.forward_host(xs.cpu().pin_memory(), hr, hy, rows_host=hrows)
             layer.wait_host_outputs()
             torch.cuda.synchronize()
+            ok = ok and int(hrows[0]) == total  # the number of defined rows travels with the result
             got = hy[:total].float()
             if mode == "nccl":  # rows arrive in a fixed order
                 ok = ok and rows >= total and torch.equal(got, want)
@@ -81,15 +87,17 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_multi_gpu(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
 
-    world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     res = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     E, top_k = 16, 4
     local = E // world
+    k = res[0]["x"].shape[1]
     for d in range(world):
         assert res[d]["host_ok"] == {"nccl": True, "fused": True}
         w = res[d]["weights"].float()
@@ -99,6 +107,8 @@ def test_expert_parallel_two_gpus(tmp_path):
             seg_ref += [int((flat == d * local + j).sum()) for j in range(local)]
         assert res[d]["nccl"]["seg"].tolist() == seg_ref
         assert res[d]["p2p"]["seg"].tolist() == seg_ref
+        for mode in ("nccl", "p2p", "fused"):
+            assert res[d][mode]["status"] == 0, f"{mode}: a bounded wait expired on the device"
         # NCCL path: rows arrive (source, expert, token order)
         off = 0
         for s in range(world):
@@ -109,30 +119,77 @@ def test_expert_parallel_two_gpus(tmp_path):
                 want = (rows @ w[j]).to(torch.bfloat16).float()
                 got = res[d]["nccl"]["y"][off:off + len(idx)].float()
                 assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
-                # peer-store path: same rows at the recorded positions
-                pos = res[s]["p2p"]["pos"].reshape(-1)[idx].long()
-                got = res[d]["p2p"]["y"][pos].float()
-                assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
-                assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
+                if len(idx):
+                    # peer-store path: same rows at the recorded positions
+                    pos = res[s]["p2p"]["pos"].reshape(-1)[idx].long()
+                    got = res[d]["p2p"]["y"][pos].float()
+                    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+                    assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
                 off += len(idx)
-        for mode in ("overlap", "fused"):
-            # overlapped modes: receive buffer ordered by position q = (d - source) mod W
-            ov = res[d][mode]
-            assert ov["status"] == 0, "a bounded wait expired on the device"
-            assert ov["flags"].tolist() == [3] * world  # third step's epoch on every position
-            off = 0
-            seg_ring = []
-            for q in range(world):
-                s = (d - q) % world
+        # fused mode: receive buffer ordered by position q = (d - source) mod W
+        ov = res[d]["fused"]
+        assert ov["flags"].tolist() == [3] * world  # third step's epoch on every position
+        off = 0
+        seg_ring = []
+        for q in range(world):
+            s = (d - q) % world
+            flat = res[s]["routing"].reshape(-1)
+            for j in range(local):
+                idx = (flat == d * local + j).nonzero().flatten()
+                seg_ring.append(len(idx))
+                if len(idx):
+                    rows = res[s]["x"][idx // top_k].float()
+                    want = (rows @ w[j]).to(torch.bfloat16).float()
+                    pos = res[s]["fused"]["pos"].reshape(-1)[idx].long()
+                    assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
+                    assert torch.allclose(ov["y"][pos].float(), want, rtol=2e-2, atol=2e-2)
+                off += len(idx)
+        assert ov["seg"].tolist() == seg_ring
+
+    # backward: dW of owner d sums x_row^T dy_row over every row it received; dx of source s sums,
+    # over a token's top_k copies, the owners' dy_row @ W^T (each rounded to bf16 by its owner)
+    for mode in ("nccl", "p2p", "fused"):
+        for d in range(world):
+            w = res[d]["weights"].float()
+            want_dW = torch.zeros_like(w)
+            for s in range(world):
                 flat = res[s]["routing"].reshape(-1)
+                pos_s = _positions(res, s, d, mode, world, local, top_k)
                 for j in range(local):
                     idx = (flat == d * local + j).nonzero().flatten()
-                    seg_ring.append(len(idx))
                     if len(idx):
-                        rows = res[s]["x"][idx // top_k].float()
-                        want = (rows @ w[j]).to(torch.bfloat16).float()
-                        pos = res[s][mode]["pos"].reshape(-1)[idx].long()
-                        assert int(pos.min()) >= off and int(pos.max()) < off + len(idx)
-                        assert torch.allclose(ov["y"][pos].float(), want, rtol=2e-2, atol=2e-2)
-                    off += len(idx)
-            assert ov["seg"].tolist() == seg_ring
+                        want_dW[j] += res[s]["x"][idx // top_k].float().T @ res[d][mode]["dy"][pos_s[idx]].float()
+            got = res[d][mode]["dW"].float()
+            assert torch.allclose(got, want_dW.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2), f"dW {mode} rank {d}"
+        for s in range(world):
+            flat = res[s]["routing"].reshape(-1)
+            want_dx = torch.zeros((res[s]["x"].shape[0], k))
+            for d in range(world):
+                w = res[d]["weights"].float()
+                pos_s = _positions(res, s, d, mode, world, local, top_k)
+                for j in range(local):
+                    idx = (flat == d * local + j).nonzero().flatten()
+                    if len(idx):
+                        rows = (res[d][mode]["dy"][pos_s[idx]].float() @ w[j].T).to(torch.bfloat16).float()
+                        want_dx.index_add_(0, idx // top_k, rows)
+            got = res[s][mode]["dx"].float()
+            assert torch.allclose(got, want_dx.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2), f"dx {mode} rank {s}"
+
+
+def _positions(res, s, d, mode, world, local, top_k):
+    """Row position, in owner d's buffer, of every routed copy (entry) of source rank s; entries
+    not routed to d hold 0.  p2p / fused record positions; the NCCL path keeps (source, expert,
+    token) order."""
+    flat = res[s]["routing"].reshape(-1)
+    if mode != "nccl":
+        return res[s][mode]["pos"].reshape(-1).long().clamp(min=0)
+    pos = torch.zeros(flat.numel(), dtype=torch.long)
+    off = 0
+    for s2 in range(world):
+        flat2 = res[s2]["routing"].reshape(-1)
+        for j in range(local):
+            idx = (flat2 == d * local + j).nonzero().flatten()
+            if s2 == s:
+                pos[idx] = off + torch.arange(len(idx))
+            off += len(idx)
+    return pos

@@ -299,52 +299,59 @@ def test_interpret_and_dtype_arguments_raise():
         rd.gmm(x.cpu(), A, gs)
 
 
-# ------------------------------------------------------------------ full-size properties
-def test_mixtral_shape_properties():
-    """At the benchmark size the oracle is too slow for a full comparison: check a sample of
-    rows against it, linearity in x, and the zero tail."""
+# ------------------------------------------------------------------ full-size parity
+def _assert_close_blocks(got, want, what, rows_per_block=4096):
+    """Elementwise tolerance over whole tensors, a block of rows at a time (bounded host memory)."""
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    for lo in range(0, got.shape[0], rows_per_block):
+        _assert_close(got[lo:lo + rows_per_block].cpu(), want[lo:lo + rows_per_block], f"{what} rows {lo}..")
+
+
+def test_mixtral_shape_full_parity():
+    """The benchmark size, forward: EVERY element of y against the oracle (its 16-bit CPU matmul
+    mode, which test_native_16bit_mode_agrees holds to the fp32 mode), plus exact linearity under
+    scaling by a power of two and the zero tail."""
     s = workloads.MIXTRAL
     gs_np = workloads.group_sizes_mixtral_ragged(0)
     gs_np[-1] -= 200  # leave a tail of unowned rows
     x, A, _ = workloads.make_inputs(s, DEV, seed=0, with_dout=False)
     gs = torch.from_numpy(gs_np).to(DEV)
-    y = ops.gmm_forward(x, A, gs)
+    ws = ops._workspace(s.m, s.g, DEV)
+    y = ops.gmm_forward(x, A, gs, workspace=ws)
+    assert ops.device_status(ws) == 0
     y2 = ops.gmm_forward(x * 2, A, gs)
     torch.cuda.synchronize()
     total = int(gs_np.sum())
     assert float(y[total:].float().abs().max()) == 0.0
-    # exact linearity under scaling by a power of two
     assert torch.equal((y.float() * 2).to(torch.bfloat16), y2)
-    # sampled rows against the oracle
-    rng = np.random.default_rng(0)
-    rows = np.sort(rng.choice(total, size=64, replace=False))
-    offs = np.concatenate([[0], np.cumsum(gs_np)])
-    for r in rows:
-        gi = int(np.searchsorted(offs, r, side="right") - 1)
-        want = (x[r].float().cpu() @ A[gi].float().cpu()).to(torch.bfloat16)
-        _assert_close(y[r].cpu(), want, f"mixtral row {r}")
+    want = oracle.ragged_dot(x, A, gs_np, native_16bit=True)
+    _assert_close_blocks(y, want, "mixtral y")
+    err = oracle.rel_l2_err(y.cpu(), want, axis=-1, mask=torch.arange(s.m) < total)
+    assert float(err.max()) < EPS_ROWS_BF16
 
 
-def test_mixtral_shape_backward_properties():
-    """dlhs and drhs at the benchmark size, ragged group sizes: sampled rows of dlhs and sampled
-    rows of every drhs block against the oracle; drhs is additive over a split of the rows."""
+def test_mixtral_shape_backward_full_parity():
+    """dlhs and drhs at the benchmark size with ragged group sizes: every element of both against
+    the oracle (so every k tile and column tile of every group, whatever order the kernel takes
+    them in), and drhs additive over a split of the rows."""
     s = workloads.MIXTRAL
     gs_np = workloads.group_sizes_mixtral_ragged(0)
     x, A, dout = workloads.make_inputs(s, DEV, seed=0)
     gs = torch.from_numpy(gs_np).to(DEV)
-    dx = ops.gmm_forward(dout, A, gs, trans_rhs=True)
-    dA = ops.tgmm_forward(x, dout, gs)
-    offs = np.concatenate([[0], np.cumsum(gs_np)])
-    rng = np.random.default_rng(1)
-    for r in np.sort(rng.choice(s.m, size=32, replace=False)):
-        gi = int(np.searchsorted(offs, r, side="right") - 1)
-        want = (dout[r].float().cpu() @ A[gi].float().cpu().T).to(torch.bfloat16)
-        _assert_close(dx[r].cpu(), want, f"dlhs row {r}")
+    ws = ops._workspace(s.m, s.g, DEV)
+    dx = ops.gmm_forward(dout, A, gs, trans_rhs=True, workspace=ws)
+    assert ops.device_status(ws) == 0
+    want_dx = oracle.ragged_dot(dout, A, gs_np, trans_rhs=True, native_16bit=True)
+    _assert_close_blocks(dx, want_dx, "mixtral dlhs")
+    assert float(oracle.rel_l2_err(dx.cpu(), want_dx, axis=-1).max()) < EPS_ROWS_BF16
+    del dx, want_dx, A
+    dA = ops.tgmm_forward(x, dout, gs, workspace=ws)
+    assert ops.device_status(ws) == 0
+    want_dA = oracle.trans_ragged_dot(x, dout, gs_np, native_16bit=True)
     for gi in range(s.g):
-        lo, hi = int(offs[gi]), int(offs[gi + 1])
-        for kr in rng.choice(s.k, size=4, replace=False):
-            want = (x[lo:hi, kr].float().cpu() @ dout[lo:hi].float().cpu()).to(torch.bfloat16)
-            _assert_close(dA[gi, kr].cpu(), want, f"drhs block {gi} row {kr}")
+        _assert_close_blocks(dA[gi], want_dA[gi], f"mixtral drhs block {gi}")
+        assert float(oracle.rel_l2_err(dA[gi].cpu(), want_dA[gi], axis=(-1, -2))) < EPS_GROUPS_BF16
+    del want_dA
     # rows of group gi split in two halves as two groups: the two blocks add up to the one block
     # (fp32 sums rounded once vs twice: within two bf16 ulps of the larger magnitude)
     gs2 = np.zeros(2 * s.g, dtype=np.int32)
@@ -355,12 +362,14 @@ def test_mixtral_shape_backward_properties():
     err = (summed - dA.float()).abs()
     tol = 2.0 ** -6 * torch.maximum(dA2[0::2].float().abs(), dA2[1::2].float().abs()) + 1e-3
     assert bool((err <= tol).all()), f"drhs not additive over a row split: worst {float((err / tol).max()):.2f}x"
+    del dA2, summed, err, tol
 
 
-def test_deepseek_shape_properties():
+def test_deepseek_shape_full_parity():
     """The largest configuration (m 32768, k 7168, n 2048, 256 experts, heavy-tailed sizes with
-    empty experts; 7.5 GB of weights and as much of drhs): sampled rows / blocks against the
-    oracle, zero blocks for empty experts, zero tail, and the device status word."""
+    empty experts; 7.5 GB of weights and as much of drhs): every element of y and of dlhs against
+    the oracle; for drhs every element of the blocks of the three largest, the three smallest
+    non-empty and ALL empty experts (zeros), the zero tail, and the device status word."""
     s = workloads.DEEPSEEK_V3
     gs_np = workloads.group_sizes_deepseek(0)
     gs_np[int(np.argmax(gs_np))] -= 100  # leave a tail of unowned rows
@@ -371,32 +380,27 @@ def test_deepseek_shape_properties():
     assert ops.device_status(ws) == 0
     total = int(gs_np.sum())
     assert float(y[total:].float().abs().max()) == 0.0
-    offs = np.concatenate([[0], np.cumsum(gs_np)])
-    rng = np.random.default_rng(2)
-    rows = np.sort(rng.choice(total, size=48, replace=False))
-    for r in rows:
-        gi = int(np.searchsorted(offs, r, side="right") - 1)
-        want = (x[r].float().cpu() @ A[gi].float().cpu()).to(torch.bfloat16)
-        _assert_close(y[r].cpu(), want, f"deepseek fwd row {r}")
+    _assert_close_blocks(y, oracle.ragged_dot(x, A, gs_np, native_16bit=True), "deepseek y")
+    del y
     dx = ops.gmm_forward(dout, A, gs, trans_rhs=True, workspace=ws)
-    for r in rows[:16]:
-        gi = int(np.searchsorted(offs, r, side="right") - 1)
-        want = (dout[r].float().cpu() @ A[gi].float().cpu().T).to(torch.bfloat16)
-        _assert_close(dx[r].cpu(), want, f"deepseek dlhs row {r}")
-    del y, dx, A
+    assert ops.device_status(ws) == 0
+    _assert_close_blocks(dx, oracle.ragged_dot(dout, A, gs_np, trans_rhs=True, native_16bit=True), "deepseek dlhs")
+    del dx, A
     torch.cuda.empty_cache()
     dA = ops.tgmm_forward(x, dout, gs, workspace=ws)
     assert ops.device_status(ws) == 0
+    offs = np.concatenate([[0], np.cumsum(gs_np)])
     empty = np.nonzero(gs_np == 0)[0]
     assert len(empty) > 0
-    for gi in empty[:8]:
+    for gi in empty:
         assert float(dA[int(gi)].float().abs().max()) == 0.0
-    big = np.argsort(gs_np)[-3:]
-    for gi in list(big) + list(np.nonzero(gs_np == gs_np[gs_np > 0].min())[0][:2]):
+    order = np.argsort(gs_np, kind="stable")
+    nonempty = [int(i) for i in order if gs_np[i] > 0]
+    xc, dc = x.cpu(), dout.cpu()
+    for gi in nonempty[:3] + nonempty[-3:]:
         lo, hi = int(offs[gi]), int(offs[gi + 1])
-        for kr in rng.choice(s.k, size=3, replace=False):
-            want = (x[lo:hi, kr].float().cpu() @ dout[lo:hi].float().cpu()).to(torch.bfloat16)
-            _assert_close(dA[int(gi), kr].cpu(), want, f"deepseek drhs block {gi} row {kr}")
+        want = (xc[lo:hi].T @ dc[lo:hi])
+        _assert_close_blocks(dA[gi], want, f"deepseek drhs block {gi} ({hi - lo} rows)")
 
 
 # ------------------------------------------------------------------ against the reference's own outputs
@@ -414,14 +418,16 @@ def test_cuda_matches_reference_golden(case):
     At = A.transpose(1, 2).contiguous()
     pairs = [
         ("y", ops.gmm_forward(x, A, gd), case["y"]),
-        ("y_trans_rhs", ops.gmm_forward(x, At, gd, trans_rhs=True), case["y_trans_rhs"]),
-        ("tgmm", ops.tgmm_forward(x, dout, gd), case["tgmm"]),
+        ("y_trans_rhs", ops.gmm_forward(x, At, gd, trans_rhs=True), case.get("y_trans_rhs")),
+        ("tgmm", ops.tgmm_forward(x, dout, gd), case.get("tgmm")),
         ("dlhs", ops.gmm_forward(dout, A, gd, trans_rhs=True), case["dlhs"]),
         ("drhs", ops.tgmm_forward(x, dout, gd), case["drhs"]),
-        ("dlhs_trans_rhs", ops.gmm_forward(dout, At, gd, trans_rhs=False), case["dlhs_trans_rhs"]),
-        ("drhs_trans_rhs", ops.tgmm_forward(dout, x, gd), case["drhs_trans_rhs"]),
+        ("dlhs_trans_rhs", ops.gmm_forward(dout, At, gd, trans_rhs=False), case.get("dlhs_trans_rhs")),
+        ("drhs_trans_rhs", ops.tgmm_forward(dout, x, gd), case.get("drhs_trans_rhs")),
     ]
     for name, got, want in pairs:
+        if want is None:
+            continue
         assert bool(torch.isfinite(want.float()).all())
         _assert_close(got.cpu(), want, f"{case['name']}:{name}")
 
@@ -550,9 +556,9 @@ def test_ep_plan_and_dispatch_emulated_ranks(world):
 
 @pytest.mark.parametrize("world", [1, 2, 4])
 def test_ep_ring_phases_emulated_ranks(world):
-    """The overlapped exchange with W ranks emulated on one GPU, everything on one stream so that
-    no kernel ever waits for a later one: all ranks' phase kernels run first (each raises its flag
-    on the destination), then every rank's flag-gated GEMM finds its flags up.  Checks the ring
+    """The ring-phased exchange with W ranks emulated on one GPU, everything on one stream so that
+    no kernel ever waits for a later one: all ranks' send lists are copied first, phase by phase
+    (each raises its flag on the destination), then every rank's flag-gated GEMM finds its flags up.  Checks the ring
     layout (position q = (dest - source) mod W), the flags, and the GEMM against the oracle; two
     epochs in a row."""
     E, k, n, T, top_k = 16, 128, 72, 200, 4
@@ -582,10 +588,13 @@ def test_ep_ring_phases_emulated_ranks(world):
             assert np.array_equal(plan["dest_offset"].cpu().numpy(), off_ref)
             assert int(plan["totals"].cpu()) == int(cnt[:, r * local:(r + 1) * local].sum())
             dest_pos = torch.full((T * top_k,), -7, dtype=torch.int32, device=DEV)
+            send_index = torch.full((T * top_k,), -7, dtype=torch.int32, device=DEV)
+            ops.ep_assign(routings[r].to(torch.int32).contiguous(), E, world, r, plan, capacity, dest_pos,
+                          send_index)
             for p in range(world):
                 d = (r + p) % world
-                ops.ep_dispatch_phase(xs[r], routings[r], E, world, r, p, plan, bufs[d].data_ptr(), capacity,
-                                      dest_pos, flags[d].data_ptr() + 4 * p, epoch)
+                ops.ep_send_list(xs[r], top_k, send_index, plan, p, world, dest_pos, bufs[d].data_ptr(),
+                                 capacity, flags[d].data_ptr() + 4 * p, epoch)
             plans.append(plan)
             poss.append(dest_pos)
         for d in range(world):
@@ -635,7 +644,7 @@ def test_ep_assign_send_lists_and_fused_single_rank():
     ya, plan = a.forward(x, routing)
     for step in range(2):
         yb, seg, dest_pos, totals = b.forward(x, routing)
-    assert ops.device_status(b._ov["ws"]) == 0
+    assert ops.device_status(b._ring["ws"]) == 0
     assert int(totals.cpu()) == T * top_k and seg.cpu().tolist() == plan.segment_sizes.cpu().tolist()
     order = torch.sort(routing.reshape(-1).cpu().long(), stable=True).indices
     pos = dest_pos.reshape(-1).cpu().long()
@@ -789,3 +798,234 @@ def test_ragged_dot_general_matches_oracle():
     got = rd.ragged_dot_general(x.to(DEV), y.to(DEV), gs.to(DEV), DN((([0], [0]), ([], [])), [0], []))
     ok, worst = oracle.allclose_report(got.cpu(), oracle.trans_ragged_dot(x, y, gs), 2e-2, 2e-2)
     assert ok, worst
+
+
+# ------------------------------------------------------------------ strided tgmm, overshooting sizes, expiry
+@pytest.mark.parametrize("n,tile_m", [(264, 128), (264, 256), (72, 0), (136, 0)])
+def test_tgmm_strided_matches_oracle(n, tile_m):
+    """rd_tgmm_strided: block i sums the groups i, i + g, i + 2g, ... (segments with ragged ends,
+    empty segments, one block whose segments are all empty)."""
+    m, k, g, seg = 1100, 256, 4, 3
+    x, _, dout = _inputs(61, m, k, n, 1)
+    sizes = [130, 0, 64, 77,   0, 0, 200, 1,   63, 0, 129, 300]  # segment-major: [q][i]
+    assert sum(sizes) <= m and all(sizes[q * g + 1] == 0 for q in range(seg))
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    want = torch.zeros((g, k, n), dtype=torch.float32)
+    for q in range(seg):
+        for i in range(g):
+            lo, hi = int(offs[q * g + i]), int(offs[q * g + i + 1])
+            want[i] += x[lo:hi].float().T @ dout[lo:hi].float()
+    cfg = _lib.TileCfg(256 if tile_m else 0, 0, 1, tile_m, 0) if tile_m else None
+    ws = ops._workspace(m, len(sizes), DEV)
+    got = ops.tgmm_forward(x.to(DEV), dout.to(DEV), torch.tensor(sizes, dtype=torch.int32, device=DEV),
+                           cfg=cfg, workspace=ws, seg_count=seg)
+    assert ops.device_status(ws) == 0
+    _assert_close(got.cpu(), want.to(torch.bfloat16), "tgmm strided")
+    assert float(got[1].float().abs().max()) == 0.0
+    e = oracle.rel_l2_err(got.cpu(), want, axis=(-1, -2), mask=torch.tensor([True, False, True, True]))
+    assert float(e.max()) < EPS_GROUPS_BF16
+    # one segment per block is plain tgmm
+    plain = ops.tgmm_forward(x.to(DEV), dout.to(DEV), torch.tensor(sizes[:g], dtype=torch.int32, device=DEV))
+    one = ops.tgmm_forward(x.to(DEV), dout.to(DEV), torch.tensor(sizes[:g], dtype=torch.int32, device=DEV),
+                           seg_count=1, cfg=cfg)
+    assert torch.equal(plain.view(torch.int16), one.view(torch.int16))
+
+
+@pytest.mark.parametrize("sizes,m,n", [([1000], 256, 1024), ([100, 300, 50], 256, 520), ([0, 5000, 7], 700, 264)])
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_group_sizes_overshooting_m(sizes, m, n, tile_m):
+    """sum(group_sizes) > m: every row below m belongs to the group whose range covers it and
+    must be written for all n columns (a group is clamped to the rows that exist)."""
+    k, g = 128, len(sizes)
+    x, A, dout = _inputs(71, m, k, n, g)
+    gs = torch.tensor(sizes, dtype=torch.int32)
+    cfg = _lib.TileCfg(256, 0, 1, tile_m, 0)
+    y = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ws = ops._workspace(m, g, DEV)
+    ops.gmm_forward(x.to(DEV), A.to(DEV), gs.to(DEV), cfg=cfg, out=y, workspace=ws)
+    assert ops.device_status(ws) == 0
+    assert bool(torch.isfinite(y.float()).all()), "rows below m left unwritten"
+    _assert_close(y.cpu(), oracle.ragged_dot(x, A, gs), "gmm, sizes overshooting m")
+    dA = ops.tgmm_forward(x.to(DEV), dout.to(DEV), gs.to(DEV), cfg=cfg)
+    _assert_close(dA.cpu(), oracle.trans_ragged_dot(x, dout, gs), "tgmm, sizes overshooting m")
+
+
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_bounded_wait_expiry_is_reported_and_recoverable(tile_m, monkeypatch):
+    """A wait that can never be satisfied (ready flags that nothing raises) must end by itself: the
+    kernel gives up after rd_tile_cfg.wait_limit_ms, returns, and the status word says so; the
+    next ordinary call on the same workspace is correct.  Nothing traps, faults or hangs."""
+    import time
+
+    m, k, n, g = 700, 128, 512, 4
+    x, A, _ = _inputs(81, m, k, n, 2)
+    gs = torch.tensor([300, 0, 250, 150], dtype=torch.int32)
+    g2w = torch.tensor([0, 1, 0, 1], dtype=torch.int32, device=DEV)
+    flags = torch.zeros(4, dtype=torch.int32, device=DEV)
+    cfg = _lib.TileCfg(256, 0, 1, tile_m, 0, 5)  # five milliseconds
+    ws = ops._workspace(m, g, DEV)
+    xd, Ad, gd = _to_dev(x, A, gs)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ops.gmm_forward(xd, Ad, gd, group_to_weight=g2w, cfg=cfg, workspace=ws, ready=(flags, 1, 1))
+    status = ops.device_status(ws)  # synchronises
+    waited = time.perf_counter() - t0
+    assert status == _lib.RD_ERR_DEVICE_WAIT
+    assert waited < 1.0, f"the kernel took {waited:.2f} s to give up on a 5 ms limit"
+    # the same call raises when the caller asks for the check
+    monkeypatch.setenv("RD_CHECK_STATUS", "1")
+    with pytest.raises(_lib.RaggedDotError) as ei:
+        ops.gmm_forward(xd, Ad, gd, group_to_weight=g2w, cfg=cfg, workspace=ws, ready=(flags, 1, 1))
+    assert ei.value.code == _lib.RD_ERR_DEVICE_WAIT
+    monkeypatch.delenv("RD_CHECK_STATUS")
+    # once the flags are up the same kernel runs through, and so does a plain call
+    flags.fill_(1)
+    y = ops.gmm_forward(xd, Ad, gd, group_to_weight=g2w, cfg=cfg, workspace=ws, ready=(flags, 1, 1))
+    assert ops.device_status(ws) == 0
+    _assert_close(y.cpu(), oracle.ragged_dot(x, A[g2w.cpu().long()], gs), "flag-gated gmm after an expiry")
+    y2 = ops.gmm_forward(xd, Ad[:1].expand(4, -1, -1).contiguous(), gd, workspace=ws)
+    assert ops.device_status(ws) == 0
+    _assert_close(y2.cpu(), oracle.ragged_dot(x, A[:1].expand(4, -1, -1), gs), "plain gmm after an expiry")
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_ep_combine_pull_emulated_ranks(world):
+    """rd_ep_combine_pull with the W owners' gradient buffers all on this GPU: each token's row is
+    the fp32 sum of its top_k rows at the recorded positions, rounded once."""
+    E, k, T, top_k = 16, 264, 300, 4
+    local = E // world
+    capacity = T * top_k * world
+    bufs = [oracle.reference_normal(90 + d, (capacity, k), torch.bfloat16).to(DEV) for d in range(world)]
+    base = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=5)).to(DEV).to(torch.int32)
+    pos = torch.from_numpy(np.random.default_rng(3).integers(0, capacity, size=(T, top_k)).astype(np.int32)).to(DEV)
+    pos[7, 2] = -1          # a dropped row adds nothing
+    routing[9, 0] = E + 3   # an expert that does not exist adds nothing
+    got = ops.ep_combine_pull(routing, pos, E, world, base, capacity, k, torch.bfloat16)
+    want = torch.zeros((T, k), dtype=torch.float32)
+    r_cpu, p_cpu = routing.cpu(), pos.cpu()
+    for t in range(T):
+        for s_ in range(top_k):
+            e, q = int(r_cpu[t, s_]), int(p_cpu[t, s_])
+            if 0 <= e < E and q >= 0:
+                want[t] += bufs[e // local][q].float().cpu()
+    assert torch.equal(got.cpu().view(torch.int16), want.to(torch.bfloat16).view(torch.int16))
+
+
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "fused"])
+def test_expert_parallel_backward_single_rank(mode):
+    """ExpertParallelRaggedDot.backward on one rank against the oracle's VJP of the same routed
+    product: dx[t] = sum over the token's experts of dy_row @ W[e]^T, dW[e] = x_e^T dy_e."""
+    from gpu_ragged_dot_b200 import ep
+
+    E, k, n, T, top_k = 8, 256, 264, 200, 2
+    layer = ep.ExpertParallelRaggedDot(E, k, n, torch.device(DEV), seed=5, dispatch=mode)
+    x = workloads.normal_tensor((T, k), 1.0, 77, DEV)
+    routing = torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=9)).to(DEV)
+    for step in range(2):
+        out = layer.forward(x, routing)
+        y = out[0]
+        dy = workloads.normal_tensor(tuple(y.shape), 1.0, 500 + step, DEV)
+        dx, dW = layer.backward(dy)
+    torch.cuda.synchronize()
+    assert layer.device_status() == 0
+    flat = routing.reshape(-1).cpu().long()
+    if mode == "nccl":
+        order = torch.sort(flat, stable=True).indices
+        pos = torch.empty_like(order)
+        pos[order] = torch.arange(order.numel())
+    else:
+        pos = out[2].reshape(-1).cpu().long()
+    W = layer.weights.float().cpu()
+    dyc, xc = dy.float().cpu(), x.float().cpu()
+    want_dx = torch.zeros((T, k))
+    want_dW = torch.zeros((E, k, n))
+    for i in range(T * top_k):
+        e, t = int(flat[i]), i // top_k
+        row = (dyc[pos[i]] @ W[e].T).to(torch.bfloat16).float()  # the owner rounds each gradient row
+        want_dx[t] += row
+        want_dW[e] += torch.outer(xc[t], dyc[pos[i]])
+    _assert_close(dx.cpu(), want_dx.to(torch.bfloat16), f"ep backward dx ({mode})")
+    _assert_close(dW.cpu(), want_dW.to(torch.bfloat16), f"ep backward dW ({mode})")
+
+
+# ------------------------------------------------------------------ compute_dtype and float32 precision
+def test_compute_dtype_casts_like_the_reference():
+    """compute_dtype != input dtype: both operands are cast before the product, the result comes
+    back in x's type (gpu_ragged_dot.py:116,145,149), in the forward and in both gradients."""
+    m, k, n, g = 300, 136, 72, 4
+    x, A, dout = _inputs(91, m, k, n, g)
+    gs = torch.tensor([100, 0, 150, 40], dtype=torch.int32)
+    xd, Ad, gd, dd = _to_dev(x, A, gs, dout)
+    # bf16 inputs multiplied as float32 (TF32 holds every bf16 value exactly): same product
+    xd.requires_grad_(True)
+    Ad.requires_grad_(True)
+    y = rd.gmm(xd, Ad, gd, compute_dtype=torch.float32)
+    assert y.dtype == torch.bfloat16
+    y.backward(dd)
+    dx_ref, dA_ref = oracle.ragged_dot_vjp(x, A, gs, dout)
+    _assert_close(y.detach().cpu(), oracle.ragged_dot(x, A, gs), "bf16 in, f32 compute: y")
+    _assert_close(xd.grad.cpu(), dx_ref, "bf16 in, f32 compute: dx")
+    _assert_close(Ad.grad.cpu(), dA_ref, "bf16 in, f32 compute: dA")
+    assert xd.grad.dtype == torch.bfloat16 and Ad.grad.dtype == torch.bfloat16
+    # float32 inputs multiplied as bf16: the oracle on the rounded operands, float32 out
+    x32 = oracle.reference_normal(5, (m, k), torch.float32)
+    A32 = oracle.reference_normal(6, (g, k, n), torch.float32)
+    y = rd.gmm(x32.to(DEV), A32.to(DEV), gd, compute_dtype=torch.bfloat16)
+    assert y.dtype == torch.float32
+    want = oracle.ragged_dot(x32.to(torch.bfloat16), A32.to(torch.bfloat16), gs).float()
+    _assert_close(y.cpu(), want, "f32 in, bf16 compute")
+    # operands of different types: A is cast to x's type
+    y = rd.gmm(xd.detach(), A32.to(DEV), gd)
+    _assert_close(y.cpu(), oracle.ragged_dot(x, A32.to(torch.bfloat16), gs), "bf16 x, f32 A")
+    out = rd.tgmm(x32.to(DEV), dd, gd, compute_dtype=torch.bfloat16)
+    assert out.dtype == torch.float32
+    _assert_close(out.cpu(), oracle.trans_ragged_dot(x32.to(torch.bfloat16), dout, gs).float(), "tgmm f32 in, bf16 compute")
+
+
+def test_float32_highest_precision_three_tf32_passes():
+    """precision="highest": float32 results within 2e-5 relative L2 of the exact product (float64
+    on the CPU), twenty times tighter than the reference's float32 gate of 5e-4 (tests.py:127),
+    where one TF32 pass sits at about 5e-4; forward, trans_rhs, tgmm and the VJP."""
+    m, k, n, g = 500, 264, 136, 5
+    gs = torch.tensor([120, 0, 200, 77, 90], dtype=torch.int32)
+    x = oracle.reference_normal(1, (m, k), torch.float32)
+    A = oracle.reference_normal(2, (g, k, n), torch.float32)
+    dout = oracle.reference_normal(3, (m, n), torch.float32)
+    total = int(gs.sum())
+
+    def oracle64(a, b, trans=False):
+        y = torch.zeros((m, b.shape[-2] if trans else b.shape[-1]), dtype=torch.float64)
+        off = 0
+        for gi, s_ in enumerate(gs.tolist()):
+            w = b[gi].double()
+            y[off:off + s_] = a[off:off + s_].double() @ (w.T if trans else w)
+            off += s_
+        return y
+
+    xd, Ad, gd, dd = _to_dev(x, A, gs, dout)
+    mask = torch.arange(m) < total
+    y_hi = rd.gmm(xd, Ad, gd, precision="highest")
+    y_lo = rd.gmm(xd, Ad, gd)
+    want = oracle64(x, A)
+    e_hi = float(oracle.rel_l2_err(y_hi.cpu().double().float(), want.float(), mask=mask).max())
+    e_lo = float(oracle.rel_l2_err(y_lo.cpu(), want.float(), mask=mask).max())
+    assert e_hi < 2e-5, e_hi
+    assert e_lo > 5 * e_hi  # the single pass really is the coarser one
+    assert float(y_hi[total:].abs().max()) == 0.0
+    At = A.transpose(1, 2).contiguous()
+    y_t = rd.gmm(xd, At.to(DEV), gd, trans_rhs=True, precision="highest")
+    assert float(oracle.rel_l2_err(y_t.cpu(), want.float(), mask=mask).max()) < 2e-5
+    out = rd.tgmm(xd, dd, gd, precision="highest")
+    want_t = torch.zeros((g, k, n), dtype=torch.float64)
+    off = 0
+    for gi, s_ in enumerate(gs.tolist()):
+        want_t[gi] = x[off:off + s_].double().T @ dout[off:off + s_].double()
+        off += s_
+    assert float(oracle.rel_l2_err(out.cpu(), want_t.float(), axis=(-1, -2), mask=gs != 0).max()) < 2e-5
+    assert float(out[1].abs().max()) == 0.0
+    xg, Ag = xd.clone().requires_grad_(True), Ad.clone().requires_grad_(True)
+    rd.gmm(xg, Ag, gd, precision="highest").backward(dd)
+    want_dx = oracle64(dout, A, trans=True)
+    assert float(oracle.rel_l2_err(xg.grad.cpu(), want_dx.float(), mask=mask).max()) < 2e-5
+    assert float(oracle.rel_l2_err(Ag.grad.cpu(), want_t.float(), axis=(-1, -2), mask=gs != 0).max()) < 2e-5

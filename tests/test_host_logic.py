@@ -55,14 +55,17 @@ def test_reference_signature_is_kept():
     import inspect
 
     sig = inspect.signature(rd.gmm)
-    assert list(sig.parameters) == [
+    # the reference's thirteen parameters, in its order; anything added is keyword-only
+    assert list(sig.parameters)[:13] == [
         "x", "A", "group_sizes", "block_m", "block_k", "block_n", "trans_rhs", "interpret",
         "compute_dtype", "acc_dtype", "num_warps", "num_stages", "chunk_m"]
+    assert all(p.kind is inspect.Parameter.KEYWORD_ONLY for p in list(sig.parameters.values())[13:])
     assert sig.parameters["block_m"].default == 64 and sig.parameters["chunk_m"].default == 512
     sig = inspect.signature(rd.tgmm)
-    assert list(sig.parameters) == [
+    assert list(sig.parameters)[:12] == [
         "x", "y", "group_sizes", "block_m", "block_k", "block_n", "interpret", "compute_dtype",
         "acc_dtype", "num_warps", "num_stages", "chunk_m"]
+    assert all(p.kind is inspect.Parameter.KEYWORD_ONLY for p in list(sig.parameters.values())[12:])
     assert rd.ragged_dot is rd.gmm and rd.trans_ragged_dot is rd.tgmm
 
 
@@ -77,7 +80,13 @@ def test_cpu_tensors_are_refused():
     with pytest.raises(NotImplementedError):
         rd.gmm(x, A, gs, interpret=True)
     with pytest.raises(NotImplementedError):
-        rd.gmm(x, A, gs, compute_dtype=torch.float32)
+        rd.gmm(x, A, gs, compute_dtype=torch.float64)  # float16, bfloat16 or float32 only
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, acc_dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        rd.gmm(x, A, gs, precision="fastest")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.gmm(x, A, gs, compute_dtype=torch.float32)  # accepted, and then there is no CPU path
     assert ops._torch_dtype("float32") is torch.float32
 
 
