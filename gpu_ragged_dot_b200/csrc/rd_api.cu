@@ -140,13 +140,13 @@ int choose_tile_n(long long /*row_tiles*/, int n, int /*sms*/) {
   return 256;
 }
 
-template <int BN, bool kBKMajor, bool kTgmm, int kCtas>
+template <int BN, bool kBKMajor, bool kTgmm, int kCtas, bool kSeg = false>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
                 const GemmArgs& args, int ctas, cudaStream_t stream) {
   constexpr int kStageBytes = rd::stage_bytes<BN, kCtas>();
   constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   constexpr int kSmem = kStages * kStageBytes + rd::kOutStagingBytes + 1024;
-  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm, kCtas>;
+  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm, kCtas, kSeg>;
   // The attribute is per device; setting it again is cheap, so do it on every call rather
   // than track which devices have seen it.
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
@@ -221,15 +221,18 @@ int encode_rows_map(CUtensorMap* map, const void* base, int dtype, int cols, int
   return encode_map(map, base, dtype, 2, dims, box);
 }
 
-template <bool kBKMajor, bool kTgmm, bool kEp = false>
+template <bool kBKMajor, bool kTgmm, bool kVariant = false>
 int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
                  const GemmArgs& args, int ctas, cudaStream_t stream) {
-  if constexpr (!kTgmm && !kEp) {
+  if constexpr (!kTgmm && !kVariant) {
     // ready flags / sender CTAs live in a separate instantiation (see rd_gemm2.cuh)
     if (args.ready_flags != nullptr || args.send.world > 0)
       return launch_gemm2<kBKMajor, false, true>(ta, tb, tout, args, ctas, stream);
   }
-  auto kernel = rd::ragged_gemm2_kernel<kBKMajor, kTgmm, kEp>;
+  if constexpr (kTgmm && !kVariant) {
+    if (args.seg_count > 1) return launch_gemm2<false, true, true>(ta, tb, tout, args, ctas, stream);
+  }
+  auto kernel = rd::ragged_gemm2_kernel<kBKMajor, kTgmm, kVariant>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rd::kG2SmemBytes) !=
       cudaSuccess)
     return RD_ERR_LAUNCH;
@@ -750,6 +753,11 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
     return launch_gemm_f32<64, false, true>(ta, tb, tout, args, ctas, stream);
   }
   if (two_half) return launch_gemm2<false, true>(ta, tb, tout, args, ctas, stream);
+  if (seg_count > 1) {
+    if (bn == 256) return launch_gemm<256, false, true, 1, true>(ta, tb, tout, args, ctas, stream);
+    if (bn == 128) return launch_gemm<128, false, true, 1, true>(ta, tb, tout, args, ctas, stream);
+    return launch_gemm<64, false, true, 1, true>(ta, tb, tout, args, ctas, stream);
+  }
   if (cta_group == 2) return launch_gemm<256, false, true, 2>(ta, tb, tout, args, ctas, stream);
   if (bn == 256) return launch_gemm<256, false, true, 1>(ta, tb, tout, args, ctas, stream);
   if (bn == 128) return launch_gemm<128, false, true, 1>(ta, tb, tout, args, ctas, stream);

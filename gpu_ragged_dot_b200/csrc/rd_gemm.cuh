@@ -169,8 +169,9 @@ __device__ __forceinline__ void segment_rows(const GemmArgs& p, int group, int& 
   rows = imax(imin(imax(p.group_sizes[group], 0), p.m - row0), 0);
 }
 
+template <bool kSeg>
 __device__ __forceinline__ int tgmm_block_count(const GemmArgs& p, const TileCoord& t) {
-  if (p.seg_count <= 1) return (t.rows + kTileK - 1) / kTileK;
+  if constexpr (!kSeg) return (t.rows + kTileK - 1) / kTileK;
   int blocks = 0;
   for (int q = 0; q < p.seg_count; ++q) {
     int row0, rows;
@@ -204,6 +205,19 @@ __device__ __forceinline__ void next_block(const GemmArgs& p, const TileCoord& t
 // Does a block with `live` rows need rows cleared before its MMAs?
 __device__ __forceinline__ bool block_needs_clearing(int live) {
   return live < kTileK && (live % kUmmaK) != 0;
+}
+
+// First row and live rows of block kb of a tile.  Plain tgmm (kSeg false) computes them from the
+// group's row range, as cheaply as can be: this sits in the producer's and the MMA warp's loops.
+template <bool kSeg>
+__device__ __forceinline__ void tgmm_block(const GemmArgs& p, const TileCoord& t, RowBlocks& it, int kb,
+                                           int& row, int& live) {
+  if constexpr (kSeg) {
+    next_block(p, t, it, row, live);
+  } else {
+    row = t.row0 + kb * kTileK;
+    live = t.rows - kb * kTileK;
+  }
 }
 
 // Zero rows [live, end of the last 16-deep MMA) of every [64 rows][128 B] box of one stage and
@@ -259,7 +273,7 @@ constexpr int stage_bytes() {
 //                  kBKMajor (trans_rhs: W[g] is [n,k]) else MN-major (W[g] is [k,n]).
 // kTgmm == true  : tgmm.  A operand = x^T tile (MN-major), B operand = dout tile (MN-major);
 //                  kBKMajor must be false.
-template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas>
+template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas, bool kSeg = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b,
@@ -267,6 +281,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
   static_assert(kCtas == 1 || (kCtas == 2 && BN >= 128), "a CTA pair needs BN >= 128");
+  static_assert(!kSeg || (kTgmm && kCtas == 1), "strided segments: tgmm on one CTA per tile");
   constexpr bool kPair = kCtas == 2;
   constexpr int kBCols = BN / kCtas;  // B-operand columns this CTA loads
   constexpr uint32_t kABytes = kTileM * kTileK * 2;
@@ -349,7 +364,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
                                   : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
         const int nb = t.n0 + cta_rank * kBCols;  // first B column this CTA loads
-        const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+        const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
         RowBlocks blocks = first_block(t);
         if (!kTgmm && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
@@ -385,7 +400,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (kTgmm) {
             int r, live;
-            next_block(p, t, blocks, r, live);
+            tgmm_block<kSeg>(p, t, blocks, kb, r, live);
             load_2d(remote_bar, sa, &tmap_a, full, t.k0, r);
             load_2d(remote_bar, sa + kBoxBytes, &tmap_a, full, t.k0 + 64, r);
 #pragma unroll
@@ -432,8 +447,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
       const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
                                 : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
-      const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
-      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);  // pairs only
+      const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
+      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
       RowBlocks blocks = first_block(t);
       const uint32_t idesc = (!kTgmm && !kPair && t.rows <= 64) ? idesc_half : idesc_full;
 
@@ -481,10 +496,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int live = kTileK;
         if (kTgmm) {
           int r;
-          next_block(p, t, blocks, r, live);
+          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
         }
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && (kPair ? (tail_stage && kb == kb_count - 1) : block_needs_clearing(live))) {
+        if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
           // Rows past the end of the group belong to the next group (or to nobody): clear them,
           // up to the end of the last MMA that is issued, in every box of this stage, so they
           // add nothing to the reduction.  (In gmm the columns past k are zero-filled by TMA.)
@@ -580,7 +595,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         warp_has_rows = out_row0 < p.k;
         slab_by_tma = true;  // rows >= k are outside the map and dropped by the store
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
-        zero_only = tgmm_block_count(p, t) == 0;
+        zero_only = kSeg ? tgmm_block_count<kSeg>(p, t) == 0 : t.rows <= 0;
       } else if (!kPair && t.rows <= 64) {
         // M = 64 tile: row 16 * quarter + lane sits in lane `lane` (< 16) of this warp's quarter
         const int r64 = quarter * 16 + lane;

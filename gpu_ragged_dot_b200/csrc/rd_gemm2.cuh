@@ -77,15 +77,19 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int 
   return t;
 }
 
-// kEp: the expert-parallel variant (ready flags in the loader, sender CTAs in the grid).  It is a
-// separate instantiation because this kernel's main loop is sensitive to code generation: merely
-// routing the tile loops through `cta_index` / `gemm_ctas` variables cost the plain kernel 3-5 %.
-template <bool kBKMajor, bool kTgmm, bool kEp = false>
+// kVariant selects a second instantiation of either product, kept apart from the plain one because
+// this kernel's main loop is sensitive to code generation (merely routing the tile loops through
+// `cta_index` / `gemm_ctas` variables cost the plain kernel 3-5 %):
+//   gmm:  the expert-parallel variant (ready flags in the loader, sender CTAs in the grid);
+//   tgmm: strided segments (a block contracts over several row ranges, rd_tgmm_strided).
+template <bool kBKMajor, bool kTgmm, bool kVariant = false>
 __global__ void __launch_bounds__(kG2Threads, 1)
 ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
+  constexpr bool kEp = !kTgmm && kVariant;
+  constexpr bool kSeg = kTgmm && kVariant;
   constexpr int BN = kG2TileN;
   constexpr int kStages = kG2Stages;
   constexpr uint32_t kHalfABytes = kTileM * kTileK * 2;  // 16 KB
@@ -103,7 +107,6 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
 
-  static_assert(!(kEp && kTgmm), "the expert-parallel variant is a gmm kernel");
   // Fused expert-parallel exchange: some CTAs of the grid send rows instead of multiplying.
   // The senders are the FIRST CTAs of the grid, so they are resident before any CTA that may wait
   // for another GPU's senders.
@@ -166,7 +169,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
         const int halves = halves_of(t);
-        const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+        const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
         RowBlocks blocks = first_block(t);
         if (kEp && p.ready_flags != nullptr) {
           const int slot = t.group / p.groups_per_flag;
@@ -193,7 +196,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           mbar_arrive_expect_tx(full, halves * kHalfABytes + kG2BBytes);
           if (kTgmm) {
             int r, live;
-            next_block(p, t, blocks, r, live);
+            tgmm_block<kSeg>(p, t, blocks, kb, r, live);
             for (int h = 0; h < halves; ++h) {
               tma_load_2d_hint(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r, keep);
               tma_load_2d_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r, keep);
@@ -239,8 +242,9 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
       const int halves = halves_of(t);
-      const int kb_count = kTgmm ? tgmm_block_count(p, t) : k_blocks_gmm;
+      const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
       RowBlocks blocks = first_block(t);
+      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
 
       if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
 #pragma unroll
@@ -269,10 +273,10 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int live = kTileK;
         if (kTgmm) {
           int r;
-          next_block(p, t, blocks, r, live);
+          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
         }
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && block_needs_clearing(live)) {
+        if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
           clear_tail_rows<kG2StageBytes / kBoxBytes>(sa, live, lane);
           __syncwarp();
         }
@@ -351,7 +355,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         warp_has_rows = out_row0 < p.k;
         slab_by_tma = true;
         row_off = (static_cast<size_t>(t.group) * p.k + kr) * static_cast<size_t>(p.n);
-        zero_only = tgmm_block_count(p, t) == 0;
+        zero_only = kSeg ? tgmm_block_count<kSeg>(p, t) == 0 : t.rows <= 0;
       } else {
         out_row0 = t.row0 + slab0;
         row_ok = r_in_tile < t.rows;

@@ -136,14 +136,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (ok) return true;
   }
   const uint64_t t0 = global_timer_ns();
-  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
   for (;;) {
     for (int i = 0; i < 64; ++i) {
       bool ok = kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
       if (ok) return true;
     }
     if (ctl->abort) return false;
-    if (global_timer_ns() - t0 > limit_ns) {
+    // The limit is read here, where the clock is checked, so that nothing but t0 lives across
+    // the polling loop: these waits sit inside the pipelines' hot loops, and a limit computed
+    // ahead of the loop cost the Mixtral-shaped GEMMs 2-4 %.
+    if (global_timer_ns() - t0 > static_cast<uint64_t>(ctl->limit_us) * 1000ull) {
       ctl->abort = 1;
       return false;
     }
@@ -155,13 +157,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // that follow after the acquire.  Same expiry rule as mbar_wait.
 __device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int value, volatile WaitCtl* ctl) {
   const uint64_t t0 = global_timer_ns();
-  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
   for (;;) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v >= value) break;
     if (ctl->abort) return false;
-    if (global_timer_ns() - t0 > limit_ns) {
+    if (global_timer_ns() - t0 > static_cast<uint64_t>(ctl->limit_us) * 1000ull) {
       ctl->abort = 1;
       return false;
     }

@@ -446,8 +446,8 @@ def ep_combine_pull(routing: torch.Tensor, dest_pos: torch.Tensor, num_experts: 
     """``rd_ep_combine_pull``: out[t] = sum over the top_k slots of the gradient rows the owners
     hold at ``dest_pos``; ``peer_base`` is an int64 device tensor of `world` buffer addresses."""
     lib = _lib.load()
-    r = _as_i32(routing)
-    tokens, top_k = r.shape
+    tokens, top_k = routing.shape
+    r = _as_i32(routing.reshape(-1))
     pos = _as_i32(dest_pos.reshape(-1))
     assert pos.numel() == tokens * top_k
     assert peer_base.dtype == torch.int64 and peer_base.numel() == world and peer_base.is_cuda
