@@ -493,14 +493,16 @@ class ExpertParallelRaggedDot:
             h["out"].record(s_out)
         return rows
 
-    def backward_host(self, dy_host: torch.Tensor, rows: int, dx_host: torch.Tensor, dW_host: torch.Tensor) -> None:
-        """``backward`` for a caller whose cotangent and gradients live in pinned host memory: the
-        first ``rows`` rows of ``dy_host`` (the rows this rank received in the last forward; see
-        ``forward_host``'s ``rows_host``) are copied in on the copy-in stream, the gradients leave on
-        the copy-out stream.  Rows of the device-side cotangent past ``rows`` are not read by the
-        kernels (they lie outside every segment)."""
+    def backward_host(self, dy_host: torch.Tensor, rows: int, dx_host: torch.Tensor,
+                      dW_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``backward`` for a caller whose cotangent and token gradients live in pinned host memory:
+        the first ``rows`` rows of ``dy_host`` (the rows this rank received in the last forward; see
+        ``forward_host``'s ``rows_host``) are copied in on the copy-in stream, dx leaves on the
+        copy-out stream.  The weight gradient stays where the weights are, on the device, and is
+        returned; it is also copied to ``dW_host`` if that is given.  Rows of the device-side
+        cotangent past ``rows`` are not read by the kernels (they lie outside every segment)."""
         for name, t in (("dy_host", dy_host), ("dx_host", dx_host), ("dW_host", dW_host)):
-            if t.is_cuda or not t.is_pinned():
+            if t is not None and (t.is_cuda or not t.is_pinned()):
                 raise ValueError(f"{name} must be a pinned host tensor")
         if self._host is None or self._saved is None:
             raise RuntimeError("backward_host needs a forward_host first")
@@ -525,11 +527,13 @@ class ExpertParallelRaggedDot:
         with torch.cuda.stream(h["s_out"]):
             h["s_out"].wait_event(done)
             dx_host.copy_(dx, non_blocking=True)
-            dW_host.copy_(dW, non_blocking=True)
             dx.record_stream(h["s_out"])
-            dW.record_stream(h["s_out"])
+            if dW_host is not None:
+                dW_host.copy_(dW, non_blocking=True)
+                dW.record_stream(h["s_out"])
             h["out"] = torch.cuda.Event()
             h["out"].record(h["s_out"])
+        return dW
 
     def wait_host_outputs(self) -> None:
         """Make the current stream wait for the last ``forward_host`` / ``backward_host`` copy-out."""
