@@ -72,7 +72,7 @@ SIGNATURES = {
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
     "rd_ep_combine_pull": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                                    _c_int, _c_int, _c_void_p, _c_void_p]),
+                                    _c_int, _c_int, _c_void_p, _c_int, _c_void_p]),
     "rd_gmm_indexed": (
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]

@@ -582,7 +582,7 @@ int rd_ep_send_list(const void* x, int top_k, int row_bytes, const int32_t* send
 
 int rd_ep_combine_pull(const int32_t* routing, const int32_t* dest_pos, int tokens, int top_k,
                        int row_bytes, int num_experts, int world, const uint64_t* peer_base,
-                       int capacity_rows, int dtype, void* out, void* stream_v) {
+                       int capacity_rows, int dtype, void* out, int max_blocks, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (dtype != RD_DTYPE_F16 && dtype != RD_DTYPE_BF16) return RD_ERR_BAD_DTYPE;
   if (tokens < 0 || top_k <= 0 || top_k > 8 || row_bytes <= 0 || (row_bytes & 15) || world <= 0 ||
@@ -592,7 +592,7 @@ int rd_ep_combine_pull(const int32_t* routing, const int32_t* dest_pos, int toke
   if (!routing || !dest_pos || !peer_base || !aligned16(out)) return RD_ERR_BAD_POINTER;
   const int warps_per_block = rd::kEpThreads / 32;
   int blocks = (tokens + warps_per_block - 1) / warps_per_block;
-  const int cap = sm_count() * 8;
+  const int cap = max_blocks > 0 ? max_blocks : sm_count() * 8;
   if (blocks > cap) blocks = cap;
   const int vecs = row_bytes / 16, local = num_experts / world;
   uint4* o = static_cast<uint4*>(out);

@@ -93,7 +93,8 @@ class ExpertParallelRaggedDot:
 
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
-                 dispatch: str = "nccl", capacity_rows: Optional[int] = None, sender_ctas: int = 0):
+                 dispatch: str = "nccl", capacity_rows: Optional[int] = None, sender_ctas: int = 0,
+                 pull_sms: int = 16):
         from . import workloads
 
         assert dispatch in ("nccl", "p2p", "fused")
@@ -108,6 +109,9 @@ class ExpertParallelRaggedDot:
         # CTAs move 600 GB/s per GPU at 2 and at 8 ranks; 8 are too few (220 GB/s), 24 are slower
         # again at 8 ranks (480 GB/s) and take more SMs from the GEMM.
         self.sender_ctas = sender_ctas or 16
+        # backward: SMs the drhs product leaves free for the return exchange that runs beside it
+        # (0: the exchange runs after drhs, on all SMs)
+        self.pull_sms = pull_sms
         assert num_experts % self.world == 0
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
         self.k, self.n, self.device = k, n, device
@@ -347,7 +351,8 @@ class ExpertParallelRaggedDot:
                       "peer_base": torch.tensor(ptrs, dtype=torch.int64, device=dev),
                       "ws": ops._workspace(capacity_rows, self.num_experts, dev),
                       "ws_tgmm": ops._workspace(capacity_rows, self.num_experts, dev),
-                      "pulled": True}
+                      "side": torch.cuda.Stream(device=dev), "ev_dlhs": torch.cuda.Event(),
+                      "ev_pull": torch.cuda.Event(), "pulled": True}
 
     def backward(self, dy: torch.Tensor, timed: bool = False):
         """VJP of the last ``forward`` with the reference's wiring (gpu_ragged_dot.py:399-402) on the
@@ -398,20 +403,43 @@ class ExpertParallelRaggedDot:
             self._grad_setup(cap)
         gr = self._grad
         assert dy.shape == (cap, self.n) and dy.is_contiguous()
+        main = torch.cuda.current_stream(self.device)
+        side = gr["side"]
         if not gr["pulled"] and gr["hdl"] is not None:
             gr["hdl"].barrier(channel=1)  # two backward calls in a row: the last pull has finished everywhere
         ops.gmm_forward(dy, self.weights, sv["seg"], trans_rhs=True, group_to_weight=sv["seg2e"], cfg=cfg,
                         out=gr["buf"], workspace=gr["ws"])
         if timed:
             ev[1].record()
-        # drhs is local work: it runs while the other ranks finish their dlhs
-        dW = ops.tgmm_forward(sv["recv"], dy, sv["seg"], seg_count=W, workspace=gr["ws_tgmm"])
-        if timed:
-            ev[2].record()
-        if gr["hdl"] is not None:
-            gr["hdl"].barrier(channel=0)  # every owner's gradient rows are complete
-        dx = ops.ep_combine_pull(sv["routing"], sv["dest_pos"], self.num_experts, W, gr["peer_base"], cap,
-                                 self.k, self.dtype)
+        tokens = sv["routing"].shape[0]
+        dx = torch.empty((tokens, self.k), dtype=self.dtype, device=self.device)
+        overlap = W > 1 and self.pull_sms > 0
+        if overlap:
+            # The return exchange runs on a side stream under the drhs product, which leaves
+            # `pull_sms` SMs free for it.  Neither kernel waits for the other on the device: the
+            # barrier and the pull only need those SMs, drhs needs nothing remote.
+            gr["ev_dlhs"].record(main)
+            side.wait_event(gr["ev_dlhs"])
+            with torch.cuda.stream(side):
+                gr["hdl"].barrier(channel=0)  # every owner's gradient rows are complete
+                ops.ep_combine_pull(sv["routing"], sv["dest_pos"], self.num_experts, W, gr["peer_base"], cap,
+                                    self.k, self.dtype, out=dx, max_blocks=8 * self.pull_sms)
+                gr["ev_pull"].record(side)
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            tcfg = _lib.TileCfg(0, max(sms - self.pull_sms, 1), 0, 0, 0)
+            dW = ops.tgmm_forward(sv["recv"], dy, sv["seg"], seg_count=W, workspace=gr["ws_tgmm"], cfg=tcfg)
+            if timed:
+                ev[2].record()
+            main.wait_event(gr["ev_pull"])
+        else:
+            # drhs is local work: it runs while the other ranks finish their dlhs
+            dW = ops.tgmm_forward(sv["recv"], dy, sv["seg"], seg_count=W, workspace=gr["ws_tgmm"])
+            if timed:
+                ev[2].record()
+            if gr["hdl"] is not None:
+                gr["hdl"].barrier(channel=0)  # every owner's gradient rows are complete
+            ops.ep_combine_pull(sv["routing"], sv["dest_pos"], self.num_experts, W, gr["peer_base"], cap,
+                                self.k, self.dtype, out=dx)
         gr["pulled"] = False
         if timed:
             ev[3].record()
@@ -420,6 +448,7 @@ class ExpertParallelRaggedDot:
 
     def backward_timers_ms(self, steps: int):
         torch.cuda.synchronize(self.device)
+        # with the return exchange running under drhs, the third span is only what sticks out
         names = ("dlhs_gemm", "drhs_tgmm", "return_exchange_and_combine")
         tot = dict.fromkeys(names, 0.0)
         for e in self._bwd_events:

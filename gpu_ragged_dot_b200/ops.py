@@ -442,7 +442,7 @@ def tgmm_forward(
 
 def ep_combine_pull(routing: torch.Tensor, dest_pos: torch.Tensor, num_experts: int, world: int,
                     peer_base: torch.Tensor, capacity_rows: int, k: int, dtype: torch.dtype,
-                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, max_blocks: int = 0) -> torch.Tensor:
     """``rd_ep_combine_pull``: out[t] = sum over the top_k slots of the gradient rows the owners
     hold at ``dest_pos``; ``peer_base`` is an int64 device tensor of `world` buffer addresses."""
     lib = _lib.load()
@@ -457,7 +457,7 @@ def ep_combine_pull(routing: torch.Tensor, dest_pos: torch.Tensor, num_experts: 
     with torch.cuda.device(r.device):
         rc = lib.rd_ep_combine_pull(r.data_ptr(), pos.data_ptr(), tokens, top_k, k * out.element_size(),
                                     num_experts, world, peer_base.data_ptr(), capacity_rows,
-                                    _DTYPE_CODE[dtype], out.data_ptr(), _stream_ptr(r.device))
+                                    _DTYPE_CODE[dtype], out.data_ptr(), int(max_blocks), _stream_ptr(r.device))
     _lib.check(rc, "rd_ep_combine_pull")
     return out
 

@@ -224,11 +224,13 @@ int rd_tgmm_strided(const void* x, const void* dout, const int32_t* group_sizes,
  * of gradient rows (its rd_gmm_indexed(dout, A, trans_rhs) result over the received layout) as
  * seen from this GPU; rows are pulled with plain peer loads, summed in fp32 and written as one
  * 16-bit row per token.  Slots with an expert outside [0, num_experts) or a position outside
- * [0, capacity_rows) add nothing.  top_k <= 8.  The caller orders this call after every owner's
- * GEMM (a cross-rank barrier) and keeps the buffers unchanged until every rank has pulled. */
+ * [0, capacity_rows) add nothing.  top_k <= 8.  max_blocks caps the grid (0 = eight blocks of
+ * 256 threads per SM), for a caller that runs the pull beside another kernel on SMs it has left
+ * free.  The caller orders this call after every owner's GEMM (a cross-rank barrier) and keeps
+ * the buffers unchanged until every rank has pulled. */
 int rd_ep_combine_pull(const int32_t* routing, const int32_t* dest_pos, int tokens, int top_k,
                        int row_bytes, int num_experts, int world, const uint64_t* peer_base,
-                       int capacity_rows, int dtype, void* out, void* stream);
+                       int capacity_rows, int dtype, void* out, int max_blocks, void* stream);
 
 /* Grouped GEMMs with the row permutation of a mixture-of-experts layer fused in.  The
  * reference takes rows that are already sorted by group (gpu_ragged_dot.py:362-376) and leaves

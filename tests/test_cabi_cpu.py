@@ -85,7 +85,7 @@ def test_argument_validation_happens_on_the_host(lib):
     assert ts(g=0) == 0
     pull = lambda **kw: lib.rd_ep_combine_pull(
         kw.get("routing", a16), a16, kw.get("tokens", 8), kw.get("top_k", 2), kw.get("row_bytes", 256),
-        kw.get("experts", 8), kw.get("world", 2), a16, 64, kw.get("dtype", 1), kw.get("out", a16), None)
+        kw.get("experts", 8), kw.get("world", 2), a16, 64, kw.get("dtype", 1), kw.get("out", a16), 0, None)
     assert pull(top_k=9) == 1
     assert pull(row_bytes=250) == 1
     assert pull(experts=7) == 1
