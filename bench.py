@@ -341,11 +341,12 @@ def run_single(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     shape = {"mixtral": workloads.MIXTRAL, "decode": workloads.EP_DECODE,
-             "deepseek": workloads.DEEPSEEK_V3}[args.workload]
+             "deepseek": workloads.DEEPSEEK_V3, "deepseek_quarter": workloads.DEEPSEEK_QUARTER}[args.workload]
+    dt = {"bf16": torch.bfloat16, "f32": torch.float32}[args.dtype]
     peaks = measured_peaks()
     kernels = ["fwd", "dlhs", "drhs"] if args.only is None else [args.only]
     # Allocate only what the selected kernels touch (keeps profiler captures small).
-    x, A, dout = workloads.make_inputs(shape, dev, seed=0, with_dout=kernels != ["fwd"])
+    x, A, dout = workloads.make_inputs(shape, dev, seed=0, dtype=dt, with_dout=kernels != ["fwd"])
     if kernels == ["dlhs"]:
         x = None
     if kernels == ["drhs"]:
@@ -354,14 +355,16 @@ def run_single(args):
         gs_fwd_np, gs_bwd_np = workloads.group_sizes_mixtral(0), workloads.group_sizes_mixtral_ragged(0)
     elif args.workload == "decode":
         gs_fwd_np = gs_bwd_np = workloads.group_sizes_from_routing(workloads.topk_routing(64, 64, 4, seed=5), 64)
+    elif args.workload == "deepseek_quarter":
+        gs_fwd_np = gs_bwd_np = workloads.group_sizes_deepseek_quarter(0)
     else:
         gs_fwd_np = gs_bwd_np = workloads.group_sizes_deepseek(0)
     gs_fwd = torch.from_numpy(gs_fwd_np).to(dev)
     gs_bwd = torch.from_numpy(gs_bwd_np).to(dev)
-    y = torch.empty((shape.m, shape.n), dtype=torch.bfloat16, device=dev) if "fwd" in kernels else None
-    dx = torch.empty((shape.m, shape.k), dtype=torch.bfloat16, device=dev) if "dlhs" in kernels else None
-    dA = (torch.empty((shape.g, shape.k, shape.n), dtype=torch.bfloat16, device=dev)
-          if "drhs" in kernels else None)
+    y = torch.empty((shape.m, shape.n), dtype=dt, device=dev) if "fwd" in kernels else None
+    dx = torch.empty((shape.m, shape.k), dtype=dt, device=dev) if "dlhs" in kernels else None
+    dA = torch.empty((shape.g, shape.k, shape.n), dtype=dt, device=dev) if "drhs" in kernels else None
+    esz = 2 if dt == torch.bfloat16 else 4
     ws = ops._workspace(shape.m, shape.g, dev)
 
     def launch(name):
@@ -411,9 +414,9 @@ def run_single(args):
     traffic = dram_traffic_per_launch() if args.workload == "mixtral" else {}
     gplus_f, gplus_b = int((gs_fwd_np > 0).sum()), int((gs_bwd_np > 0).sum())
     alg_bytes = {
-        "fwd": 2.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
-        "dlhs": 2.0 * (shape.m * shape.n + gplus_b * shape.k * shape.n + shape.m * shape.k),
-        "drhs": 2.0 * (shape.m * shape.k + shape.m * shape.n + shape.g * shape.k * shape.n),
+        "fwd": esz * 1.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
+        "dlhs": esz * 1.0 * (shape.m * shape.n + gplus_b * shape.k * shape.n + shape.m * shape.k),
+        "drhs": esz * 1.0 * (shape.m * shape.k + shape.m * shape.n + shape.g * shape.k * shape.n),
     }
     for name, ms in per_kernel_ms.items():
         gbs = alg_bytes[name] / (ms * 1e-3) / 1e9
@@ -459,13 +462,14 @@ def run_single(args):
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "bf16",
+        "dtype": args.dtype if args.dtype == "bf16" else "f32 in/out, TF32 products, fp32 accumulate (the bf16 peak is NOT its roof)",
         "data": "synthetic",
         "config": (mixtral_config(shape, args.only, shape.m) if args.workload == "mixtral" else {
             "workload": shape.name + ("_fwd_bwd" if args.only is None else "_" + args.only),
             "m": shape.m, "k": shape.k, "n": shape.n, "g": shape.g,
             "group_sizes": {"decode": "64 tokens x uniform top-4 of 64 experts",
-                            "deepseek": "multinomial(Dirichlet(0.3)), ~20% empty"}[args.workload],
+                            "deepseek": "multinomial(Dirichlet(0.3)), ~20% empty",
+                            "deepseek_quarter": "multinomial(Dirichlet(0.3)) over 64 experts"}[args.workload],
             "l2": "inputs larger than L2 (weights %d MB per GEMM)" % (shape.g * shape.k * shape.n * 2 // 1000000),
         }),
         "method": "CUDA events on the launch stream; per-kernel events inside the timed region",
@@ -1050,7 +1054,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
-    ap.add_argument("--workload", default="mixtral", choices=["mixtral", "decode", "deepseek", "permute"],
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"],
+                    help="N=1 profiling runs only: f32 times the TF32 kernels (use with --no-e2e --no-cpu-baseline)")
+    ap.add_argument("--workload", default="mixtral",
+                    choices=["mixtral", "decode", "deepseek", "deepseek_quarter", "permute"],
                     help="N=1 only; the headline line is the default (mixtral); the others are for profiling")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -211,7 +211,7 @@ def gmm_forward(
     else:
         y = torch.empty((m, np_), dtype=x.dtype, device=x.device)
     ws = workspace if workspace is not None else _workspace(m, g, x.device)
-    if cfg is None:
+    if cfg is None and x.dtype != torch.float32:  # the table's entries are for the 16-bit kernels
         cfg = tile_table.lookup("gmm_t" if trans_rhs else "gmm", m, kp, np_, g)
     with torch.cuda.device(x.device):
         if group_to_weight is None:
@@ -417,7 +417,7 @@ def tgmm_forward(
     else:
         res = torch.empty((g, kp, np_), dtype=x.dtype, device=x.device)
     ws = workspace if workspace is not None else _workspace(m, gs.numel(), x.device)
-    if cfg is None and seg_count == 1:
+    if cfg is None and seg_count == 1 and x.dtype != torch.float32:
         cfg = tile_table.lookup("tgmm", m, kp, np_, g)
     with torch.cuda.device(x.device):
         if seg_count == 1:

@@ -27,6 +27,9 @@ class Shape:
 SMALL = Shape("small_m512_k256_n384_g8", 512, 256, 384, 8)
 MIXTRAL = Shape("mixtral8x7b_up_m8192_k4096_n14336_g8", 8192, 4096, 14336, 8)
 DEEPSEEK_V3 = Shape("deepseekv3_m32768_k7168_n2048_g256", 32768, 7168, 2048, 256)
+# a quarter of the DeepSeek-V3 shape (same k, n and mean rows per expert): small enough for a
+# profiler capture, still 1.9 GB of weights
+DEEPSEEK_QUARTER = Shape("deepseekv3_quarter_m8192_k7168_n2048_g64", 8192, 7168, 2048, 64)
 EP_PREFILL = Shape("ep_prefill_m32768_k4096_n1536_g64", 32768, 4096, 1536, 64)
 EP_DECODE = Shape("ep_decode_m256_k4096_n1536_g64", 256, 4096, 1536, 64)
 
@@ -64,6 +67,13 @@ def group_sizes_deepseek(seed: int = 0) -> np.ndarray:
     rng = np.random.default_rng(seed)
     p = rng.dirichlet(0.3 * np.ones(DEEPSEEK_V3.g))
     return rng.multinomial(DEEPSEEK_V3.m, p).astype(np.int32)
+
+
+def group_sizes_deepseek_quarter(seed: int = 0) -> np.ndarray:
+    """multinomial(8192, Dirichlet(0.3)) over 64 experts: the DeepSeek draw at a quarter of the size."""
+    rng = np.random.default_rng(seed)
+    p = rng.dirichlet(0.3 * np.ones(DEEPSEEK_QUARTER.g))
+    return rng.multinomial(DEEPSEEK_QUARTER.m, p).astype(np.int32)
 
 
 def topk_routing(tokens: int, experts: int, top_k: int, seed: int) -> np.ndarray:
