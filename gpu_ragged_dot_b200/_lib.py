@@ -81,6 +81,11 @@ SIGNATURES = {
     ),
     "rd_ep_plan_ring": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                  _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
+    "rd_ep_count_share": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
+                                   _c_void_p, _c_int, _c_void_p]),
+    "rd_ep_plan_ring_when_counted": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                              _c_void_p, _c_int, _c_void_p]),
     "rd_ep_assign": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
     "rd_ep_send_list": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,

@@ -523,7 +523,7 @@ int rd_ep_plan(const int32_t* counts_all, int world, int num_experts, int rank, 
   if (!counts_all || !dest_offset || !segment_sizes || !fill || !totals) return RD_ERR_BAD_POINTER;
   rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 0, nullptr, nullptr,
-      nullptr);
+      nullptr, nullptr, 0, 0u, nullptr);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -537,7 +537,43 @@ int rd_ep_plan_ring(const int32_t* counts_all, int world, int num_experts, int r
   if ((send_start == nullptr) != (list_fill == nullptr)) return RD_ERR_BAD_POINTER;
   rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 1, phase_done,
-      send_start, list_fill);
+      send_start, list_fill, nullptr, 0, 0u, nullptr);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_count_share(const int32_t* routing, int entries, int num_experts, int32_t* counts_scratch,
+                      int32_t* ticket, int world, int rank, const uint64_t* peer_counts,
+                      const uint64_t* peer_flags, int epoch, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (entries < 0 || num_experts <= 0 || num_experts > 8192 || world <= 0 || world > rd::kEpThreads ||
+      rank < 0 || rank >= world)
+    return RD_ERR_BAD_SHAPE;
+  if (!counts_scratch || !ticket || !peer_counts || !peer_flags || (entries > 0 && routing == nullptr))
+    return RD_ERR_BAD_POINTER;
+  int blocks = (entries + rd::kEpThreads - 1) / rd::kEpThreads;
+  if (blocks > sm_count()) blocks = sm_count();
+  if (blocks < 1) blocks = 1;  // the counts (zeros) and the flag go out even without entries
+  rd::ep_count_share_kernel<<<blocks, rd::kEpThreads, sizeof(int32_t) * num_experts, stream>>>(
+      routing, entries, num_experts, counts_scratch, ticket, world, rank, peer_counts, peer_flags, epoch);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+int rd_ep_plan_ring_when_counted(const int32_t* counts_all, const int32_t* count_flags, int epoch,
+                                 int world, int num_experts, int rank, int32_t* dest_offset,
+                                 int32_t* segment_sizes, int32_t* fill, int32_t* totals,
+                                 int32_t* phase_done, int32_t* send_start, int32_t* list_fill,
+                                 int32_t* status, int wait_limit_ms, void* stream) {
+  if (world <= 0 || world > rd::kEpThreads || num_experts <= 0 || num_experts % world != 0 || rank < 0 ||
+      rank >= world)
+    return RD_ERR_BAD_SHAPE;
+  if (!counts_all || !count_flags || !dest_offset || !segment_sizes || !fill || !totals || !phase_done)
+    return RD_ERR_BAD_POINTER;
+  if ((send_start == nullptr) != (list_fill == nullptr)) return RD_ERR_BAD_POINTER;
+  rd_tile_cfg cfg = {};
+  cfg.wait_limit_ms = wait_limit_ms;
+  rd::ep_plan_kernel<<<1, rd::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts_all, world, num_experts, rank, dest_offset, segment_sizes, fill, totals, 1, phase_done,
+      send_start, list_fill, count_flags, epoch, wait_limit_us(&cfg), status);
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 

@@ -22,6 +22,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "rd_ptx.cuh"
+
 namespace rd {
 
 constexpr int kEpThreads = 256;
@@ -41,6 +43,46 @@ ep_count_kernel(const int32_t* __restrict__ routing, int entries, int num_expert
     if (hist[e]) atomicAdd(&counts[e], hist[e]);
 }
 
+// ep_count_kernel + the exchange of the counts, without a collective library: the last block to
+// finish stores this rank's E counts into row `rank` of every rank's counts_all (peer stores; its
+// own included), fences at system scope and stores `epoch` into word `rank` of every rank's count
+// flags.  `counts` (E words) and `ticket` (1 word) are scratch that must be zero on entry and is
+// left zero again.  The consumer is ep_plan_kernel with count_flags set, on every rank.
+__global__ void __launch_bounds__(kEpThreads)
+ep_count_share_kernel(const int32_t* __restrict__ routing, int entries, int num_experts, int32_t* counts,
+                      int32_t* ticket, int world, int rank, const uint64_t* __restrict__ peer_counts,
+                      const uint64_t* __restrict__ peer_flags, int epoch) {
+  extern __shared__ int32_t hist[];
+  __shared__ int last;
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < entries; i += gridDim.x * blockDim.x) {
+    const int e = routing[i];
+    if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
+    if (hist[e]) atomicAdd(&counts[e], hist[e]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const int c = atomicExch(&counts[e], 0);  // read the total and leave the scratch zero
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<int32_t*>(peer_counts[r])[rank * num_experts + e] = c;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) *ticket = 0;
+  if (threadIdx.x < world) {
+    int32_t* flag = reinterpret_cast<int32_t*>(peer_flags[threadIdx.x]) + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  }
+}
+
 // One CTA.  counts_all[s * E + e]: rows source s routes to global expert e.
 //   dest_offset[e]        first row, inside the receive buffer of e's owner, of MY rows for e
 //   segment_sizes[s*El+j] rows I receive from source s for my local expert j
@@ -56,7 +98,22 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, int world, int num_expert
                int32_t* __restrict__ dest_offset, int32_t* __restrict__ segment_sizes,
                int32_t* __restrict__ fill, int32_t* __restrict__ totals, int ring,
                int32_t* __restrict__ phase_done, int32_t* __restrict__ send_start,
-               int32_t* __restrict__ list_fill) {
+               int32_t* __restrict__ list_fill, const int32_t* count_flags, int epoch,
+               uint32_t wait_limit_us, int32_t* status) {
+  // With count_flags (ep_count_share_kernel's exchange): row s of counts_all is complete once
+  // count_flags[s] >= epoch.  The waits are bounded like every wait in these kernels; on expiry
+  // the status word is set and the plan is made from whatever is there.
+  if (count_flags != nullptr) {
+    __shared__ WaitCtl ctl;
+    if (threadIdx.x == 0) {
+      ctl.abort = 0;
+      ctl.limit_us = wait_limit_us;
+    }
+    __syncthreads();
+    if (threadIdx.x < world && !wait_flag_ge(count_flags + threadIdx.x, epoch, &ctl) && status != nullptr)
+      atomicMax(status, 1);
+    __syncthreads();
+  }
   const int local = num_experts / world;
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     const int owner = e / local;

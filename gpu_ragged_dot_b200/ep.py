@@ -94,7 +94,7 @@ class ExpertParallelRaggedDot:
     def __init__(self, num_experts: int, k: int, n: int, device: torch.device, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, group: Optional[dist.ProcessGroup] = None,
                  dispatch: str = "nccl", capacity_rows: Optional[int] = None, sender_ctas: int = 0,
-                 pull_sms: int = 16):
+                 pull_sms: int = 0, count_exchange: str = "peer"):
         from . import workloads
 
         assert dispatch in ("nccl", "p2p", "fused")
@@ -111,7 +111,11 @@ class ExpertParallelRaggedDot:
         self.sender_ctas = sender_ctas or 16
         # backward: SMs the drhs product leaves free for the return exchange that runs beside it
         # (0: the exchange runs after drhs, on all SMs)
-        self.pull_sms = pull_sms
+        self.pull_sms = pull_sms or (16 if self.world <= 2 else 24)
+        # fused mode: how the per-expert counts cross ranks: "peer" = stored by the count kernel
+        # itself into every rank's table (rd_ep_count_share), "nccl" = an all-gather
+        assert count_exchange in ("peer", "nccl")
+        self.count_exchange = count_exchange
         assert num_experts % self.world == 0
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
         self.k, self.n, self.device = k, n, device
@@ -133,6 +137,8 @@ class ExpertParallelRaggedDot:
         for st in (self._ring, self._grad):
             if st is not None and ops.device_status(st["ws"]) != 0:
                 return ops.device_status(st["ws"])
+        if self._ring is not None and self._ring["share"] is not None:
+            return ops.device_status(self._ring["share"]["status"])
         return 0
 
     def timers_ms(self, steps: int):
@@ -230,7 +236,28 @@ class ExpertParallelRaggedDot:
             hb = hf = None
             buf_ptrs, flag_ptrs = [buf.data_ptr()], [flags.data_ptr()]
         E, W = self.num_experts, self.world
+        share = None
+        if W > 1 and self.count_exchange == "peer":
+            # two counts_all tables (by epoch parity) and the count flags, addressable by every rank
+            tables = symm_mem.empty((2, W, E), dtype=torch.int32, device=dev)
+            cflags = symm_mem.empty((max(W, 4),), dtype=torch.int32, device=dev)
+            tables.zero_()
+            cflags.zero_()
+            ht, hc = symm_mem.rendezvous(tables, grp), symm_mem.rendezvous(cflags, grp)
+            torch.cuda.synchronize(dev)
+            hc.barrier(channel=0)
+            torch.cuda.synchronize(dev)
+            tptr = [int(p) for p in ht.buffer_ptrs]
+            share = {"tables": tables, "flags": cflags, "handles": (ht, hc),
+                     "scratch": torch.zeros(E + 1, dtype=torch.int32, device=dev),
+                     # set by the plan kernel if its wait for the counts expired (the GEMM's own
+                     # status word is reset by the GEMM call that follows the plan)
+                     "status": torch.zeros(4, dtype=torch.int32, device=dev),
+                     "peer_counts": [torch.tensor([p + par * W * E * 4 for p in tptr], dtype=torch.int64, device=dev)
+                                     for par in (0, 1)],
+                     "peer_flags": torch.tensor([int(p) for p in hc.buffer_ptrs], dtype=torch.int64, device=dev)}
         self._ring = {
+            "share": share,
             "buf": buf, "flags": flags, "handles": (hb, hf), "capacity": capacity_rows,
             "buf_ptrs": buf_ptrs, "flag_ptrs": flag_ptrs,
             "counts_all": torch.empty((W, E), dtype=torch.int32, device=dev),
@@ -264,12 +291,20 @@ class ExpertParallelRaggedDot:
             ev[0].record()
         routing = routing.to(torch.int32).contiguous()
         x_tokens = x_tokens.contiguous()
-        counts = ops.ep_count(routing, self.num_experts)
-        if W > 1:
-            dist.all_gather_into_tensor(st["counts_all"].view(-1), counts, group=self.group)
+        if st["share"] is not None:
+            # counts cross ranks inside the count kernel; the plan kernel waits for them
+            sh = st["share"]
+            ops.ep_count_share(routing, self.num_experts, sh["scratch"], W, self.rank,
+                               sh["peer_counts"][epoch & 1], sh["peer_flags"], epoch)
+            plan = ops.ep_plan_ring_when_counted(sh["tables"][epoch & 1], sh["flags"], epoch, self.rank,
+                                                 st["plan"], sh["status"])
         else:
-            st["counts_all"].copy_(counts.view(1, -1))
-        plan = ops.ep_plan_ring(st["counts_all"], self.rank, st["plan"])
+            counts = ops.ep_count(routing, self.num_experts)
+            if W > 1:
+                dist.all_gather_into_tensor(st["counts_all"].view(-1), counts, group=self.group)
+            else:
+                st["counts_all"].copy_(counts.view(1, -1))
+            plan = ops.ep_plan_ring(st["counts_all"], self.rank, st["plan"])
         entries = tokens * top_k
         dest_pos = torch.empty(entries, dtype=torch.int32, device=self.device)
         send_index = torch.empty(entries, dtype=torch.int32, device=self.device)

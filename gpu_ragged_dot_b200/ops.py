@@ -333,6 +333,41 @@ def ep_plan_ring(counts_all: torch.Tensor, rank: int, bufs: Optional[dict] = Non
     return bufs
 
 
+def ep_count_share(routing: torch.Tensor, num_experts: int, scratch: torch.Tensor, world: int, rank: int,
+                   peer_counts: torch.Tensor, peer_flags: torch.Tensor, epoch: int) -> None:
+    """``rd_ep_count_share``: count the routing table and store the counts into row ``rank`` of every
+    rank's counts_all, then ``epoch`` into every rank's count flag ``rank``.  ``scratch`` is an int32
+    device tensor of num_experts + 1 zeros (the call leaves it zero); ``peer_counts`` / ``peer_flags``
+    are int64 device tensors of `world` addresses."""
+    lib = _lib.load()
+    r = _as_i32(routing.reshape(-1))
+    assert scratch.dtype == torch.int32 and scratch.numel() >= num_experts + 1 and scratch.is_cuda
+    with torch.cuda.device(r.device):
+        rc = lib.rd_ep_count_share(r.data_ptr(), r.numel(), num_experts, scratch.data_ptr(),
+                                   scratch.data_ptr() + 4 * num_experts, world, rank, peer_counts.data_ptr(),
+                                   peer_flags.data_ptr(), int(epoch), _stream_ptr(r.device))
+    _lib.check(rc, "rd_ep_count_share")
+
+
+def ep_plan_ring_when_counted(counts_all: torch.Tensor, count_flags: torch.Tensor, epoch: int, rank: int,
+                              bufs: dict, workspace: torch.Tensor, wait_limit_ms: int = 0) -> dict:
+    """``rd_ep_plan_ring_when_counted``: ``ep_plan_ring`` that first waits, on the device and bounded,
+    for every source's counts of this epoch.  ``workspace`` holds the status word that reports an
+    expired wait (any int32 device tensor; ``device_status`` reads it)."""
+    lib = _lib.load()
+    assert counts_all.dim() == 2 and counts_all.dtype == torch.int32 and counts_all.is_contiguous()
+    world, experts = counts_all.shape
+    dev = counts_all.device
+    with torch.cuda.device(dev):
+        rc = lib.rd_ep_plan_ring_when_counted(
+            counts_all.data_ptr(), count_flags.data_ptr(), int(epoch), world, experts, rank,
+            bufs["dest_offset"].data_ptr(), bufs["segment_sizes"].data_ptr(), bufs["fill"].data_ptr(),
+            bufs["totals"].data_ptr(), bufs["phase_done"].data_ptr(), bufs["send_start"].data_ptr(),
+            bufs["list_fill"].data_ptr(), workspace.data_ptr(), int(wait_limit_ms), _stream_ptr(dev))
+    _lib.check(rc, "rd_ep_plan_ring_when_counted")
+    return bufs
+
+
 def ep_assign(routing: torch.Tensor, num_experts: int, world: int, rank: int, plan: dict, capacity_rows: int,
               dest_pos: torch.Tensor, send_index: torch.Tensor) -> None:
     """``rd_ep_assign``: positions at the owners (dest_pos) and the per-phase send lists."""

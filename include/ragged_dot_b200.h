@@ -163,6 +163,29 @@ int rd_gmm_indexed_when_ready(const void* x, const void* A, int num_weights, con
                               int dtype, const rd_tile_cfg* cfg, const int32_t* ready_flags,
                               int groups_per_flag, int epoch, void* stream);
 
+/* The exchange of the per-expert counts without a collective library (no counterpart in the
+ * reference): a small all-gather costs more in launch latency than in bytes.
+ *   rd_ep_count_share            rd_ep_count whose last block stores this rank's E counts into row
+ *                                `rank` of EVERY rank's counts_all[world][E] (peer_counts[r] = that
+ *                                array on rank r as seen from this GPU, its own included) and then
+ *                                `epoch` into word `rank` of every rank's count flags (peer_flags[r]).
+ *                                counts_scratch[E] and ticket[1] must be zero before the first call;
+ *                                every call leaves them zero.
+ *   rd_ep_plan_ring_when_counted rd_ep_plan_ring that first waits (bounded; expiry sets *status,
+ *                                the workspace status word of the GEMM that follows) until
+ *                                count_flags[s] >= epoch for every source s.
+ * The pair also orders the buffers' reuse, as the all-gather did: a rank's counts of step t+1
+ * leave only after its kernels of step t.  Callers alternate between two counts_all arrays by
+ * epoch parity so that a fast rank cannot overwrite counts a slow rank has not planned from. */
+int rd_ep_count_share(const int32_t* routing, int entries, int num_experts, int32_t* counts_scratch,
+                      int32_t* ticket, int world, int rank, const uint64_t* peer_counts,
+                      const uint64_t* peer_flags, int epoch, void* stream);
+int rd_ep_plan_ring_when_counted(const int32_t* counts_all, const int32_t* count_flags, int epoch,
+                                 int world, int num_experts, int rank, int32_t* dest_offset,
+                                 int32_t* segment_sizes, int32_t* fill, int32_t* totals,
+                                 int32_t* phase_done, int32_t* send_start, int32_t* list_fill,
+                                 int32_t* status, int wait_limit_ms, void* stream);
+
 /* The same exchange with the sending done INSIDE the GEMM kernel (one launch does both): 
  * `sender_ctas` CTAs of the persistent grid push this rank's rows of phases 1 .. world-1 to
  * their owners (bulk async copies global -> shared, plain stores shared -> peer memory, then the
