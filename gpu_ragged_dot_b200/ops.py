@@ -938,33 +938,98 @@ class RaggedDotDimensionNumbers(NamedTuple):
 
 def ragged_dot_general(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor,
                        ragged_dot_dimension_numbers: RaggedDotDimensionNumbers, **kwargs) -> torch.Tensor:
-    """The two modes of ``jax.lax.ragged_dot_general`` that the reference implements, chosen by
-    dimension numbers as its tests spell them (tests.py:31-48):
+    """``jax.lax.ragged_dot_general`` over the grouped GEMMs of this library.  The reference
+    implements the first two modes without batch dimensions (its tests spell them as dimension
+    numbers, tests.py:31-48); the third mode and one batch dimension are added here.
 
-    * ragged non-contracting dimension -- lhs ``[m, k]`` ragged in dim 0, rhs ``[g, k, n]`` (or
-      ``[g, n, k]`` when the rhs contracting dimension is 2) with group dimension 0 -> ``gmm``;
-    * ragged contracting dimension -- lhs ``[m, k]`` and rhs ``[m, n]`` contracted over dim 0, which
-      is the ragged one, no rhs group dimension -> ``tgmm``, result ``[g, k, n]``.
+    With g groups, one contracting dimension and at most one batch dimension b on each side:
 
-    Batch dimensions and the ragged-batch mode are not built and raise ``NotImplementedError``.
-    ``kwargs`` are passed on (``block_*`` hints and so on)."""
+    * ragged non-contracting dimension -- lhs ``[m, k]`` / ``[b, m, k]`` ragged in m, rhs with one
+      group dimension ``[g, k, n]`` (``[g, n, k]`` when its contracting dimension comes last), with a
+      batch dimension in any position, group_sizes ``[g]`` / ``[b, g]``  ->  ``[m, n]`` / ``[b, m, n]``
+      (``gmm`` per batch element);
+    * ragged contracting dimension -- lhs ``[m, k]`` / ``[b, m, k]`` and rhs ``[m, n]`` / ``[b, m, n]``
+      contracted over m, the ragged one, no rhs group dimension  ->  ``[g, k, n]`` / ``[g, b, k, n]``
+      (``tgmm`` per batch element; the group dimension leads, as in jax);
+    * ragged batch dimension -- lhs ``[b, m, k]``, rhs ``[b, k, n]``, group_sizes ``[g]`` partitioning
+      b  ->  ``[b, m, n]``: every batch element is its own product, elements past
+      ``sum(group_sizes)`` are zero (one ``gmm`` with b groups of m rows).
+
+    Anything else (several contracting or batch dimensions, extra free dimensions, a group offset)
+    raises ``NotImplementedError``.  ``kwargs`` are passed on (``block_*`` hints and so on)."""
     dn = ragged_dot_dimension_numbers
     (lhs_c, rhs_c), (lhs_b, rhs_b) = dn.dot_dimension_numbers
     lhs_c, rhs_c = [int(d) for d in lhs_c], [int(d) for d in rhs_c]
+    lhs_b, rhs_b = [int(d) for d in lhs_b], [int(d) for d in rhs_b]
     ragged = [int(d) for d in dn.lhs_ragged_dimensions]
     groups = [int(d) for d in dn.rhs_group_dimensions]
-    if len(lhs_b) or len(rhs_b):
-        raise NotImplementedError("ragged_dot_general: batch dimensions are not supported")
-    if lhs.dim() != 2 or ragged != [0] or len(lhs_c) != 1 or len(rhs_c) != 1:
-        raise NotImplementedError(
-            "ragged_dot_general: lhs must be [m, k] (or [m, n]) with ragged dimension 0 and one "
-            f"contracting dimension, got {lhs.dim()=} {ragged=} {lhs_c=} {rhs_c=}")
-    if groups == [0] and lhs_c == [1] and rhs.dim() == 3 and rhs_c[0] in (1, 2):
-        return gmm(lhs, rhs, group_sizes, trans_rhs=(rhs_c[0] == 2), **kwargs)
-    if groups == [] and lhs_c == [0] and rhs_c == [0] and rhs.dim() == 2:
-        return tgmm(lhs, rhs, group_sizes, **kwargs)
-    raise NotImplementedError(
-        f"ragged_dot_general: unsupported dimension numbers {dn} for shapes {tuple(lhs.shape)}, {tuple(rhs.shape)}")
+
+    def bad(why):
+        return NotImplementedError(
+            f"ragged_dot_general: {why} (dimension numbers {dn}, shapes {tuple(lhs.shape)}, {tuple(rhs.shape)})")
+
+    if len(lhs_c) != 1 or len(rhs_c) != 1 or len(ragged) != 1:
+        raise bad("exactly one contracting and one ragged dimension are supported")
+    if len(lhs_b) != len(rhs_b) or len(lhs_b) > 1:
+        raise bad("at most one batch dimension on each side is supported")
+    if len(groups) > 1:
+        raise bad("at most one rhs group dimension")
+    nb = len(lhs_b)
+    if lhs.dim() != 2 + nb:
+        raise bad("lhs must be [m, k] or [b, m, k] up to the order of its dimensions")
+    if len(set(lhs_c + lhs_b)) != 1 + nb or len(set(rhs_c + rhs_b + groups)) != 1 + nb + len(groups):
+        raise bad("a dimension is named twice")
+    rg, lc = ragged[0], lhs_c[0]
+
+    # ---- ragged batch dimension
+    if nb == 1 and rg == lhs_b[0]:
+        if groups or rhs.dim() != 3:
+            raise bad("the ragged-batch mode takes an rhs [b, k, n] without a group dimension")
+        m_dim = ({0, 1, 2} - {lhs_b[0], lc}).pop()
+        n_dim = ({0, 1, 2} - {rhs_b[0], rhs_c[0]}).pop()
+        x = lhs.permute(lhs_b[0], m_dim, lc).contiguous()          # [b, m, k]
+        w = rhs.permute(rhs_b[0], rhs_c[0], n_dim).contiguous()    # [b, k, n]
+        b, m, k = x.shape
+        if w.shape[0] != b or w.shape[1] != k:
+            raise bad("batch / contracting sizes of lhs and rhs differ")
+        gs = _as_i32(group_sizes)
+        live = torch.clamp(gs.sum(), max=b)                       # batch elements that belong to a group
+        per_batch = torch.where(torch.arange(b, device=x.device) < live, m, 0).to(torch.int32)
+        return gmm(x.reshape(b * m, k), w, per_batch, **kwargs).reshape(b, m, w.shape[2])
+
+    # ---- ragged non-contracting dimension (gmm)
+    if rg != lc and len(groups) == 1:
+        if rhs.dim() != 3 + nb:
+            raise bad("rhs must have a group, a contracting and a free dimension (and the batch dimension)")
+        free = (set(range(rhs.dim())) - {groups[0], rhs_c[0]} - set(rhs_b)).pop()
+        trans = rhs_c[0] > free  # rhs stored [.., n, k]: use the transposed-rhs kernel, no copy of the weights
+        order = rhs_b + [groups[0]] + ([free, rhs_c[0]] if trans else [rhs_c[0], free])
+        w = rhs.permute(*order)
+        x = lhs.permute(*(lhs_b + [rg, lc]))
+        if nb == 0:
+            return gmm(x, w.contiguous(), group_sizes, trans_rhs=trans, **kwargs)
+        gs = group_sizes
+        if gs.dim() != 2 or gs.shape[0] != x.shape[0] or w.shape[0] != x.shape[0]:
+            raise bad("with a batch dimension group_sizes must be [b, g] and the batch sizes must agree")
+        return torch.stack([gmm(x[i].contiguous(), w[i].contiguous(), gs[i], trans_rhs=trans, **kwargs)
+                            for i in range(x.shape[0])])
+
+    # ---- ragged contracting dimension (tgmm)
+    if rg == lc and not groups:
+        if rhs.dim() != 2 + nb:
+            raise bad("rhs must be [m, n] or [b, m, n] up to the order of its dimensions")
+        k_dim = (set(range(lhs.dim())) - {lc} - set(lhs_b)).pop()
+        n_dim = (set(range(rhs.dim())) - {rhs_c[0]} - set(rhs_b)).pop()
+        x = lhs.permute(*(lhs_b + [lc, k_dim]))
+        y = rhs.permute(*(rhs_b + [rhs_c[0], n_dim]))
+        if nb == 0:
+            return tgmm(x.contiguous(), y.contiguous(), group_sizes, **kwargs)
+        gs = group_sizes
+        if gs.dim() != 2 or gs.shape[0] != x.shape[0] or y.shape[0] != x.shape[0]:
+            raise bad("with a batch dimension group_sizes must be [b, g] and the batch sizes must agree")
+        return torch.stack([tgmm(x[i].contiguous(), y[i].contiguous(), gs[i], **kwargs)
+                            for i in range(x.shape[0])], dim=1)  # [g, b, k, n]
+    raise bad("unsupported combination of ragged, group and contracting dimensions")
 
 
 def device_status(workspace: torch.Tensor) -> int:

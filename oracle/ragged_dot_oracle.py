@@ -12,6 +12,9 @@ It restates, in NumPy / torch-CPU, what the reference computes:
   * trans_ragged_dot     -- _gpu_tgmm_kernel, gpu_ragged_dot.py:250-281 (zero block for an
                             empty group), dimension numbers of tests.py:34-36
   * ragged_dot_vjp       -- _gpu_gmm_bwd, gpu_ragged_dot.py:399-402
+  * ragged_dot_general_batched -- the op of tests.py:39-48 with a batch dimension / ragged batch
+                            (jax.lax.ragged_dot_general's published semantics; the reference
+                            itself has no batched form)
   * rel_l2_err           -- err_fn, tests.py:74-79
   * reference_group_sizes / reference_normal -- the generators of tests.py:51-62
 
@@ -156,6 +159,27 @@ def ragged_dot_permuted(x, A, group_sizes, in_rows=None, out_rows=None, y_rows=N
     y = torch.zeros((y_rows, ys.shape[1]), dtype=ys.dtype) if out is None else out.clone()
     y[torch.as_tensor(out_rows).long()[:total]] = ys[:total]
     return y
+
+
+def ragged_dot_general_batched(mode: str, lhs: torch.Tensor, rhs: torch.Tensor, group_sizes) -> torch.Tensor:
+    """jax.lax.ragged_dot_general with one batch dimension in canonical layouts (the dimension
+    numbers of tests.py:31-36 with a leading batch dimension added):
+      "ragged_m":     lhs [b,m,k], rhs [b,g,k,n], group_sizes [b,g] -> [b,m,n]
+      "ragged_k":     lhs [b,m,k], rhs [b,m,n],   group_sizes [b,g] -> [g,b,k,n]
+      "ragged_batch": lhs [b,m,k], rhs [b,k,n],   group_sizes [g]   -> [b,m,n], zero past sum(group_sizes)
+    """
+    b = lhs.shape[0]
+    if mode == "ragged_m":
+        return torch.stack([ragged_dot(lhs[i], rhs[i], group_sizes[i]) for i in range(b)])
+    if mode == "ragged_k":
+        return torch.stack([trans_ragged_dot(lhs[i], rhs[i], group_sizes[i]) for i in range(b)], dim=1)
+    if mode == "ragged_batch":
+        live = min(int(torch.as_tensor(group_sizes).sum()), b)
+        out = torch.zeros((b, lhs.shape[1], rhs.shape[2]), dtype=torch.float32)
+        for i in range(live):
+            out[i] = _f32(lhs[i]) @ _f32(rhs[i])
+        return out.to(lhs.dtype)
+    raise ValueError(mode)
 
 
 def rel_l2_err(a: torch.Tensor, b: torch.Tensor, axis=-1, mask=None) -> torch.Tensor:

@@ -1029,3 +1029,42 @@ def test_float32_highest_precision_three_tf32_passes():
     want_dx = oracle64(dout, A, trans=True)
     assert float(oracle.rel_l2_err(xg.grad.cpu(), want_dx.float(), mask=mask).max()) < 2e-5
     assert float(oracle.rel_l2_err(Ag.grad.cpu(), want_t.float(), axis=(-1, -2), mask=gs != 0).max()) < 2e-5
+
+
+# ------------------------------------------------------------------ ragged_dot_general: batch dimension, ragged batch
+def test_ragged_dot_general_batched_and_ragged_batch():
+    """The three modes of jax.lax.ragged_dot_general with one batch dimension, in permuted layouts
+    too, against the oracle's loops over the batch."""
+    b, m, k, n, g = 3, 200, 72, 136, 4
+    rng = np.random.default_rng(33)
+    bf = lambda a: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16)  # noqa: E731
+    lhs = bf(rng.standard_normal((b, m, k)))
+    w = bf(rng.standard_normal((b, g, k, n)) / np.sqrt(k))
+    y = bf(rng.standard_normal((b, m, n)))
+    gs = torch.tensor([[50, 0, 100, 30], [200, 0, 0, 0], [1, 64, 65, 70]], dtype=torch.int32)
+    DN = rd.RaggedDotDimensionNumbers
+    close = lambda got, want, what: _assert_close(got.cpu(), want, what)  # noqa: E731
+    # ragged m, rhs [b, g, k, n]
+    got = rd.ragged_dot_general(lhs.to(DEV), w.to(DEV), gs.to(DEV), DN((([2], [2]), ([0], [0])), [1], [1]))
+    want = oracle.ragged_dot_general_batched("ragged_m", lhs, w, gs)
+    assert got.shape == (b, m, n)
+    close(got, want, "general: ragged m, batched")
+    # the same with rhs stored [g, b, n, k] (group first, contracting last)
+    w2 = w.permute(1, 0, 3, 2).contiguous()
+    got = rd.ragged_dot_general(lhs.to(DEV), w2.to(DEV), gs.to(DEV), DN((([2], [3]), ([0], [1])), [1], [0]))
+    close(got, want, "general: ragged m, batched, rhs [g, b, n, k]")
+    # ragged k -> [g, b, k, n]
+    got = rd.ragged_dot_general(lhs.to(DEV), y.to(DEV), gs.to(DEV), DN((([1], [1]), ([0], [0])), [1], []))
+    want = oracle.ragged_dot_general_batched("ragged_k", lhs, y, gs)
+    assert got.shape == (g, b, k, n)
+    close(got, want, "general: ragged k, batched")
+    # ragged batch: group sizes partition b; elements past their sum are zero
+    w3 = bf(rng.standard_normal((b, k, n)) / np.sqrt(k))
+    for sizes in ([1, 1], [3], [0, 2, 1], [5]):
+        gsb = torch.tensor(sizes, dtype=torch.int32)
+        got = rd.ragged_dot_general(lhs.to(DEV), w3.to(DEV), gsb.to(DEV), DN((([2], [1]), ([0], [0])), [0], []))
+        want = oracle.ragged_dot_general_batched("ragged_batch", lhs, w3, gsb)
+        assert got.shape == (b, m, n)
+        close(got, want, f"general: ragged batch {sizes}")
+        live = min(sum(sizes), b)
+        assert float(got[live:].float().abs().max() if live < b else 0.0) == 0.0

@@ -116,9 +116,30 @@ def test_ragged_dot_general_dimension_numbers():
     for dn, rhs in ((gmm_dn, A), (tgmm_dn, y), (DN((([1], [2]), ([], [])), [0], [0]), A.transpose(1, 2))):
         with pytest.raises(RuntimeError, match="no CPU fallback"):
             rd.ragged_dot_general(x, rhs, gs, dn)
-    for dn, rhs in ((DN((([1], [1]), ([0], [0])), [0], [0]), A),   # batch dimensions
+    for dn, rhs in ((DN((([1], [1]), ([0], [0])), [0], [0]), A),   # a batch dimension on a 2-D lhs
+                    (DN((([1, 0], [1, 0]), ([], [])), [0], [0]), A),  # two contracting dimensions
                     (DN((([1], [1]), ([], [])), [1], [0]), A),     # ragged in the contracting dim of a 3-D rhs
                     (DN((([0], [0]), ([], [])), [0], [0]), y),     # group dimension on a 2-D rhs
                     (gmm_dn, y)):                                  # gmm numbers, 2-D rhs
         with pytest.raises(NotImplementedError):
             rd.ragged_dot_general(x, rhs, gs, dn)
+
+
+def test_ragged_dot_general_batched_modes_reach_the_kernels():
+    """One batch dimension and the ragged-batch mode are routed to gmm / tgmm (which refuse CPU
+    tensors); malformed batched calls are refused first."""
+    DN = rd.RaggedDotDimensionNumbers
+    b, m, k, n, g = 2, 8, 4, 6, 3
+    lhs, w, y = torch.zeros(b, m, k), torch.zeros(b, g, k, n), torch.zeros(b, m, n)
+    gs2 = torch.tensor([[3, 5, 0], [8, 0, 0]], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.ragged_dot_general(lhs, w, gs2, DN((([2], [2]), ([0], [0])), [1], [1]))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.ragged_dot_general(lhs, y, gs2, DN((([1], [1]), ([0], [0])), [1], []))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        rd.ragged_dot_general(lhs, torch.zeros(b, k, n), torch.tensor([1, 1], dtype=torch.int32),
+                              DN((([2], [1]), ([0], [0])), [0], []))
+    with pytest.raises(NotImplementedError):  # group_sizes must carry the batch dimension
+        rd.ragged_dot_general(lhs, w, gs2[0], DN((([2], [2]), ([0], [0])), [1], [1]))
+    with pytest.raises(NotImplementedError):  # ragged batch with a group dimension on rhs
+        rd.ragged_dot_general(lhs, w, gs2[0], DN((([2], [2]), ([0], [0])), [0], [1]))
