@@ -745,7 +745,8 @@ EP_COLLECTIVE = {
              "back with peer loads after a symmetric-memory barrier",
 }
 # our kernels per step (forward + backward), collectives and torch's own kernels not counted
-EP_LAUNCHES = {"nccl": 1 + 2 + 2 + 2, "p2p": 4 + 2 + 2 + 2 + 1, "fused": 6 + 2 + 2 + 1}
+EP_LAUNCHES = {"nccl": 1 + 2 + 2 + 2, "p2p": 4 + 2 + 2 + 2 + 1, "fused": 6 + 2 + 2 + 1}  # fused: count+share,
+# plan, assign, own rows, metadata, send+GEMM; metadata + dlhs; metadata + drhs; pull
 
 
 def ep_parity_check(layer, mode, out, dy, dx, dW, routing, world, dev, sample_tokens=48):
@@ -849,16 +850,22 @@ def run_expert_parallel(args):
         torch.cuda.synchronize()
         sampler = ClockSampler(physical_gpu_index(local)).start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        layer.reset_timers()
         e0.record()
         for _ in range(args.steps):
-            layer.forward(x_tokens, routing, timed=True)
-            layer.backward(dy, timed=True)
+            layer.forward(x_tokens, routing)
+            layer.backward(dy)
         e1.record()
         torch.cuda.synchronize()
         dist.barrier()
         clocks = sampler.stop()
         ms = e0.elapsed_time(e1) / args.steps
+        # the breakdown comes from a second, untimed pass with events between the parts of a step
+        layer.reset_timers()
+        for _ in range(args.steps):
+            layer.forward(x_tokens, routing, timed=True)
+            layer.backward(dy, timed=True)
+        torch.cuda.synchronize()
+        dist.barrier()
         parts = layer.timers_ms(args.steps)
         bparts = layer.backward_timers_ms(args.steps)
         bad = torch.tensor([float(layer.device_status() != 0)], device=dev)

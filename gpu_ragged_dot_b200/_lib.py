@@ -45,6 +45,21 @@ class EpSend(ctypes.Structure):
                 ("rank", ctypes.c_int32), ("capacity_rows", ctypes.c_int32), ("sender_ctas", ctypes.c_int32)]
 
 
+class EpStep(ctypes.Structure):
+    """Mirror of ``rd_ep_step``."""
+
+    _fields_ = [("routing", ctypes.c_void_p), ("tokens", ctypes.c_int32), ("top_k", ctypes.c_int32),
+                ("num_experts", ctypes.c_int32), ("epoch", ctypes.c_int32),
+                ("counts_scratch", ctypes.c_void_p), ("ticket", ctypes.c_void_p),
+                ("peer_counts", ctypes.c_void_p), ("peer_count_flags", ctypes.c_void_p),
+                ("counts_all", ctypes.c_void_p), ("count_flags", ctypes.c_void_p),
+                ("dest_offset", ctypes.c_void_p), ("segment_sizes", ctypes.c_void_p), ("fill", ctypes.c_void_p),
+                ("totals", ctypes.c_void_p), ("send_start", ctypes.c_void_p), ("list_fill", ctypes.c_void_p),
+                ("plan_status", ctypes.c_void_p), ("dest_pos", ctypes.c_void_p), ("send_index", ctypes.c_void_p),
+                ("own_buffer", ctypes.c_void_p), ("own_ready_flag", ctypes.c_void_p),
+                ("wait_limit_ms", ctypes.c_int32)]
+
+
 SIGNATURES = {
     "rd_version": (_c_int, []),
     "rd_status_string": (ctypes.c_char_p, [_c_int]),
@@ -120,6 +135,11 @@ SIGNATURES = {
     "rd_ep_count": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]),
     "rd_ep_plan": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                             _c_void_p]),
+    "rd_ep_fused_forward": (
+        _c_int,
+        [ctypes.POINTER(EpStep), _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_size_t,
+         _c_int, _c_int, _c_int, _c_int, ctypes.POINTER(TileCfg), _c_void_p, ctypes.POINTER(EpSend), _c_void_p],
+    ),
     "rd_ep_dispatch": (
         _c_int,
         [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,

@@ -1008,6 +1008,36 @@ int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t
                   n, g, trans_rhs, dtype, cfg, stream, ReadyFlags{ready_flags, groups_per_flag, epoch}, &a);
 }
 
+int rd_ep_fused_forward(const rd_ep_step* st, const void* recv, const void* A, int num_weights,
+                        const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                        int capacity_rows, int k, int n, int dtype, const rd_tile_cfg* cfg,
+                        const int32_t* ready_flags, const rd_ep_send* send, void* stream) {
+  if (st == nullptr || send == nullptr) return RD_ERR_BAD_POINTER;
+  const int world = send->world, rank = send->rank;
+  if (world < 2 || st->tokens < 0 || st->top_k <= 0 || st->num_experts <= 0 || st->num_experts % world != 0)
+    return RD_ERR_BAD_SHAPE;
+  const int entries = st->tokens * st->top_k;
+  const int local = st->num_experts / world;
+  int rc = rd_ep_count_share(st->routing, entries, st->num_experts, st->counts_scratch, st->ticket, world,
+                             rank, st->peer_counts, st->peer_count_flags, st->epoch, stream);
+  if (rc != RD_OK) return rc;
+  rc = rd_ep_plan_ring_when_counted(st->counts_all, st->count_flags, st->epoch, world, st->num_experts, rank,
+                                    st->dest_offset, st->segment_sizes, st->fill, st->totals,
+                                    send->phase_done, st->send_start, st->list_fill, st->plan_status,
+                                    st->wait_limit_ms, stream);
+  if (rc != RD_OK) return rc;
+  rc = rd_ep_assign(st->routing, entries, st->num_experts, world, rank, st->dest_offset, st->fill,
+                    capacity_rows, st->dest_pos, st->send_start, st->list_fill, st->send_index, stream);
+  if (rc != RD_OK) return rc;
+  rc = rd_ep_send_list(send->x_tokens, st->top_k, send->row_bytes, st->send_index, st->send_start, 0, world,
+                       entries, st->dest_pos, st->own_buffer, capacity_rows, send->phase_done,
+                       st->own_ready_flag, st->epoch, stream);
+  if (rc != RD_OK) return rc;
+  return rd_gmm_ep_fused(recv, A, num_weights, st->segment_sizes, group_to_weight, y, workspace,
+                         workspace_bytes, capacity_rows, k, n, world * local, 0, dtype, cfg, ready_flags, local,
+                         st->epoch, send, stream);
+}
+
 int rd_device_status(const void* workspace, void* stream) {
   if (workspace == nullptr) return RD_ERR_BAD_POINTER;
   int32_t word = 0;

@@ -291,6 +291,9 @@ class ExpertParallelRaggedDot:
             ev[0].record()
         routing = routing.to(torch.int32).contiguous()
         x_tokens = x_tokens.contiguous()
+        entries = tokens * top_k
+        if st["share"] is not None and not timed:
+            return self._forward_fused_one_call(st, x_tokens, routing, tokens, top_k, epoch)
         if st["share"] is not None:
             # counts cross ranks inside the count kernel; the plan kernel waits for them
             sh = st["share"]
@@ -305,7 +308,6 @@ class ExpertParallelRaggedDot:
             else:
                 st["counts_all"].copy_(counts.view(1, -1))
             plan = ops.ep_plan_ring(st["counts_all"], self.rank, st["plan"])
-        entries = tokens * top_k
         dest_pos = torch.empty(entries, dtype=torch.int32, device=self.device)
         send_index = torch.empty(entries, dtype=torch.int32, device=self.device)
         ops.ep_assign(routing, self.num_experts, W, self.rank, plan, st["capacity"], dest_pos, send_index)
@@ -317,6 +319,20 @@ class ExpertParallelRaggedDot:
         if timed:
             ev[4].record()
             ev[2].record()
+        send = self._send_struct(st, x_tokens, send_index, dest_pos, plan, top_k)
+        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        y = ops.gmm_ep_fused(st["buf"], self.weights, plan["segment_sizes"], st["seg2e"], st["y"], st["ws"],
+                             st["flags"], self.local_experts, epoch, send, cfg=cfg)
+        if timed:
+            ev[3].record()
+            self._events.append(ev)
+        self._saved = {"recv": st["buf"], "seg": plan["segment_sizes"], "seg2e": st["seg2e"],
+                       "dest_pos": dest_pos, "routing": routing, "capacity": st["capacity"]}
+        return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
+
+    def _send_struct(self, st, x_tokens, send_index, dest_pos, plan, top_k):
+        from . import _lib
+
         if "send" not in st:
             st["send_arrays"] = (torch.tensor(st["buf_ptrs"], dtype=torch.int64, device=self.device),
                                  torch.tensor(st["flag_ptrs"], dtype=torch.int64, device=self.device))
@@ -328,17 +344,49 @@ class ExpertParallelRaggedDot:
         send.send_start, send.dest_pos = plan["send_start"].data_ptr(), dest_pos.data_ptr()
         send.phase_done = plan["phase_done"].data_ptr()
         send.row_bytes, send.top_k = x_tokens.shape[1] * x_tokens.element_size(), top_k
-        send.world, send.rank, send.capacity_rows = W, self.rank, st["capacity"]
-        send.sender_ctas = self.sender_ctas if W > 1 else 1
-        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
-        y = ops.gmm_ep_fused(st["buf"], self.weights, plan["segment_sizes"], st["seg2e"], st["y"], st["ws"],
-                             st["flags"], self.local_experts, epoch, send, cfg=cfg)
-        if timed:
-            ev[3].record()
-            self._events.append(ev)
+        send.world, send.rank, send.capacity_rows = self.world, self.rank, st["capacity"]
+        send.sender_ctas = self.sender_ctas if self.world > 1 else 1
+        return send
+
+    def _forward_fused_one_call(self, st, x_tokens, routing, tokens, top_k, epoch):
+        """The fused forward through ``rd_ep_fused_forward``: the five launches of the step from one
+        C call, with persistent position / send-list buffers (two sets, taken in turn, so the
+        dest_pos a step returns stays valid until the step after the next)."""
+        from . import _lib, ops
+
+        sh, plan, par = st["share"], st["plan"], epoch & 1
+        entries = tokens * top_k
+        key = (entries, par)
+        if key not in st.setdefault("pos", {}):
+            st["pos"][key] = (torch.empty(entries, dtype=torch.int32, device=self.device),
+                              torch.empty(entries, dtype=torch.int32, device=self.device))
+        dest_pos, send_index = st["pos"][key]
+        send = self._send_struct(st, x_tokens, send_index, dest_pos, plan, top_k)
+        if "step" not in st:
+            step = _lib.EpStep()
+            step.num_experts = self.num_experts
+            step.counts_scratch = sh["scratch"].data_ptr()
+            step.ticket = sh["scratch"].data_ptr() + 4 * self.num_experts
+            step.peer_count_flags = sh["peer_flags"].data_ptr()
+            step.count_flags = sh["flags"].data_ptr()
+            for name in ("dest_offset", "segment_sizes", "fill", "totals", "send_start", "list_fill"):
+                setattr(step, name, plan[name].data_ptr())
+            step.plan_status = sh["status"].data_ptr()
+            step.own_buffer = st["buf_ptrs"][self.rank]
+            step.own_ready_flag = st["flag_ptrs"][self.rank]
+            step.wait_limit_ms = 0
+            st["step"] = step
+            st["cfg"] = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        step = st["step"]
+        step.routing, step.tokens, step.top_k, step.epoch = routing.data_ptr(), tokens, top_k, epoch
+        step.peer_counts = sh["peer_counts"][par].data_ptr()
+        step.counts_all = sh["tables"][par].data_ptr()
+        step.dest_pos, step.send_index = dest_pos.data_ptr(), send_index.data_ptr()
+        ops.ep_fused_forward(step, st["buf"], self.weights, st["seg2e"], st["y"], st["ws"], st["capacity"],
+                             st["flags"], send, st["cfg"])
         self._saved = {"recv": st["buf"], "seg": plan["segment_sizes"], "seg2e": st["seg2e"],
                        "dest_pos": dest_pos, "routing": routing, "capacity": st["capacity"]}
-        return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
+        return st["y"], plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
 
     def forward(self, x_tokens: torch.Tensor, routing: torch.Tensor, timed: bool = False):
         """Returns (y [rows_received, n], plan).  y's rows are ordered (source rank, local expert)."""

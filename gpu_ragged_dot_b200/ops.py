@@ -418,6 +418,23 @@ def gmm_ep_fused(recv: torch.Tensor, A: torch.Tensor, segment_sizes: torch.Tenso
     return out
 
 
+def ep_fused_forward(step: "_lib.EpStep", recv: torch.Tensor, A: torch.Tensor, group_to_weight: torch.Tensor,
+                     out: torch.Tensor, workspace: torch.Tensor, capacity_rows: int, flags: torch.Tensor,
+                     send: "_lib.EpSend", cfg: Optional[_lib.TileCfg] = None) -> torch.Tensor:
+    """``rd_ep_fused_forward``: count + share, plan, assign, own-row copy and the fused send + GEMM
+    kernel of one expert-parallel forward step, enqueued by one C call."""
+    lib = _lib.load()
+    k, n = recv.shape[1], A.shape[-1]
+    with torch.cuda.device(recv.device):
+        rc = lib.rd_ep_fused_forward(
+            ctypes.byref(step), recv.data_ptr(), A.data_ptr(), A.shape[0], group_to_weight.data_ptr(),
+            out.data_ptr(), workspace.data_ptr(), workspace.numel(), int(capacity_rows), k, n,
+            _DTYPE_CODE[recv.dtype], _cfg_ptr(cfg), flags.data_ptr(), ctypes.byref(send), _stream_ptr(recv.device))
+    _lib.check(rc, "rd_ep_fused_forward")
+    _maybe_check_status(workspace, "rd_ep_fused_forward")
+    return out
+
+
 def tgmm_forward(
     x: torch.Tensor,
     y: torch.Tensor,

@@ -223,6 +223,39 @@ int rd_gmm_ep_fused(const void* x, const void* A, int num_weights, const int32_t
                     const int32_t* ready_flags, int groups_per_flag, int epoch, const rd_ep_send* send,
                     void* stream);
 
+/* One call for the whole fused expert-parallel forward step (no counterpart in the reference):
+ * rd_ep_count_share, rd_ep_plan_ring_when_counted, rd_ep_assign, rd_ep_send_list (phase 0, the
+ * rank's own rows) and rd_gmm_ep_fused, enqueued back to back on `stream` with exactly the
+ * arguments those entry points take.  It exists because a decode-sized step is bound by the
+ * host's cost of five separate calls, not by the GPU.  world == 1 is not served (nothing to
+ * exchange: use rd_ep_count / rd_ep_plan_ring).  Returns the first non-zero status. */
+typedef struct rd_ep_step {
+  const int32_t* routing;        /* [tokens, top_k] expert ids */
+  int32_t tokens, top_k, num_experts, epoch;
+  int32_t* counts_scratch;       /* rd_ep_count_share */
+  int32_t* ticket;
+  const uint64_t* peer_counts;   /* this epoch's table on every rank */
+  const uint64_t* peer_count_flags;
+  const int32_t* counts_all;     /* this rank's own copy of this epoch's table, [world, num_experts] */
+  const int32_t* count_flags;    /* this rank's count flags */
+  int32_t* dest_offset;          /* rd_ep_plan_ring outputs */
+  int32_t* segment_sizes;
+  int32_t* fill;
+  int32_t* totals;
+  int32_t* send_start;
+  int32_t* list_fill;
+  int32_t* plan_status;          /* status word of the plan kernel's wait */
+  int32_t* dest_pos;             /* rd_ep_assign outputs, [tokens * top_k] */
+  int32_t* send_index;
+  void* own_buffer;              /* this rank's receive buffer (destination of phase 0) */
+  int32_t* own_ready_flag;       /* word 0 of this rank's ready flags */
+  int32_t wait_limit_ms;
+} rd_ep_step;
+int rd_ep_fused_forward(const rd_ep_step* step, const void* recv, const void* A, int num_weights,
+                        const int32_t* group_to_weight, void* y, void* workspace, size_t workspace_bytes,
+                        int capacity_rows, int k, int n, int dtype, const rd_tile_cfg* cfg,
+                        const int32_t* ready_flags, const rd_ep_send* send, void* stream);
+
 /* Transposed grouped GEMM out[g,k,n] = x_g^T . dout_g; replaces _gpu_tgmm_fwd +
  * _gpu_tgmm_kernel (gpu_ragged_dot.py:231-342), the drhs half of the backward pass
  * (gpu_ragged_dot.py:401).  Empty groups produce zero blocks. */
