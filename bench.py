@@ -71,7 +71,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index = index
         self.period = period_s
         self.samples = []

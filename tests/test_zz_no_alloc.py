@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from gpu_ragged_dot_b200 import _lib, ops
+from oracle import ragged_dot_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -60,12 +61,14 @@ def test_static_scratch_matches_workspace_variant_twice():
     gs = torch.tensor([100, 0, 257, 1, 128, 64, 0, 300, 90, 10, 200, 100], dtype=torch.int32, device=dev)
     got, want = _both(lib, x, A, gs, trans_rhs=False)
     _check(got, want, "first call")
+    _check(got, oracle.ragged_dot(x, A, gs).to(dev), "first call vs the CPU oracle")
     assert float(got[int(gs.sum()):].float().abs().max()) == 0.0
     # second call, straight after: fewer groups, fewer rows, transposed weights
     x2, A2 = _inputs(2, 300, 128, 264, 3, dev)
     gs2 = torch.tensor([37, 0, 200], dtype=torch.int32, device=dev)
     got2, want2 = _both(lib, x2, A2.transpose(1, 2).contiguous(), gs2, trans_rhs=True)
     _check(got2, want2, "second call")
+    _check(got2, oracle.ragged_dot(x2, A2, gs2).to(dev), "second call vs the CPU oracle")
     assert float(got2[237:].float().abs().max()) == 0.0
 
 
