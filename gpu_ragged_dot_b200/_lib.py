@@ -21,6 +21,7 @@ RD_DTYPE_F16 = 0
 RD_DTYPE_BF16 = 1
 RD_DTYPE_F32 = 2
 RD_CFG_NO_ZERO_TAIL = 1
+RD_CFG_GROUP_BY_WEIGHT = 2
 
 # Every symbol include/ragged_dot_b200.h declares, with its ctypes signature.
 _c_int = ctypes.c_int

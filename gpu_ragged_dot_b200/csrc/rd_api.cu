@@ -123,7 +123,17 @@ int bind_workspace(void* ws, size_t ws_bytes, int m, int g, Workspace* out) {
 }
 
 void launch_internal_metadata(const int32_t* group_sizes, const int32_t* group_to_weight, int g,
-                              int m, int tile_m, const Workspace& w, cudaStream_t stream) {
+                              int m, int tile_m, const Workspace& w, cudaStream_t stream,
+                              bool by_weight = false) {
+  if (by_weight && group_to_weight != nullptr && m > 0) {
+    // the two reference-shaped arrays are not needed by the kernels: their space (U >= g + 1
+    // words each) serves as the scratch of the visiting order
+    rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, stream>>>(
+        group_sizes, g, m, tile_m, w.layout.max_tiles, w.group_offsets(), nullptr, nullptr, w.totals(),
+        w.tile_prefix(), w.totals() + 1, w.status(), w.tile_rec(), group_to_weight, w.tile2group(),
+        w.tile2idx());
+    return;
+  }
   rd::group_metadata_kernel<<<1, rd::kMetaThreads, 0, stream>>>(
       group_sizes, g, m, tile_m, w.layout.max_tiles, w.group_offsets(), w.tile2group(),
       w.tile2idx(), w.totals(), w.tile_prefix(), w.totals() + 1, w.status(), w.tile_rec(),
@@ -390,7 +400,8 @@ static int gmm_impl(const void* x, const void* A, const int32_t* group_sizes,
   // which the driver's tensor-map encoder needs (threads such as torch's autograd workers
   // arrive here without one).
   launch_internal_metadata(group_sizes, group_to_weight, g, m,
-                           two_half ? rd::kG2TileRows : rd::kTileM * cta_group, w, stream);
+                           two_half ? rd::kG2TileRows : rd::kTileM * cta_group, w, stream,
+                           cfg != nullptr && (cfg->flags & RD_CFG_GROUP_BY_WEIGHT) != 0);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
   CUtensorMap ta, tb;

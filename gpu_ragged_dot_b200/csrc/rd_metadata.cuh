@@ -58,6 +58,11 @@ __device__ __forceinline__ int warp_inclusive_scan(int v, int lane) {
 //   row_total[1]       min(sum(group_sizes), m) (extra)
 //   status[1]          device status word, reset to 0 here at the start of every call (extra)
 //   tile_rec[U]        one TileRecord per live row tile; needs tile_prefix and group_offsets (extra)
+//   visit_group[g], visit_prefix[g+1]  scratch; when given (with group_to_weight and tile_rec), the
+//                      tile records are laid out in VISITING order = groups sorted by the weight
+//                      they use (stable), so that groups sharing a weight matrix are multiplied
+//                      one after the other and the matrix leaves HBM once.  Rows, offsets and
+//                      results are unchanged; only the order in which tiles are taken differs.
 __global__ void __launch_bounds__(kMetaThreads, 1)
 group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int tile_m,
                       int max_tiles, int32_t* group_offsets,
@@ -65,7 +70,8 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
                       int32_t* __restrict__ total_tiles, int32_t* tile_prefix,
                       int32_t* __restrict__ row_total, int32_t* __restrict__ status,
                       TileRecord* __restrict__ tile_rec,
-                      const int32_t* __restrict__ group_to_weight) {
+                      const int32_t* __restrict__ group_to_weight,
+                      int32_t* visit_group = nullptr, int32_t* visit_prefix = nullptr) {
   __shared__ int warp_rows[32];
   __shared__ int warp_tiles[32];
   __shared__ int carry_rows;
@@ -146,12 +152,47 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
   }
   if (tile2group == nullptr && tile2idx == nullptr && tile_rec == nullptr) return;
 
+  const bool by_weight = visit_group != nullptr && visit_prefix != nullptr && group_to_weight != nullptr &&
+                         tile_rec != nullptr && tile_prefix != nullptr;
+  if (by_weight) {
+    __syncthreads();
+    for (int gi = tid; gi < g; gi += kMetaThreads) {  // rank of the group: by weight, then by index
+      const int w = group_to_weight[gi];
+      int rank = 0;
+      for (int j = 0; j < g; ++j) {
+        const int wj = group_to_weight[j];
+        rank += (wj < w || (wj == w && j < gi)) ? 1 : 0;
+      }
+      visit_group[rank] = gi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int acc = 0;
+      for (int v = 0; v < g; ++v) {
+        const int gi = visit_group[v];
+        visit_prefix[v] = acc;
+        acc += tile_prefix[gi + 1] - tile_prefix[gi];
+      }
+      visit_prefix[g] = acc;
+    }
+  }
+
   // Pass 2: every row tile finds its group by binary search over the per-group tile prefix
   // (recomputed from group_sizes when the caller did not ask for tile_prefix).
   __syncthreads();
   for (int u = tid; u < max_tiles; u += kMetaThreads) {
     int gi = 0, idx = 0;
-    if (u < live_tiles) {
+    int visit_base = -1;
+    if (u < live_tiles && by_weight) {
+      int lo = 0, hi = g;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (visit_prefix[mid + 1] > u) hi = mid; else lo = mid + 1;
+      }
+      gi = visit_group[lo];
+      visit_base = visit_prefix[lo];
+      idx = u - visit_base;
+    } else if (u < live_tiles) {
       if (tile_prefix) {
         int lo = 0, hi = g;  // first index with tile_prefix[index] > u lies in (lo, hi]
         while (lo < hi) {
@@ -186,8 +227,8 @@ group_metadata_kernel(const int32_t* __restrict__ group_sizes, int g, int m, int
       rows = rows < 0 ? 0 : rows;
       const int left = m - r.group_offset;
       r.group_size = left <= 0 ? 0 : (rows < left ? rows : left);
-      r.tile_base = tile_prefix[gi];
-      r.tiles = tile_prefix[gi + 1] - r.tile_base;
+      r.tile_base = by_weight ? visit_base : tile_prefix[gi];
+      r.tiles = tile_prefix[gi + 1] - tile_prefix[gi];
       r.idx = idx;
       r.pad = 0;
       tile_rec[u] = r;

@@ -204,7 +204,7 @@ class ExpertParallelRaggedDot:
             st["hdl"].barrier(channel=0)  # every rank's rows have landed everywhere
         if timed:
             ev[2].record()
-        cfg = _lib.TileCfg(0, 0, 0, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        cfg = _lib.TileCfg(0, 0, 0, 0, _lib.RD_CFG_NO_ZERO_TAIL | self._order_flag(tokens, top_k))
         y = ops.gmm_forward(st["buf"], self.weights, seg_sizes, group_to_weight=st["seg2e"], cfg=cfg,
                             out=st["y"])
         if timed:
@@ -320,7 +320,7 @@ class ExpertParallelRaggedDot:
             ev[4].record()
             ev[2].record()
         send = self._send_struct(st, x_tokens, send_index, dest_pos, plan, top_k)
-        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        cfg = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL | self._order_flag(tokens, top_k))
         y = ops.gmm_ep_fused(st["buf"], self.weights, plan["segment_sizes"], st["seg2e"], st["y"], st["ws"],
                              st["flags"], self.local_experts, epoch, send, cfg=cfg)
         if timed:
@@ -329,6 +329,15 @@ class ExpertParallelRaggedDot:
         self._saved = {"recv": st["buf"], "seg": plan["segment_sizes"], "seg2e": st["seg2e"],
                        "dest_pos": dest_pos, "routing": routing, "capacity": st["capacity"]}
         return y, plan["segment_sizes"], dest_pos.view(tokens, top_k), plan["totals"]
+
+    def _order_flag(self, tokens: int, top_k: int) -> int:
+        """Small steps (a decode batch: a few rows per expert and source) are bound by the weights'
+        way out of HBM, and an expert's W segments lie far apart in the receive buffer: take the
+        segments expert by expert (RD_CFG_GROUP_BY_WEIGHT) so each weight matrix is read once.
+        Large steps keep the row order, which is the order the rows arrive in."""
+        from . import _lib
+
+        return _lib.RD_CFG_GROUP_BY_WEIGHT if tokens * top_k <= 4096 else 0
 
     def _send_struct(self, st, x_tokens, send_index, dest_pos, plan, top_k):
         from . import _lib
@@ -345,7 +354,10 @@ class ExpertParallelRaggedDot:
         send.phase_done = plan["phase_done"].data_ptr()
         send.row_bytes, send.top_k = x_tokens.shape[1] * x_tokens.element_size(), top_k
         send.world, send.rank, send.capacity_rows = self.world, self.rank, st["capacity"]
-        send.sender_ctas = self.sender_ctas if self.world > 1 else 1
+        # a decode-sized step has a few hundred rows to send: four sender CTAs (60 copying warps) are
+        # plenty, and the multiplying CTAs are what such a step is short of
+        small = x_tokens.shape[0] * top_k <= 4096
+        send.sender_ctas = (min(self.sender_ctas, 4) if small else self.sender_ctas) if self.world > 1 else 1
         return send
 
     def _forward_fused_one_call(self, st, x_tokens, routing, tokens, top_k, epoch):
@@ -377,6 +389,7 @@ class ExpertParallelRaggedDot:
             step.wait_limit_ms = 0
             st["step"] = step
             st["cfg"] = _lib.TileCfg(0, 0, 1, 0, _lib.RD_CFG_NO_ZERO_TAIL)
+        st["cfg"].flags = _lib.RD_CFG_NO_ZERO_TAIL | self._order_flag(tokens, top_k)
         step = st["step"]
         step.routing, step.tokens, step.top_k, step.epoch = routing.data_ptr(), tokens, top_k, epoch
         step.peer_counts = sh["peer_counts"][par].data_ptr()

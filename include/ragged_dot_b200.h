@@ -62,11 +62,17 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1, RD_DTYPE_F32 = 2 };
  *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice.
  *   flags     : RD_CFG_NO_ZERO_TAIL = rd_gmm leaves the rows past sum(group_sizes) unwritten
  *               (for callers that pass an upper bound as m and never read those rows).
+ *               RD_CFG_GROUP_BY_WEIGHT = rd_gmm_indexed takes the groups in the order of the weight
+ *               matrix they use (stable) instead of in row order, so groups that share a matrix
+ *               are multiplied one after the other and it leaves HBM once: for many small
+ *               groups over few matrices (the decode-sized expert-parallel step).  Results are
+ *               the same; with ready flags a late group may be waited for early.
  *   wait_limit_ms : how long a wait inside a kernel (on a pipeline barrier, on a ready flag of
  *               rd_gmm_indexed_when_ready) may last before the kernel gives up, records
  *               RD_ERR_DEVICE_WAIT in the status word and returns; 0 = the environment variable
  *               RD_WAIT_LIMIT_MS if set, else 2000. */
 #define RD_CFG_NO_ZERO_TAIL 1
+#define RD_CFG_GROUP_BY_WEIGHT 2
 typedef struct rd_tile_cfg {
   int32_t tile_n;
   int32_t max_ctas;

@@ -1068,3 +1068,37 @@ def test_ragged_dot_general_batched_and_ragged_batch():
         close(got, want, f"general: ragged batch {sizes}")
         live = min(sum(sizes), b)
         assert float(got[live:].float().abs().max() if live < b else 0.0) == 0.0
+
+
+def test_group_by_weight_order_gives_identical_results():
+    """RD_CFG_GROUP_BY_WEIGHT only changes the order in which tiles are taken: many small segments
+    over few weight matrices (the decode-sized expert-parallel layout), with empty segments, a
+    segment over one tile, and both tile kernels; bit-identical output, oracle-checked."""
+    experts, world, k, n = 6, 5, 136, 520
+    rng = np.random.default_rng(17)
+    sizes = rng.integers(0, 9, size=experts * world).astype(np.int32)
+    sizes[3] = 0
+    sizes[7] = 300
+    m = int(sizes.sum()) + 40
+    x, A, _ = _inputs(19, m, k, n, experts)
+    seg2e = torch.arange(experts, dtype=torch.int32).repeat(world)
+    gs = torch.from_numpy(sizes)
+    want = oracle.ragged_dot(x, A[seg2e.long()], gs)
+    xd, Ad, gd, sd = _to_dev(x, A, gs, seg2e)
+    for tile_m in (128, 256):
+        outs = []
+        for flags in (0, _lib.RD_CFG_GROUP_BY_WEIGHT):
+            ws = ops._workspace(m, len(sizes), DEV)
+            y = ops.gmm_forward(xd, Ad, gd, group_to_weight=sd, cfg=_lib.TileCfg(256, 0, 1, tile_m, flags), workspace=ws)
+            assert ops.device_status(ws) == 0
+            outs.append(y)
+        assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+        _assert_close(outs[1].cpu(), want, f"group-by-weight order, tile_m {tile_m}")
+        assert float(outs[1][int(sizes.sum()):].float().abs().max()) == 0.0
+    # with ready flags too (the flag of a later segment is waited for early: it is already up)
+    flags_t = torch.full((8,), 2, dtype=torch.int32, device=DEV)
+    ws = ops._workspace(m, len(sizes), DEV)
+    y = ops.gmm_forward(xd, Ad, gd, group_to_weight=sd, workspace=ws, ready=(flags_t, experts, 2),
+                        cfg=_lib.TileCfg(256, 0, 1, 128, _lib.RD_CFG_GROUP_BY_WEIGHT))
+    assert ops.device_status(ws) == 0
+    _assert_close(y.cpu(), want, "group-by-weight order with ready flags")
