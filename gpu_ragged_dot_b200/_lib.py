@@ -81,6 +81,12 @@ SIGNATURES = {
         + [_c_int] * 5
         + [ctypes.POINTER(TileCfg), _c_void_p],
     ),
+    "rd_gmm_fp8": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]
+        + [_c_int] * 4
+        + [ctypes.POINTER(TileCfg), _c_void_p],
+    ),
     "rd_tgmm_strided": (
         _c_int,
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t]

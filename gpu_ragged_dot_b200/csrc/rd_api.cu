@@ -150,13 +150,13 @@ int choose_tile_n(long long /*row_tiles*/, int n, int /*sms*/) {
   return 256;
 }
 
-template <int BN, bool kBKMajor, bool kTgmm, int kCtas, bool kSeg = false>
+template <int BN, bool kBKMajor, bool kTgmm, int kCtas, bool kSeg = false, bool kFp8 = false>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
                 const GemmArgs& args, int ctas, cudaStream_t stream) {
   constexpr int kStageBytes = rd::stage_bytes<BN, kCtas>();
   constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   constexpr int kSmem = kStages * kStageBytes + rd::kOutStagingBytes + 1024;
-  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm, kCtas, kSeg>;
+  auto kernel = rd::ragged_gemm_kernel<BN, kBKMajor, kStages, kTgmm, kCtas, kSeg, kFp8>;
   // The attribute is per device; setting it again is cheap, so do it on every call rather
   // than track which devices have seen it.
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
@@ -1047,6 +1047,75 @@ int rd_ep_fused_forward(const rd_ep_step* st, const void* recv, const void* A, i
   return rd_gmm_ep_fused(recv, A, num_weights, st->segment_sizes, group_to_weight, y, workspace,
                          workspace_bytes, capacity_rows, k, n, world * local, 0, dtype, cfg, ready_flags, local,
                          st->epoch, send, stream);
+}
+
+int rd_gmm_fp8(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+               const int32_t* group_to_weight, const float* weight_scale, void* y, void* workspace,
+               size_t workspace_bytes, int m, int k, int n, int g, const rd_tile_cfg* cfg, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // rows of k one-byte elements and of n two-byte results must be multiples of 16 bytes
+  if (m < 0 || k < 0 || n < 0 || g < 0 || num_weights < 0 || (k & 15) || (n & 7)) return RD_ERR_BAD_SHAPE;
+  if (group_to_weight == nullptr && num_weights != g) return RD_ERR_BAD_SHAPE;
+  if (m == 0 || n == 0) return RD_OK;
+  if (!aligned16(y)) return RD_ERR_BAD_POINTER;
+  if (g == 0 || k == 0 || num_weights == 0) {
+    cudaMemsetAsync(y, 0, static_cast<size_t>(m) * n * 2, stream);
+    return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+  }
+  if (!aligned16(x) || !aligned16(A) || group_sizes == nullptr) return RD_ERR_BAD_POINTER;
+  Workspace w;
+  int rc = bind_workspace(workspace, workspace_bytes, m, g, &w);
+  if (rc != RD_OK) return rc;
+  int bn = cfg && cfg->tile_n ? cfg->tile_n : choose_tile_n(0, n, 0);
+  if (bn != 64 && bn != 128 && bn != 256) return RD_ERR_BAD_CONFIG;
+  if (cfg && (cfg->cta_group == 2 || cfg->tile_m == 256)) return RD_ERR_BAD_CONFIG;  // 128-row tiles only
+
+  launch_internal_metadata(group_sizes, group_to_weight, g, m, rd::kTileM, w, stream,
+                           cfg != nullptr && (cfg->flags & RD_CFG_GROUP_BY_WEIGHT) != 0);
+  if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
+
+  // Both operands are K-major, so a row of k one-byte elements is described to TMA as k/2
+  // two-byte elements: the bytes that land in shared memory are the same.
+  const int k2 = k / 2;
+  CUtensorMap ta, tb, tout;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k2), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {64, rd::kTileM};
+    rc = encode_map(&ta, x, RD_DTYPE_BF16, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k2), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_weights)};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(bn), 1};
+    rc = encode_map(&tb, A, RD_DTYPE_BF16, 3, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
+    const uint32_t box[2] = {64, 32};
+    rc = encode_map(&tout, y, RD_DTYPE_BF16, 2, dims, box);
+    if (rc != RD_OK) return rc;
+  }
+  GemmArgs args = {};
+  args.m = m; args.k = k2; args.n = n; args.g = g;
+  args.n_tiles = (n + bn - 1) / bn;
+  args.max_m_tiles = w.layout.max_tiles;
+  args.ab_format = RD_DTYPE_BF16;  // type of the output
+  args.wait_limit_us = wait_limit_us(cfg);
+  args.weight_scale = weight_scale;
+  args.zero_tail = (cfg && (cfg->flags & RD_CFG_NO_ZERO_TAIL)) ? 0 : 1;
+  args.group_sizes = group_sizes;
+  args.group_offsets = w.group_offsets();
+  args.tile_rec = w.tile_rec();
+  args.totals = w.totals();
+  args.status = w.status();
+  args.out = y;
+  args.groups_per_flag = 1;
+  const int ctas = pick_ctas(cfg);
+  if (bn == 256) return launch_gemm<256, true, false, 1, false, true>(ta, tb, tout, args, ctas, stream);
+  if (bn == 128) return launch_gemm<128, true, false, 1, false, true>(ta, tb, tout, args, ctas, stream);
+  return launch_gemm<64, true, false, 1, false, true>(ta, tb, tout, args, ctas, stream);
 }
 
 int rd_device_status(const void* workspace, void* stream) {

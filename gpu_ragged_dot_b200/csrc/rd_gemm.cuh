@@ -68,6 +68,7 @@ struct GemmArgs {
   int ab_format;    // 0 = fp16, 1 = bf16
   int zero_tail;    // gmm: write zeros to the rows past sum(group_sizes)
   uint32_t wait_limit_us;  // how long a bounded wait inside the kernel may last (microseconds)
+  const float* weight_scale;  // 8-bit inputs: scale of weight matrix w, applied to the accumulator (null: 1)
   const int32_t* group_sizes;
   const int32_t* group_offsets;
   const TileRecord* tile_rec;  // gmm: one record per live row tile (of 128 * kCtas rows)
@@ -273,7 +274,7 @@ constexpr int stage_bytes() {
 //                  kBKMajor (trans_rhs: W[g] is [n,k]) else MN-major (W[g] is [k,n]).
 // kTgmm == true  : tgmm.  A operand = x^T tile (MN-major), B operand = dout tile (MN-major);
 //                  kBKMajor must be false.
-template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas, bool kSeg = false>
+template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas, bool kSeg = false, bool kFp8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b,
@@ -282,6 +283,11 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
   static_assert(kCtas == 1 || (kCtas == 2 && BN >= 128), "a CTA pair needs BN >= 128");
   static_assert(!kSeg || (kTgmm && kCtas == 1), "strided segments: tgmm on one CTA per tile");
+  // 8-bit inputs (e4m3): both operands K-major (x[m,k], W[g,n,k]), so the tiles are byte for byte
+  // those of a 16-bit problem with k/2 elements per row (which is what the tensor maps and
+  // GemmArgs::k describe); only the MMA kind differs, 32 elements = 32 bytes per instruction, and
+  // the epilogue multiplies by the weight matrix's scale.  Output is bf16.
+  static_assert(!kFp8 || (kBKMajor && !kTgmm && kCtas == 1), "8-bit inputs: gmm with K-major weights, one CTA");
   constexpr bool kPair = kCtas == 2;
   constexpr int kBCols = BN / kCtas;  // B-operand columns this CTA loads
   constexpr uint32_t kABytes = kTileM * kTileK * 2;
@@ -425,11 +431,11 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // In a pair only the leader issues MMAs.  The peer's warp 1 has nothing to do except for
     // the tgmm stages whose tail rows it must clear in its own shared memory.
     const uint32_t idesc_full =
-        make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
+        make_idesc_f16(kFp8 ? 0 : p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
     // A gmm row tile with at most 64 rows (the short last tile of a group, a small expert) is
     // multiplied with M = 64: half the tensor-core time for a tile that is mostly padding.
     // Its accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory.
-    const uint32_t idesc_half = make_idesc_f16(p.ab_format, 0, kBKMajor ? 0 : 1, 64, BN);
+    const uint32_t idesc_half = make_idesc_f16(kFp8 ? 0 : p.ab_format, 0, kBKMajor ? 0 : 1, 64, BN);
     // Stage-0 operand descriptors; later stages / k-steps only add to the 16-byte-unit address.
     constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;       // A: MN-major (tgmm) or K-major
     constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;    // B: K-major or MN-major
@@ -523,16 +529,16 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
           if (kTgmm && n_mma < kTileK / kUmmaK) {
             for (int kk = 0; kk < n_mma; ++kk) {
-              umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+              umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
                               make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
                               (kb > 0 || kk > 0) ? 1u : 0u);
             }
           } else {
-            umma_f16<kCtas>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
+            umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
                             kb > 0 ? 1u : 0u);
 #pragma unroll
             for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
-              umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+              umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
                               make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
             }
           }
@@ -627,6 +633,11 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else {
 #pragma unroll
           for (int j = 0; j < 64; ++j) v[j] = 0u;
+        }
+        if constexpr (kFp8) {  // dequantise: one scale per weight matrix (1 when none is given)
+          const float sc = p.weight_scale != nullptr ? p.weight_scale[t.weight] : 1.0f;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * sc);
         }
         if (c == n_chunks - 1) {
           // Everything this warp needs from the accumulator is in registers: hand it back.

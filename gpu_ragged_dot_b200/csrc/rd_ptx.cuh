@@ -349,6 +349,30 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         : "memory");
 }
 
+// Same for 8-bit floating-point inputs (kind::f8f6f4; K = 32 per instruction), one CTA.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 16-bit or 8-bit inputs, chosen at compile time (the issue path stays free of branches).
+template <int kCtaGroup, bool kFp8>
+__device__ __forceinline__ void umma_ab(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  if constexpr (kFp8) {
+    umma_f8(tmem_d, adesc, bdesc, idesc, accumulate);
+  } else {
+    umma_f16<kCtaGroup>(tmem_d, adesc, bdesc, idesc, accumulate);
+  }
+}
+
 // Make `bar` observe completion of every tcgen05.mma this thread issued so far.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -409,6 +433,7 @@ __device__ __forceinline__ uint64_t make_desc64(uint32_t lo, uint32_t hi) {
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B both `ab_format`
 // (0 = fp16, 1 = bf16); *_mn_major = 1 when the operand's M/N index is the contiguous one.
+// kind::f8f6f4 uses the same fields with its own format codes (0 = e4m3, 1 = e5m2).
 __host__ __device__ constexpr uint32_t make_idesc_f16(int ab_format, int a_mn_major,
                                                       int b_mn_major, int mma_m, int mma_n) {
   return (1u << 4) | (static_cast<uint32_t>(ab_format) << 7) |

@@ -245,6 +245,47 @@ def gmm_forward(
     return y
 
 
+def gmm_fp8_forward(x: torch.Tensor, A: torch.Tensor, group_sizes: torch.Tensor,
+                    weight_scale: Optional[torch.Tensor] = None, group_to_weight: Optional[torch.Tensor] = None,
+                    cfg: Optional[_lib.TileCfg] = None, out: Optional[torch.Tensor] = None,
+                    workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``rd_gmm_fp8``: ragged x[m,k] . A[w]^T for e4m3 operands (``torch.float8_e4m3fn``), A stored
+    ``[num_weights, n, k]``; fp32 accumulation, times ``weight_scale[w]`` (float32, optional), bf16
+    result.  Forward only (an inference path): there is no 8-bit tgmm."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    _require_cuda(A, "A")
+    f8 = torch.float8_e4m3fn
+    if x.dtype != f8 or A.dtype != f8:
+        raise NotImplementedError(f"inputs must both be float8_e4m3fn, got {x.dtype} / {A.dtype}")
+    assert x.dim() == 2 and A.dim() == 3 and A.shape[2] == x.shape[1], "x [m,k], A [num_weights,n,k]"
+    gs = _as_i32(group_sizes)
+    g, (m, k), n = gs.numel(), x.shape, A.shape[1]
+    if group_to_weight is None:
+        assert A.shape[0] == g, f"{A.shape[0]=} != {g=}"
+    else:
+        group_to_weight = _as_i32(group_to_weight)
+    if k % 16 or n % 8:
+        raise NotImplementedError("8-bit inputs: k must be a multiple of 16 and n of 8")
+    x, A = _dense16(x), _dense16(A)
+    if weight_scale is not None:
+        weight_scale = weight_scale.to(device=x.device, dtype=torch.float32).contiguous()
+        assert weight_scale.numel() == A.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.is_contiguous()
+    ws = workspace if workspace is not None else _workspace(m, g, x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.rd_gmm_fp8(x.data_ptr(), A.data_ptr(), A.shape[0], gs.data_ptr(),
+                            group_to_weight.data_ptr() if group_to_weight is not None else None,
+                            weight_scale.data_ptr() if weight_scale is not None else None,
+                            out.data_ptr(), ws.data_ptr(), ws.numel(), m, k, n, g, _cfg_ptr(cfg),
+                            _stream_ptr(x.device))
+    _lib.check(rc, "rd_gmm_fp8")
+    _maybe_check_status(ws, "rd_gmm_fp8")
+    return out
+
+
 def gather_rows(src: torch.Tensor, row_index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """dst[i] = src[row_index[i]] through ``rd_gather_rows`` (rows must be a multiple of 16 bytes)."""
     lib = _lib.load()

@@ -113,6 +113,16 @@ int rd_gmm_indexed(const void* x, const void* A, int num_weights, const int32_t*
                    int m, int k, int n, int g, int trans_rhs, int dtype, const rd_tile_cfg* cfg,
                    void* stream);
 
+/* rd_gmm_indexed for 8-bit floating-point inputs (e4m3), a Blackwell extension with no counterpart
+ * in the reference: x [m, k] and A [num_weights, n, k] (the trans_rhs layout: both operands
+ * contiguous along k) hold one-byte e4m3 values, products are exact, accumulation is fp32, and
+ * y [m, n] = weight_scale[w] * (x_rows . A[w]^T) is written as bf16 (w = group_to_weight[i], or i
+ * when group_to_weight is NULL and num_weights == g; weight_scale NULL = 1; a scale for x is a
+ * factor the caller folds into weight_scale).  k must be a multiple of 16, n of 8.  128-row tiles. */
+int rd_gmm_fp8(const void* x, const void* A, int num_weights, const int32_t* group_sizes,
+               const int32_t* group_to_weight, const float* weight_scale, void* y, void* workspace,
+               size_t workspace_bytes, int m, int k, int n, int g, const rd_tile_cfg* cfg, void* stream);
+
 /* dst[i, :] = src[row_index[i], :] for rows of row_bytes (a multiple of 16) bytes: the permute
  * that precedes ragged_dot in an MoE layer (rows replicated per routed expert, sorted by
  * expert).  The reference leaves this step to its caller.  An index outside [0, rows_in)

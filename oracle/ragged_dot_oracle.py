@@ -161,6 +161,23 @@ def ragged_dot_permuted(x, A, group_sizes, in_rows=None, out_rows=None, y_rows=N
     return y
 
 
+def ragged_dot_fp8(x: torch.Tensor, A: torch.Tensor, group_sizes, weight_scale=None,
+                   group_to_weight=None) -> torch.Tensor:
+    """The 8-bit extension (no counterpart in the reference): e4m3 operands, A stored [w, n, k];
+    y[rows of group i] = bf16(scale[w] * (f32(x[rows]) @ f32(A[w])^T)), w = group_to_weight[i] or i.
+    Products of e4m3 values are exact in fp32, so this is the same arithmetic as the kernel's."""
+    m, k = x.shape
+    n = A.shape[1]
+    xf = _f32(x)
+    y = torch.zeros((m, n), dtype=torch.float32)
+    for gi, lo, hi in _group_ranges(group_sizes, m):
+        if hi > lo:
+            w = int(group_to_weight[gi]) if group_to_weight is not None else gi
+            sc = float(weight_scale[w]) if weight_scale is not None else 1.0
+            y[lo:hi] = (xf[lo:hi] @ _f32(A[w]).T) * sc
+    return y.to(torch.bfloat16)
+
+
 def ragged_dot_general_batched(mode: str, lhs: torch.Tensor, rhs: torch.Tensor, group_sizes) -> torch.Tensor:
     """jax.lax.ragged_dot_general with one batch dimension in canonical layouts (the dimension
     numbers of tests.py:31-36 with a leading batch dimension added):

@@ -93,6 +93,15 @@ def test_argument_validation_happens_on_the_host(lib):
     assert pull(routing=None) == 3
     assert pull(out=a16 + 4) == 3
     assert pull(tokens=0) == 0
+    f8 = lambda **kw: lib.rd_gmm_fp8(
+        kw.get("x", a16), a16, kw.get("nw", 2), a16, kw.get("g2w", None), None, kw.get("y", a16), a16,
+        kw.get("ws_bytes", 1 << 20), kw.get("m", 128), kw.get("k", 64), kw.get("n", 64), kw.get("g", 2), cfg, None)
+    assert f8(k=24) == 1      # rows of k bytes must be multiples of 16 bytes
+    assert f8(n=20) == 1
+    assert f8(nw=3) == 1      # without an index there is one weight matrix per group
+    assert f8(x=a16 + 4) == 3
+    assert f8(ws_bytes=8) == 4
+    assert f8(m=0) == 0
     assert lib.rd_metadata(a16, -1, 16, 8, None, None, None, None, None) == 1
     assert lib.rd_metadata(a16, 4, 16, 0, None, None, None, None, None) == 1
     assert lib.rd_device_status(None, None) == 3

@@ -1102,3 +1102,48 @@ def test_group_by_weight_order_gives_identical_results():
                         cfg=_lib.TileCfg(256, 0, 1, 128, _lib.RD_CFG_GROUP_BY_WEIGHT))
     assert ops.device_status(ws) == 0
     _assert_close(y.cpu(), want, "group-by-weight order with ready flags")
+
+
+# ------------------------------------------------------------------ 8-bit (e4m3) inputs
+@pytest.mark.parametrize("m,k,n,tile_n", [(700, 256, 520, 0), (700, 144, 72, 0), (300, 128, 136, 128),
+                                           (300, 1040, 264, 64), (1, 16, 8, 0)])
+def test_gmm_fp8_matches_oracle(m, k, n, tile_n):
+    """rd_gmm_fp8: e4m3 x [m,k] and A [g,n,k], fp32 accumulation, per-weight scale, bf16 out; every
+    tile width, k not a multiple of the 128-byte stage, empty groups, tiles of at most 64 rows,
+    the zero tail."""
+    g = 5
+    rng = np.random.default_rng(7)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.float8_e4m3fn)
+    A = torch.from_numpy(rng.standard_normal((g, n, k)).astype(np.float32)).to(torch.float8_e4m3fn)
+    scale = torch.tensor([0.5, 2.0, 1.0, 0.03125, 3.0], dtype=torch.float32) / k ** 0.5
+    sizes = [m // 3, 0, m // 2, 0, max(m - m // 3 - m // 2 - 7, 0)]
+    gs = torch.tensor(sizes, dtype=torch.int32)
+    cfg = _lib.TileCfg(tile_n, 0, 0, 0, 0) if tile_n else None
+    ws = ops._workspace(m, g, DEV)
+    y = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gmm_fp8_forward(x.to(DEV), A.to(DEV), gs.to(DEV), weight_scale=scale.to(DEV), cfg=cfg, out=y, workspace=ws)
+    assert ops.device_status(ws) == 0
+    want = oracle.ragged_dot_fp8(x, A, gs, scale)
+    _assert_close(y.cpu(), want, "gmm fp8")
+    total = int(gs.sum())
+    assert float(y[total:].float().abs().max() if total < m else 0.0) == 0.0
+    err = oracle.rel_l2_err(y.cpu(), want, axis=-1, mask=torch.arange(m) < total)
+    assert float(err.max()) < EPS_ROWS_BF16
+    # no scale, and segments sharing weights through an index
+    g2w = torch.tensor([2, 0, 2, 1, 0], dtype=torch.int32)
+    y2 = ops.gmm_fp8_forward(x.to(DEV), A[:3].contiguous().to(DEV), gs.to(DEV), group_to_weight=g2w.to(DEV))
+    want2 = oracle.ragged_dot_fp8(x, A[:3], gs, None, g2w)
+    ok, worst = oracle.allclose_report(y2.cpu(), want2, 2e-2, 2e-2 * max(float(want2.float().abs().max()), 1.0))
+    assert ok, f"gmm fp8 indexed, unscaled: worst ratio {worst:.3f}"
+
+
+def test_gmm_fp8_rejects_what_it_does_not_do():
+    x = torch.zeros(8, 32, dtype=torch.float8_e4m3fn, device=DEV)
+    A = torch.zeros(1, 8, 32, dtype=torch.float8_e4m3fn, device=DEV)
+    gs = torch.tensor([8], dtype=torch.int32, device=DEV)
+    with pytest.raises(NotImplementedError):
+        ops.gmm_fp8_forward(x.to(torch.bfloat16), A, gs)
+    with pytest.raises(NotImplementedError):
+        ops.gmm_fp8_forward(x[:, :24].contiguous(), A[:, :, :24].contiguous(), gs)  # k not a multiple of 16
+    with pytest.raises(_lib.RaggedDotError):
+        ops.gmm_fp8_forward(x, A, gs, cfg=_lib.TileCfg(256, 0, 2, 0, 0))  # no CTA pairs for 8-bit inputs
