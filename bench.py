@@ -617,7 +617,12 @@ def run_other_workloads(dev, peaks):
     ms = _time_ms(lambda: ops.gmm_forward(x, A, gs, out=y, workspace=ws), 30)
     out[s.name + "_fwd"] = entry(ms, 2.0 * s.m * s.k * s.n, 2.0 * (s.m * s.k + gplus * s.k * s.n + s.m * s.n))
     out[s.name + "_fwd"]["nonempty_groups"] = gplus
-    del x, A, y
+    # the same product with e4m3 operands (rd_gmm_fp8; weights stored [g, n, k]): half the weight bytes
+    f8 = torch.float8_e4m3fn
+    x8, A8 = x.to(f8), A.transpose(1, 2).contiguous().to(f8)
+    ms8 = _time_ms(lambda: ops.gmm_fp8_forward(x8, A8, gs, out=y, workspace=ws), 30)
+    out[s.name + "_fwd_e4m3"] = entry(ms8, 2.0 * s.m * s.k * s.n, 1.0 * (s.m * s.k + gplus * s.k * s.n) + 2.0 * s.m * s.n)
+    del x, A, y, x8, A8
     torch.cuda.empty_cache()
 
     # DeepSeek-V3 shaped: heavy-tailed groups, ~20 % empty

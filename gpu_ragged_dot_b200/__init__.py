@@ -13,6 +13,7 @@ from .ops import (  # noqa: F401
     RaggedDotSizes,
     gmm,
     gmm_forward,
+    gmm_fp8_forward,
     make_group_metadata,
     ragged_dot,
     ragged_dot_general,
@@ -22,5 +23,5 @@ from .ops import (  # noqa: F401
     trans_ragged_dot,
 )
 
-__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted", "HostRaggedDot",
+__all__ = ["gmm", "tgmm", "ragged_dot", "trans_ragged_dot", "ragged_dot_permuted", "HostRaggedDot", "gmm_fp8_forward",
            "ragged_dot_general", "RaggedDotDimensionNumbers"]
