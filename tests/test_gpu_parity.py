@@ -554,7 +554,7 @@ def test_ep_plan_and_dispatch_emulated_ranks(world):
         assert bool(torch.isnan(y[total:].float()).all()), "NO_ZERO_TAIL: rows past the total must stay untouched"
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_ep_ring_phases_emulated_ranks(world):
     """The ring-phased exchange with W ranks emulated on one GPU, everything on one stream so that
     no kernel ever waits for a later one: all ranks' send lists are copied first, phase by phase
@@ -652,7 +652,7 @@ def test_ep_assign_send_lists_and_fused_single_rank():
     _assert_close(yb.cpu()[pos[order]], ya.cpu(), "fused vs nccl path")
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ep_assign_send_lists_emulated_ranks(world):
     """rd_ep_plan_ring + rd_ep_assign for W emulated ranks: every phase's send list holds exactly the
     entries routed to rank + p, and positions at the owners are a permutation of each segment."""
@@ -888,7 +888,7 @@ def test_bounded_wait_expiry_is_reported_and_recoverable(tile_m, monkeypatch):
     _assert_close(y2.cpu(), oracle.ragged_dot(x, A[:1].expand(4, -1, -1), gs), "plain gmm after an expiry")
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_ep_combine_pull_emulated_ranks(world):
     """rd_ep_combine_pull with the W owners' gradient buffers all on this GPU: each token's row is
     the fp32 sum of its top_k rows at the recorded positions, rounded once."""
@@ -1147,3 +1147,39 @@ def test_gmm_fp8_rejects_what_it_does_not_do():
         ops.gmm_fp8_forward(x[:, :24].contiguous(), A[:, :, :24].contiguous(), gs)  # k not a multiple of 16
     with pytest.raises(_lib.RaggedDotError):
         ops.gmm_fp8_forward(x, A, gs, cfg=_lib.TileCfg(256, 0, 2, 0, 0))  # no CTA pairs for 8-bit inputs
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_count_share_emulated_ranks(world):
+    """rd_ep_count_share + rd_ep_plan_ring_when_counted with W ranks emulated on one GPU (every
+    rank's count kernel first, then every rank's plan: no kernel waits for a later one): every
+    rank's table ends up holding all ranks' counts, the flags carry the epoch, the scratch is left
+    zero, and the plan equals the one made from an all-gathered table; two epochs, two tables."""
+    E, T, top_k = 64, 300, 4
+    tables = [torch.zeros((2, world, E), dtype=torch.int32, device=DEV) for _ in range(world)]
+    flags = [torch.zeros(max(world, 4), dtype=torch.int32, device=DEV) for _ in range(world)]
+    scratch = [torch.zeros(E + 1, dtype=torch.int32, device=DEV) for _ in range(world)]
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=DEV)
+    for epoch in (1, 2):
+        par = epoch & 1
+        peer_counts = torch.tensor([t[par].data_ptr() for t in tables], dtype=torch.int64, device=DEV)
+        routings = [torch.from_numpy(workloads.topk_routing(T, E, top_k, seed=100 * epoch + r)).to(DEV).to(torch.int32)
+                    for r in range(world)]
+        routings[0][5, 1] = E + 7  # an expert id that does not exist is not counted
+        for r in range(world):
+            ops.ep_count_share(routings[r], E, scratch[r], world, r, peer_counts, peer_flags, epoch)
+        want = torch.stack([ops.ep_count(routings[r], E) for r in range(world)])
+        for r in range(world):
+            assert torch.equal(tables[r][par], want), f"rank {r}: table of epoch {epoch}"
+            assert flags[r][:world].tolist() == [epoch] * world
+            assert int(scratch[r].abs().sum()) == 0
+            got = ops.ep_plan_ring_when_counted(tables[r][par], flags[r], epoch, r, ops.ep_plan_ring(want, r), status)
+            ref = ops.ep_plan_ring(want.contiguous(), r)
+            for name in ("dest_offset", "segment_sizes", "totals", "send_start"):
+                assert torch.equal(got[name], ref[name]), name
+        assert ops.device_status(status) == 0
+    # a count that never arrives: the plan kernel gives up after its limit and says so
+    late = torch.zeros(max(world, 4), dtype=torch.int32, device=DEV)
+    ops.ep_plan_ring_when_counted(tables[0][0], late, 1, 0, ops.ep_plan_ring(want, 0), status, wait_limit_ms=5)
+    assert ops.device_status(status) == _lib.RD_ERR_DEVICE_WAIT
