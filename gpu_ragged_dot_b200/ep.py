@@ -603,6 +603,7 @@ class ExpertParallelRaggedDot:
         done = torch.cuda.Event()
         done.record(cur)
         h["read"][slot] = done
+        h["last_slot"] = slot
         rows = min(y_host.shape[0], y.shape[0])
         with torch.cuda.stream(s_out):
             s_out.wait_event(done)
@@ -649,6 +650,9 @@ class ExpertParallelRaggedDot:
         done = torch.cuda.Event()
         done.record(cur)
         h["dy_read"] = done
+        # the backward pass still reads the routing table of the slot the forward used: the slot
+        # may be refilled only after it
+        h["read"][h["last_slot"]] = done
         with torch.cuda.stream(h["s_out"]):
             h["s_out"].wait_event(done)
             dx_host.copy_(dx, non_blocking=True)
