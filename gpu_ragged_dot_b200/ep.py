@@ -277,7 +277,9 @@ class ExpertParallelRaggedDot:
         CTAs that wait for other GPUs' senders, resident before them by construction, so no rank's
         progress depends on a separately launched kernel finding room on a busy GPU.
 
-        Returns (y [capacity, n], segment_sizes [W*El] in position order, dest_pos [T, top_k], totals)."""
+        Returns (y [capacity, n], segment_sizes [W*El] in position order, dest_pos [T, top_k], totals).
+        y, segment_sizes and totals are buffers of the layer that the next forward overwrites;
+        dest_pos stays valid until the step after the next."""
         from . import _lib, ops
 
         tokens, top_k = routing.shape

@@ -68,11 +68,20 @@ def _worker(rank, world, port, out_dir):
             out = layer.forward(xs, routing)
             total = out[0].shape[0] if mode == "nccl" else int(out[3].cpu())
             want = out[0][:total].float().cpu()
+            dy_dev = workloads.normal_tensor(tuple(out[0].shape), 1.0, 8000 + rank + step, dev)
+            dx_dev, dW_dev = layer.backward(dy_dev)
             hy = torch.zeros((out[0].shape[0], n), dtype=torch.bfloat16).pin_memory()
             hrows = torch.zeros(1, dtype=torch.int32).pin_memory()
             rows = layer.forward_host(xs.cpu().pin_memory(), hr, hy, rows_host=hrows)
+            # the cotangent belongs to ROWS of y; rows keep their order in the nccl mode only, so the
+            # host-path gradient is compared there (the fused mode's forward is compared below)
+            hdx = torch.zeros((T, k), dtype=torch.bfloat16).pin_memory()
+            dW_host_path = layer.backward_host(dy_dev.cpu().pin_memory(), total, hdx)
             layer.wait_host_outputs()
             torch.cuda.synchronize()
+            if mode == "nccl":
+                ok = ok and torch.allclose(hdx.float(), dx_dev.float().cpu(), rtol=2e-2, atol=2e-2)
+                ok = ok and torch.allclose(dW_host_path.float(), dW_dev.float(), rtol=2e-2, atol=2e-2)
             ok = ok and int(hrows[0]) == total  # the number of defined rows travels with the result
             got = hy[:total].float()
             if mode == "nccl":  # rows arrive in a fixed order
