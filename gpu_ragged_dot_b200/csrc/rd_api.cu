@@ -80,6 +80,31 @@ int encode_map(CUtensorMap* map, const void* base, int dtype, int rank, const ui
   return RD_OK;
 }
 
+// "Column-blocked" view of a dense row-major 16-bit [rows, cols] tensor, cols a multiple of 64:
+// (64 columns, rows, cols / 64 blocks).  A box of (64, box_rows, box_blocks) lands in shared memory
+// as box_blocks slabs of [box_rows][128 B], block after block -- what box_blocks separate 2-D boxes
+// of 64 columns would write -- in ONE TMA instruction.
+int encode_blocked_map(CUtensorMap* map, const void* base, int dtype, int cols, int rows, int box_rows,
+                       int box_blocks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return RD_ERR_DRIVER;
+  cuuint64_t gdims[3] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(cols / 64)};
+  cuuint64_t gstrides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+  cuuint32_t gbox[3] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_blocks)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      dtype == RD_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), gdims, gstrides, gbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "ragged_dot_b200: cuTensorMapEncodeTiled failed (CUresult %d): blocked map base=%p "
+            "rows=%d cols=%d box=(64,%d,%d)\n", static_cast<int>(r), base, rows, cols, box_rows, box_blocks);
+    return RD_ERR_TENSOR_MAP;
+  }
+  return RD_OK;
+}
+
 // ------------------------------------------------------------------ device properties
 int sm_count() {
   static int cached[64] = {0};
@@ -247,6 +272,40 @@ int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap
       cudaSuccess)
     return RD_ERR_LAUNCH;
   kernel<<<ctas, rd::kG2Threads, rd::kG2SmemBytes, stream>>>(ta, tb, tout, args);
+  return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
+}
+
+// tgmm with 512 x 256 tiles on CTA pairs (rd_gemm2.cuh, kPair).
+int launch_gemm2_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout,
+                      const GemmArgs& args, int ctas, cudaStream_t stream) {
+  auto kernel = rd::ragged_gemm2_kernel<false, true, false, true>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rd::kG2PairSmemBytes) !=
+      cudaSuccess)
+    return RD_ERR_LAUNCH;
+  cudaLaunchConfig_t lc = {};
+  lc.blockDim = dim3(rd::kG2Threads, 1, 1);
+  lc.dynamicSmemBytes = rd::kG2PairSmemBytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  // A persistent grid must be fully co-resident: ask how many CTA pairs fit at once.
+  lc.gridDim = dim3(2, 1, 1);
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &lc) != cudaSuccess || clusters <= 0)
+    return RD_ERR_LAUNCH;
+  int pairs = ctas / 2;
+  if (pairs > clusters) pairs = clusters;
+  if (pairs < 1) pairs = 1;
+  lc.gridDim = dim3(2 * pairs, 1, 1);
+  if (cudaLaunchKernelEx(&lc, kernel, ta, tb, tout, args) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return RD_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? RD_OK : RD_ERR_LAUNCH;
 }
 
@@ -722,7 +781,7 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
   int tile_m = cfg ? cfg->tile_m : 0;
   if (cta_group < 0 || cta_group > 2 || (cta_group == 2 && bn != 256)) return RD_ERR_BAD_CONFIG;
   if (tile_m != 0 && tile_m != 128 && tile_m != 256) return RD_ERR_BAD_CONFIG;
-  if (tile_m == 256 && (bn != 256 || cta_group == 2)) return RD_ERR_BAD_CONFIG;
+  if (tile_m == 256 && bn != 256) return RD_ERR_BAD_CONFIG;
   if (f32) {  // the float32 (TF32) kernels exist as single-CTA 128-row tiles only
     if (cta_group == 2 || tile_m == 256 || seg_count > 1) return RD_ERR_BAD_CONFIG;
     cta_group = 1;
@@ -743,7 +802,7 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
                     : 1;
   }
   const bool two_half = tile_m == 256;
-  const int tile_rows = two_half ? rd::kG2TileRows : rd::kTileM * cta_group;
+  const int tile_rows = two_half ? rd::kG2TileRows * cta_group : rd::kTileM * cta_group;
   const long long k_tiles = (k + tile_rows - 1) / tile_rows;
 
   // Launch the metadata kernel before encoding the tensor maps: besides being the first step
@@ -753,18 +812,28 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
   launch_internal_metadata(group_sizes, nullptr, g_fine, m, rd::kTileM, w, stream);
   if (cudaGetLastError() != cudaSuccess) return RD_ERR_LAUNCH;
 
+  // 256-row tiles fetch each operand of a stage with one box when the 64-column blocks tile the
+  // rows exactly (see rd_gemm2.cuh); otherwise one 2-D box per 64 columns.
+  const bool blocked = two_half && !f32 && k % 64 == 0 && n % 64 == 0;
   CUtensorMap ta, tb;
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
-    rc = encode_map(&ta, x, dtype, 2, dims, box, /*atom32=*/f32);
+  if (blocked) {
+    rc = encode_blocked_map(&ta, x, dtype, k, m, rd::kTileK, rd::kG2TileRows / 64);
     if (rc != RD_OK) return rc;
-  }
-  {
-    const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
-    const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
-    rc = encode_map(&tb, dout, dtype, 2, dims, box, /*atom32=*/f32);
+    rc = encode_blocked_map(&tb, dout, dtype, n, m, rd::kTileK, rd::kG2TileN / 64 / cta_group);
     if (rc != RD_OK) return rc;
+  } else {
+    {
+      const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+      const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
+      rc = encode_map(&ta, x, dtype, 2, dims, box, /*atom32=*/f32);
+      if (rc != RD_OK) return rc;
+    }
+    {
+      const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
+      const uint32_t box[2] = {static_cast<uint32_t>(row_elems), static_cast<uint32_t>(row_elems)};
+      rc = encode_map(&tb, dout, dtype, 2, dims, box, /*atom32=*/f32);
+      if (rc != RD_OK) return rc;
+    }
   }
 
   CUtensorMap tout;
@@ -782,6 +851,7 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
   args.k_tiles = static_cast<int>(k_tiles);
   args.seg_count = seg_count;
   args.seg_stride = g;
+  args.blocked_maps = blocked ? 1 : 0;
   args.max_m_tiles = w.layout.max_tiles;
   args.ab_format = dtype;
   args.wait_limit_us = wait_limit_us(cfg);
@@ -799,6 +869,7 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
     if (bn == 128) return launch_gemm_f32<128, false, true>(ta, tb, tout, args, ctas, stream);
     return launch_gemm_f32<64, false, true>(ta, tb, tout, args, ctas, stream);
   }
+  if (two_half && cta_group == 2) return launch_gemm2_pair(ta, tb, tout, args, ctas, stream);
   if (two_half) return launch_gemm2<false, true>(ta, tb, tout, args, ctas, stream);
   if (seg_count > 1) {
     if (bn == 256) return launch_gemm<256, false, true, 1, true>(ta, tb, tout, args, ctas, stream);

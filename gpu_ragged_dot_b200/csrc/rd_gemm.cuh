@@ -67,6 +67,9 @@ struct GemmArgs {
   int max_m_tiles;  // static upper bound on live row tiles (gmm)
   int ab_format;    // 0 = fp16, 1 = bf16
   int zero_tail;    // gmm: write zeros to the rows past sum(group_sizes)
+  // tgmm on 256-row tiles: the operand maps are "column-blocked" views (64 columns, rows, blocks
+  // of 64 columns), so that ONE box fetches all the 64-column slabs an operand has in a stage.
+  int blocked_maps;
   uint32_t wait_limit_us;  // how long a bounded wait inside the kernel may last (microseconds)
   const float* weight_scale;  // 8-bit inputs: scale of weight matrix w, applied to the accumulator (null: 1)
   const int32_t* group_sizes;

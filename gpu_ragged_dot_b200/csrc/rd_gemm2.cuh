@@ -17,6 +17,21 @@
 // Same roles, operand layouts, barrier discipline (bounded waits) and epilogue (swizzled smem
 // staging + TMA stores, row-masked stores where a gmm slab crosses its group's end) as
 // rd_gemm.cuh; the helpers of that file are reused.
+//
+// kPair (tgmm only): two CTAs of a cluster own a 512 x 256 tile, CTA c its rows [256 c, 256 c +
+// 256).  Half h is ONE tcgen05.mma.cta_group::2 product of 256 rows, rows [128 h, 128 h + 128) of
+// either CTA; each CTA loads its own rows of the A operand (32 KB) and HALF of the B operand's
+// columns (16 KB), so a stage is 48 KB for the same MMAs per SM, a quarter less L2 -> SM traffic
+// per flop, and four stages fit.  The hand-shakes between the two CTAs are those of the 128-row
+// pair kernel in rd_gemm.cuh.  Measured on the Mixtral-shaped weight gradient it moves 5.8 GB
+// instead of 7.75 GB from L2 but takes 0.78 ms against 0.75 ms for one CTA per tile, so it is
+// only used on request (rd_tile_cfg: tile_m 256 with cta_group 2).
+//
+// Blocked operand maps (GemmArgs::blocked_maps, tgmm): x and dout are described to TMA as
+// (64 columns, rows, blocks of 64 columns), so ONE box of (64, 64 rows, 4 blocks) = 32 KB lands as
+// the same four [64 rows][128 B] slabs that four 2-D boxes would write: two TMA instructions per
+// stage instead of eight (about 1 % on the Mixtral-shaped weight gradient).  Needs k and n to be
+// multiples of 64; otherwise one 2-D box per 64 columns, as in rd_gemm.cuh.
 #pragma once
 
 #include "rd_gemm.cuh"
@@ -26,6 +41,7 @@ namespace rd {
 constexpr int kG2EpilogueWarps = 8;
 constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps;
 constexpr int kG2Stages = 3;
+constexpr int kG2PairStages = 4;  // 48 KB stages when a CTA pair shares the B operand
 constexpr int kG2TileN = 256;
 constexpr int kG2TileRows = 2 * kTileM;
 constexpr int kG2TgmmBand = 8;  // column tiles per band of the tgmm tile order
@@ -33,6 +49,8 @@ constexpr uint32_t kG2ABytes = 2 * kTileM * kTileK * 2;   // two 128-row halves
 constexpr uint32_t kG2BBytes = kG2TileN * kTileK * 2;
 constexpr uint32_t kG2StageBytes = kG2ABytes + kG2BBytes;  // 64 KB
 constexpr int kG2SmemBytes = kG2Stages * kG2StageBytes + kG2EpilogueWarps * kOutBoxBytes + 1024;
+constexpr uint32_t kG2PairStageBytes = kG2ABytes + kG2BBytes / 2;  // 48 KB
+constexpr int kG2PairSmemBytes = kG2PairStages * kG2PairStageBytes + kG2EpilogueWarps * kOutBoxBytes + 1024;
 
 // rows: valid rows of the whole 256-row tile (gmm) / rows of the group (tgmm).
 __device__ __forceinline__ TileCoord decode_gmm_tile256(const GemmArgs& p, int tile) {
@@ -54,6 +72,7 @@ __device__ __forceinline__ TileCoord decode_gmm_tile256(const GemmArgs& p, int t
   return t;
 }
 
+template <int kRows = kG2TileRows>
 __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int tile) {
   const int per_group = p.k_tiles * p.n_tiles;
   const int gi = tile / per_group;
@@ -73,7 +92,7 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int 
   t.row0 = p.group_offsets[gi];
   t.rows = imax(imin(imax(p.group_sizes[gi], 0), p.m - t.row0), 0);
   t.n0 = nt * kG2TileN;
-  t.k0 = kt * kG2TileRows;
+  t.k0 = kt * kRows;
   return t;
 }
 
@@ -82,30 +101,39 @@ __device__ __forceinline__ TileCoord decode_tgmm_tile256(const GemmArgs& p, int 
 // `cta_index` / `gemm_ctas` variables cost the plain kernel 3-5 %):
 //   gmm:  the expert-parallel variant (ready flags in the loader, sender CTAs in the grid);
 //   tgmm: strided segments (a block contracts over several row ranges, rd_tgmm_strided).
-template <bool kBKMajor, bool kTgmm, bool kVariant = false>
+template <bool kBKMajor, bool kTgmm, bool kVariant = false, bool kPair = false>
 __global__ void __launch_bounds__(kG2Threads, 1)
 ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   static_assert(!(kTgmm && kBKMajor), "tgmm reads both operands MN-major");
+  static_assert(!kPair || (kTgmm && !kVariant), "CTA pairs: plain tgmm only");
   constexpr bool kEp = !kTgmm && kVariant;
   constexpr bool kSeg = kTgmm && kVariant;
+  constexpr int kCtas = kPair ? 2 : 1;
   constexpr int BN = kG2TileN;
-  constexpr int kStages = kG2Stages;
+  constexpr int kBCols = BN / kCtas;  // B-operand columns this CTA loads
+  constexpr int kStages = kPair ? kG2PairStages : kG2Stages;
   constexpr uint32_t kHalfABytes = kTileM * kTileK * 2;  // 16 KB
+  constexpr uint32_t kBBytes = kBCols * kTileK * 2;
+  constexpr uint32_t kStageBytes = kG2ABytes + kBBytes;  // 64 KB, 48 KB in a pair
   constexpr uint32_t kTmemCols = 2 * BN;                 // accumulator of half h at column h * BN
+  constexpr int kCtaRows = 2 * kTileM;                   // output rows of one CTA (both halves)
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kStages];
   __shared__ __align__(8) uint64_t bar_empty[kStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];   // per half
-  __shared__ __align__(8) uint64_t bar_acc_empty[2];  // per half
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];  // per half (pair: the leader's is used)
+  __shared__ __align__(8) uint64_t bar_peer_ready[kPair ? kStages : 1];  // leader: peer cleared its tail rows
   __shared__ uint32_t tmem_slot;
   __shared__ WaitCtl wait_ctl;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const int cta_rank = kPair ? static_cast<int>(cluster_cta_rank()) : 0;
+  const bool leader = cta_rank == 0;
 
   // Fused expert-parallel exchange: some CTAs of the grid send rows instead of multiplying.
   // The senders are the FIRST CTAs of the grid, so they are resident before any CTA that may wait
@@ -132,16 +160,20 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int h = 0; h < 2; ++h) {
       mbar_init(smem_u32(&bar_acc_full[h]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[h]), 4);  // the four epilogue warps of that half
+      mbar_init(smem_u32(&bar_acc_empty[h]), 4 * kCtas);  // the four epilogue warps of that half (per CTA)
+    }
+    if constexpr (kPair) {
+      for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&bar_peer_ready[s]), 1);
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(&tmem_slot), kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<kCtas>(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish<kCtas>();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) cluster_sync();  // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   volatile WaitCtl* abort_ptr = &wait_ctl;
@@ -149,9 +181,20 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles =
       kTgmm ? p.g * p.k_tiles * p.n_tiles : imin(p.totals[0], p.max_m_tiles) * p.n_tiles;
   const int k_blocks_gmm = (p.k + kTileK - 1) / kTileK;
-  const int tile_step = kEp ? static_cast<int>(gridDim.x) - sender_ctas : static_cast<int>(gridDim.x);
+  const int tile_step = kPair ? static_cast<int>(gridDim.x >> 1)
+                        : kEp ? static_cast<int>(gridDim.x) - sender_ctas : static_cast<int>(gridDim.x);
+  auto first_tile = [&]() -> int {
+    if constexpr (kPair) return static_cast<int>(blockIdx.x >> 1);
+    if constexpr (kEp) return static_cast<int>(blockIdx.x) - sender_ctas;
+    return static_cast<int>(blockIdx.x);
+  };
+  auto decode = [&](int tile) -> TileCoord {
+    if constexpr (kPair) return decode_tgmm_tile256<2 * kG2TileRows>(p, tile);
+    if constexpr (kTgmm) return decode_tgmm_tile256(p, tile);
+    return decode_gmm_tile256(p, tile);
+  };
 
-  // Number of 128-row halves of a tile that exist.
+  // Number of halves of a tile that exist.
   auto halves_of = [&](const TileCoord& t) -> int {
     if (kTgmm) return (t.k0 + kTileM < p.k) ? 2 : 1;
     return t.rows > kTileM ? 2 : 1;
@@ -166,8 +209,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int ready_slot = -1;  // last ready flag this producer has seen set
       uint64_t waited_ns = 0;
       const uint64_t t_start = kEp ? global_timer_ns() : 0;
-      for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
-        const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+      for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = decode(tile);
         const int halves = halves_of(t);
         const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
         RowBlocks blocks = first_block(t);
@@ -190,13 +233,60 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bar_full[s]);
-          const uint32_t sa = stage_base + s * kG2StageBytes;
+          uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t sa = stage_base + s * kStageBytes;
           const uint32_t sb = sa + kG2ABytes;
-          mbar_arrive_expect_tx(full, halves * kHalfABytes + kG2BBytes);
+          const uint32_t own_bytes = halves * kHalfABytes + kBBytes;
+          if constexpr (kPair) {
+            // The peer's bytes are counted on the leader's barrier, except for the stage whose tail
+            // rows the peer has to clear first (it then needs to see its own data land).
+            const bool local_stage = kb == kb_count - 1 && tail_needs_clearing(t.rows);
+            int r, live;
+            tgmm_block<false>(p, t, blocks, kb, r, live);
+            const int ka = t.k0 + cta_rank * kCtaRows;
+            const int nb = t.n0 + cta_rank * kBCols;
+            const uint32_t bytes = p.blocked_maps ? kStageBytes : own_bytes;  // a blocked A box always has both halves
+            if (leader || local_stage) {
+              mbar_arrive_expect_tx(full, (leader && !local_stage) ? 2 * bytes : bytes);
+              if (p.blocked_maps) {
+                tma_load_3d_hint(sa, &tmap_a, full, 0, r, ka >> 6, keep);
+                tma_load_3d_hint(sb, &tmap_b, full, 0, r, nb >> 6, keep);
+              } else {
+                for (int h = 0; h < halves; ++h) {
+                  tma_load_2d_hint(sa + h * kHalfABytes, &tmap_a, full, ka + h * kTileM, r, keep);
+                  tma_load_2d_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, ka + h * kTileM + 64, r, keep);
+                }
+#pragma unroll
+                for (int j = 0; j < kBCols / 64; ++j)
+                  tma_load_2d_hint(sb + j * kBoxBytes, &tmap_b, full, nb + j * 64, r, keep);
+              }
+            } else {
+              full = map_to_cta(full, 0);
+              if (p.blocked_maps) {
+                tma_load_3d_pair_hint(sa, &tmap_a, full, 0, r, ka >> 6, keep);
+                tma_load_3d_pair_hint(sb, &tmap_b, full, 0, r, nb >> 6, keep);
+              } else {
+                for (int h = 0; h < halves; ++h) {
+                  tma_load_2d_pair_hint(sa + h * kHalfABytes, &tmap_a, full, ka + h * kTileM, r, keep);
+                  tma_load_2d_pair_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, ka + h * kTileM + 64, r, keep);
+                }
+#pragma unroll
+                for (int j = 0; j < kBCols / 64; ++j)
+                  tma_load_2d_pair_hint(sb + j * kBoxBytes, &tmap_b, full, nb + j * 64, r, keep);
+              }
+            }
+            continue;
+          }
           if (kTgmm) {
             int r, live;
             tgmm_block<kSeg>(p, t, blocks, kb, r, live);
+            if (p.blocked_maps) {  // one box per operand; the A box always has both halves
+              mbar_arrive_expect_tx(full, kStageBytes);
+              tma_load_3d_hint(sa, &tmap_a, full, 0, r, t.k0 >> 6, keep);
+              tma_load_3d_hint(sb, &tmap_b, full, 0, r, t.n0 >> 6, keep);
+              continue;
+            }
+            mbar_arrive_expect_tx(full, own_bytes);
             for (int h = 0; h < halves; ++h) {
               tma_load_2d_hint(sa + h * kHalfABytes, &tmap_a, full, t.k0 + h * kTileM, r, keep);
               tma_load_2d_hint(sa + h * kHalfABytes + kBoxBytes, &tmap_a, full, t.k0 + h * kTileM + 64, r, keep);
@@ -205,6 +295,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d_hint(sb + j * kBoxBytes, &tmap_b, full, t.n0 + j * 64, r, keep);
           } else {
+            mbar_arrive_expect_tx(full, own_bytes);
             for (int h = 0; h < halves; ++h)
               tma_load_2d(sa + h * kHalfABytes, &tmap_a, full, kb * kTileK, t.row0 + h * kTileM);
             if (kBKMajor) {
@@ -226,7 +317,9 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM, BN);
+    // In a pair only the leader issues MMAs; the peer's warp has nothing to do except for the
+    // stages whose tail rows it must clear in its own shared memory.
+    const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
     constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;
     constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;
     const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
@@ -238,13 +331,35 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);
     uint32_t it = 0;
     uint32_t uses[2] = {0u, 0u};  // how often each half's accumulator has been used
+    uint32_t tail_parity = 0;     // pair, bit s: parity of the next tail hand-shake on stage s
     bool ok = true;
-    for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
-      const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+    for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
+      const TileCoord t = decode(tile);
       const int halves = halves_of(t);
       const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
       RowBlocks blocks = first_block(t);
       const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+
+      if constexpr (kPair) {
+        if (!leader) {
+          if (tail_stage) {
+            const uint32_t s = (it + kb_count - 1) % kStages;
+            const uint32_t par = (tail_parity >> s) & 1u;
+            tail_parity ^= 1u << s;
+            if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
+              ok = false;
+              break;
+            }
+            clear_tail_rows<kStageBytes / kBoxBytes>(stage_base + s * kStageBytes,
+                                                     t.rows - (kb_count - 1) * kTileK, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&bar_peer_ready[s]), 0);
+            __syncwarp();
+          }
+          it += kb_count;
+          continue;
+        }
+      }
 
       if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
 #pragma unroll
@@ -255,7 +370,10 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
               break;
             }
             ++uses[h];
-            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_full[h]));
+            if (lane == 0) {
+              mbar_arrive(smem_u32(&bar_acc_full[h]));
+              if constexpr (kPair) mbar_arrive_cluster(smem_u32(&bar_acc_full[h]), 1);
+            }
           }
         }
         __syncwarp();
@@ -269,7 +387,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = false;
           break;
         }
-        const uint32_t sa = stage_base + s * kG2StageBytes;
+        const uint32_t sa = stage_base + s * kStageBytes;
         int live = kTileK;
         if (kTgmm) {
           int r;
@@ -277,11 +395,20 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
         if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
-          clear_tail_rows<kG2StageBytes / kBoxBytes>(sa, live, lane);
+          clear_tail_rows<kStageBytes / kBoxBytes>(sa, live, lane);
           __syncwarp();
+          if constexpr (kPair) {  // ... and wait until the peer has done the same in its stage
+            const uint32_t par = (tail_parity >> s) & 1u;
+            tail_parity ^= 1u << s;
+            if (!mbar_wait<true>(smem_u32(&bar_peer_ready[s]), par, abort_ptr)) {
+              ok = false;
+              break;
+            }
+          }
         }
         const bool last = kb == kb_count - 1;
-        const uint32_t b_lo = bdesc0_lo + s * (kG2StageBytes >> 4);
+        const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
+        tc_fence_after_sync();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (h < halves) {
@@ -291,33 +418,44 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 break;
               }
               ++uses[h];
+              tc_fence_after_sync();
             }
-            tc_fence_after_sync();
             if (lane == 0) {
               const uint32_t tmem_d = tmem_base + h * BN;
-              const uint32_t a_lo = adesc0_lo + s * (kG2StageBytes >> 4) + h * (kHalfABytes >> 4);
+              const uint32_t a_lo = adesc0_lo + s * (kStageBytes >> 4) + h * (kHalfABytes >> 4);
               if (kTgmm && n_mma < kTileK / kUmmaK) {
                 for (int kk = 0; kk < n_mma; ++kk) {
-                  umma_f16<1>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                  umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
                               make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
                               (kb > 0 || kk > 0) ? 1u : 0u);
                 }
               } else {
-                umma_f16<1>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
+                umma_f16<kCtas>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
                             kb > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
-                  umma_f16<1>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
+                  umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
                               make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
                 }
               }
-              if (last) umma_commit(smem_u32(&bar_acc_full[h]));  // this half is complete
+              if (last) {  // this half is complete
+                if constexpr (kPair) {
+                  umma_commit_pair(smem_u32(&bar_acc_full[h]), 0x3);
+                } else {
+                  umma_commit(smem_u32(&bar_acc_full[h]));
+                }
+              }
             }
-            __syncwarp();
           }
         }
         if (!ok) break;
-        if (lane == 0) umma_commit(smem_u32(&bar_empty[s]));  // both halves have read the stage
+        if (lane == 0) {  // both halves have read the stage (in both CTAs of a pair)
+          if constexpr (kPair) {
+            umma_commit_pair(smem_u32(&bar_empty[s]), 0x3);
+          } else {
+            umma_commit(smem_u32(&bar_empty[s]));
+          }
+        }
         __syncwarp();
       }
     }
@@ -327,14 +465,14 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // of its quarter (warp index mod 4).
     const int half = (warp - 2) >> 2;
     const int quarter = warp & 3;
-    const int r_in_tile = half * kTileM + quarter * 32 + lane;
-    const uint32_t buf = stage_base + kStages * kG2StageBytes + (warp - 2) * kOutBoxBytes;
+    const int r_in_tile = cta_rank * kCtaRows + half * kTileM + quarter * 32 + lane;
+    const uint32_t buf = stage_base + kStages * kStageBytes + (warp - 2) * kOutBoxBytes;
     uint32_t uses = 0;
     bool ok = true;
     const uint64_t stream_out = l2_policy_evict_first();
     uint16_t* out16 = reinterpret_cast<uint16_t*>(p.out);
-    for (int tile = kEp ? static_cast<int>(blockIdx.x) - sender_ctas : blockIdx.x; tile < num_tiles && ok; tile += tile_step) {
-      const TileCoord t = kTgmm ? decode_tgmm_tile256(p, tile) : decode_gmm_tile256(p, tile);
+    for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
+      const TileCoord t = decode(tile);
       if (half >= halves_of(t)) continue;  // this half does not exist in this tile
       const int n0 = t.n0;
       if (!mbar_wait(smem_u32(&bar_acc_full[half]), uses & 1u, abort_ptr)) {
@@ -347,7 +485,7 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool row_ok, warp_has_rows, slab_by_tma, zero_only = false;
       size_t row_off;
       int out_row0;
-      const int slab0 = half * kTileM + quarter * 32;  // first tile row of this warp's slab
+      const int slab0 = cta_rank * kCtaRows + half * kTileM + quarter * 32;  // first tile row of this warp's slab
       if (kTgmm) {
         const int kr = t.k0 + r_in_tile;
         out_row0 = t.k0 + slab0;
@@ -432,7 +570,13 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (n_chunks > 0) {  // the accumulator is in registers: hand it back
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar);
+        if (lane == 0) {
+          if constexpr (kPair) {
+            mbar_arrive_cluster(acc_empty_bar, 0);
+          } else {
+            mbar_arrive(acc_empty_bar);
+          }
+        }
       }
 #pragma unroll
       for (int c = 1; c < BN / 64; ++c) {
@@ -441,7 +585,13 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (n_chunks == 0) {
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar);
+        if (lane == 0) {
+          if constexpr (kPair) {
+            mbar_arrive_cluster(acc_empty_bar, 0);
+          } else {
+            mbar_arrive(acc_empty_bar);
+          }
+        }
       }
     }
     if (lane == 0) bulk_wait_group<0>();
@@ -470,9 +620,11 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  // Neither CTA of a pair may leave while the other can still reach its barriers or smem.
+  if constexpr (kPair) cluster_sync();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<kCtas>(tmem_base, kTmemCols);
   }
 }
 

@@ -56,10 +56,11 @@ enum rd_dtype { RD_DTYPE_F16 = 0, RD_DTYPE_BF16 = 1, RD_DTYPE_F32 = 2 };
  *   tile_n    : output columns per tile, one of 64, 128, 256; 0 = library's choice
  *               (the contraction step is always 64).
  *   max_ctas  : cap on the persistent grid (0 = one CTA per SM).
- *   cta_group : 1 = one CTA per tile; 2 = a pair of CTAs per 256-row tile
- *               (tile_n must be 256, tile_m must not be 256); 0 = library's choice.
+ *   cta_group : 1 = one CTA per tile; 2 = a pair of CTAs per tile, each with half of the B operand
+ *               (tile_n must be 256); 0 = library's choice.
  *   tile_m    : 128, or 256 = one CTA computes 256-row tiles as two 128-row halves sharing
- *               each B stage (tile_n must be 256, cta_group 1); 0 = library's choice.
+ *               each B stage (tile_n must be 256); 0 = library's choice.  With cta_group 2,
+ *               tile_m 256 (512-row tiles on a CTA pair) exists for rd_tgmm only.
  *   flags     : RD_CFG_NO_ZERO_TAIL = rd_gmm leaves the rows past sum(group_sizes) unwritten
  *               (for callers that pass an upper bound as m and never read those rows).
  *               RD_CFG_GROUP_BY_WEIGHT = rd_gmm_indexed takes the groups in the order of the weight

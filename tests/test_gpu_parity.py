@@ -200,6 +200,21 @@ def test_256_row_tiles_ragged_boundaries(cta_group, tile_m, trans_rhs):
         _check_tgmm(x, dout, sizes, cfg=cfg, what="pair ragged tgmm")
 
 
+@pytest.mark.parametrize("k", [136, 264, 392, 520, 1032])
+def test_tgmm_512_row_tiles_on_cta_pairs(k):
+    """tgmm with 512 x 256 tiles on CTA pairs (tile_m 256, cta_group 2): k values that end inside
+    the first CTA's rows, the second CTA's rows, the second half and the second tile; group sizes
+    around the 64-row reduction step and the 16-row MMA depth (both CTAs clear their tail rows);
+    empty groups; rows past the last group hold NaN and must not reach any output."""
+    sizes = [1, 63, 64, 65, 0, 130, 15, 16, 17, 0, 300, 77]
+    m, n = sum(sizes) + 40, 392
+    x, _, dout = _inputs(8, m, k, n, len(sizes))
+    x[sum(sizes):] = float("nan")
+    dout[sum(sizes):] = float("nan")
+    got = _check_tgmm(x, dout, sizes, cfg=_lib.TileCfg(256, 0, 2, 256), what=f"pair 512-row tgmm k={k}")
+    assert torch.isfinite(got.float()).all()
+
+
 def test_group_boundaries_every_residue():
     """Group sizes 1..40 and 120..136: every boundary residue around the 64-row reduction
     step and the 128-row tile."""
