@@ -39,7 +39,8 @@
 namespace rd {
 
 constexpr int kG2EpilogueWarps = 8;
-constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps;
+constexpr int kG2FixerWarp = 2 + kG2EpilogueWarps;  // warp 10: clears tail rows of tgmm stages
+constexpr int kG2Threads = 64 + 32 * kG2EpilogueWarps + 32;
 constexpr int kG2Stages = 3;
 constexpr int kG2PairStages = 4;  // 48 KB stages when a CTA pair shares the B operand
 constexpr int kG2TileN = 256;
@@ -125,7 +126,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_empty[kStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];   // per half
   __shared__ __align__(8) uint64_t bar_acc_empty[2];  // per half (pair: the leader's is used)
-  __shared__ __align__(8) uint64_t bar_peer_ready[kPair ? kStages : 1];  // leader: peer cleared its tail rows
+  __shared__ __align__(8) uint64_t bar_tail_go;    // MMA thread -> fixer warp(s): a stage with tail rows has landed
+  __shared__ __align__(8) uint64_t bar_tail_done;  // fixer warp(s) -> MMA thread: its tail rows are cleared
   __shared__ uint32_t tmem_slot;
   __shared__ WaitCtl wait_ctl;
 
@@ -162,9 +164,8 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(smem_u32(&bar_acc_full[h]), 1);
       mbar_init(smem_u32(&bar_acc_empty[h]), 4 * kCtas);  // the four epilogue warps of that half (per CTA)
     }
-    if constexpr (kPair) {
-      for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&bar_peer_ready[s]), 1);
-    }
+    mbar_init(smem_u32(&bar_tail_go), 1);
+    mbar_init(smem_u32(&bar_tail_done), kCtas);  // one arrival per CTA's fixer warp (pair: the leader's is used)
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -317,125 +318,102 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    // In a pair only the leader issues MMAs; the peer's warp has nothing to do except for the
-    // stages whose tail rows it must clear in its own shared memory.
-    const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
-    constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;
-    constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;
-    const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
-                                  : make_smem_desc(stage_base, 16, 1024);
-    const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kG2ABytes, 16, 1024)
-                                     : make_smem_desc(stage_base + kG2ABytes, kBoxBytes, 1024);
-    const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
-    const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
-    const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);
-    uint32_t it = 0;
-    uint32_t uses[2] = {0u, 0u};  // how often each half's accumulator has been used
-    uint32_t tail_parity = 0;     // pair, bit s: parity of the next tail hand-shake on stage s
-    bool ok = true;
-    for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
-      const TileCoord t = decode(tile);
-      const int halves = halves_of(t);
-      const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
-      RowBlocks blocks = first_block(t);
-      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+    // ONE thread runs the whole loop (in a pair: of the leader CTA).  The loop sits on the ring's
+    // critical path -- a stage can be refilled only after its MMAs, and they only start after
+    // this thread has seen the stage land -- and warp-wide steps are expensive there (a
+    // __syncwarp costs about 160 clocks on B200, a stage's MMAs take 1024).  The one warp-wide
+    // job, clearing the rows past a group's end in a tgmm stage, belongs to the fixer warp.
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_f16(p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
+      constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;
+      constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;
+      const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
+                                    : make_smem_desc(stage_base, 16, 1024);
+      const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kG2ABytes, 16, 1024)
+                                       : make_smem_desc(stage_base + kG2ABytes, kBoxBytes, 1024);
+      const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
+      const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
+      const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);
+      uint32_t it = 0;
+      uint32_t uses[2] = {0u, 0u};  // how often each half's accumulator has been used
+      uint32_t tail_events = 0;     // stages handed to the fixer warp so far
+      bool ok = true;
+      for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = decode(tile);
+        const int halves = halves_of(t);
+        const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
+        RowBlocks blocks = first_block(t);
+        const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
 
-      if constexpr (kPair) {
-        if (!leader) {
-          if (tail_stage) {
-            const uint32_t s = (it + kb_count - 1) % kStages;
-            const uint32_t par = (tail_parity >> s) & 1u;
-            tail_parity ^= 1u << s;
-            if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
-              ok = false;
-              break;
-            }
-            clear_tail_rows<kStageBytes / kBoxBytes>(stage_base + s * kStageBytes,
-                                                     t.rows - (kb_count - 1) * kTileK, lane);
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(smem_u32(&bar_peer_ready[s]), 0);
-            __syncwarp();
-          }
-          it += kb_count;
-          continue;
-        }
-      }
-
-      if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
+        if (kb_count == 0) {  // tgmm, empty group: the epilogue writes zeros, nothing to compute
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h < halves) {
-            if (!mbar_wait(smem_u32(&bar_acc_empty[h]), (uses[h] & 1u) ^ 1u, abort_ptr)) {
-              ok = false;
-              break;
-            }
-            ++uses[h];
-            if (lane == 0) {
-              mbar_arrive(smem_u32(&bar_acc_full[h]));
-              if constexpr (kPair) mbar_arrive_cluster(smem_u32(&bar_acc_full[h]), 1);
-            }
-          }
-        }
-        __syncwarp();
-        continue;
-      }
-
-      uint32_t s = it % kStages;
-      uint32_t ph = (it / kStages) & 1u;
-      for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
-        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_ptr)) {
-          ok = false;
-          break;
-        }
-        const uint32_t sa = stage_base + s * kStageBytes;
-        int live = kTileK;
-        if (kTgmm) {
-          int r;
-          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
-        }
-        const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
-          clear_tail_rows<kStageBytes / kBoxBytes>(sa, live, lane);
-          __syncwarp();
-          if constexpr (kPair) {  // ... and wait until the peer has done the same in its stage
-            const uint32_t par = (tail_parity >> s) & 1u;
-            tail_parity ^= 1u << s;
-            if (!mbar_wait<true>(smem_u32(&bar_peer_ready[s]), par, abort_ptr)) {
-              ok = false;
-              break;
-            }
-          }
-        }
-        const bool last = kb == kb_count - 1;
-        const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h < halves) {
-            if (kb == 0) {  // the half's accumulator must have been drained by the epilogue
+          for (int h = 0; h < 2; ++h) {
+            if (h < halves) {
               if (!mbar_wait(smem_u32(&bar_acc_empty[h]), (uses[h] & 1u) ^ 1u, abort_ptr)) {
                 ok = false;
                 break;
               }
               ++uses[h];
-              tc_fence_after_sync();
+              mbar_arrive(smem_u32(&bar_acc_full[h]));
+              if constexpr (kPair) mbar_arrive_cluster(smem_u32(&bar_acc_full[h]), 1);
             }
-            if (lane == 0) {
+          }
+          continue;
+        }
+
+        uint32_t s = it % kStages;
+        uint32_t ph = (it / kStages) & 1u;
+        for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          int live = kTileK;
+          if (kTgmm) {
+            int r;
+            tgmm_block<kSeg>(p, t, blocks, kb, r, live);
+          }
+          const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
+          if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
+            // Rows past the end of the group belong to the next group (or to nobody): the fixer
+            // warp (of either CTA in a pair) clears them before the MMAs read the stage.
+            mbar_arrive(smem_u32(&bar_tail_go));
+            if constexpr (kPair) mbar_arrive_cluster(smem_u32(&bar_tail_go), 1);
+            if (!mbar_wait<kPair>(smem_u32(&bar_tail_done), tail_events & 1u, abort_ptr)) {
+              ok = false;
+              break;
+            }
+            ++tail_events;
+          }
+          const bool last = kb == kb_count - 1;
+          const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h < halves) {
+              if (kb == 0) {  // the half's accumulator must have been drained by the epilogue
+                if (!mbar_wait(smem_u32(&bar_acc_empty[h]), (uses[h] & 1u) ^ 1u, abort_ptr)) {
+                  ok = false;
+                  break;
+                }
+                ++uses[h];
+                tc_fence_after_sync();
+              }
               const uint32_t tmem_d = tmem_base + h * BN;
               const uint32_t a_lo = adesc0_lo + s * (kStageBytes >> 4) + h * (kHalfABytes >> 4);
               if (kTgmm && n_mma < kTileK / kUmmaK) {
                 for (int kk = 0; kk < n_mma; ++kk) {
                   umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
-                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
-                              (kb > 0 || kk > 0) ? 1u : 0u);
+                                  make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
+                                  (kb > 0 || kk > 0) ? 1u : 0u);
                 }
               } else {
                 umma_f16<kCtas>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
-                            kb > 0 ? 1u : 0u);
+                                kb > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
                   umma_f16<kCtas>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
-                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
+                                  make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
                 }
               }
               if (last) {  // this half is complete
@@ -447,16 +425,64 @@ ragged_gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
-        }
-        if (!ok) break;
-        if (lane == 0) {  // both halves have read the stage (in both CTAs of a pair)
+          if (!ok) break;
+          // both halves have read the stage (in both CTAs of a pair)
           if constexpr (kPair) {
             umma_commit_pair(smem_u32(&bar_empty[s]), 0x3);
           } else {
             umma_commit(smem_u32(&bar_empty[s]));
           }
         }
-        __syncwarp();
+      }
+    }
+  } else if (warp == kG2FixerWarp) {
+    // ------------------------------------------------------------ tail fixer (tgmm)
+    // Walks the tiles like the MMA thread and, for every stage whose last 16-deep MMA reaches past
+    // the end of its group, waits for the MMA thread's go (the stage has landed), clears those
+    // rows in every box of the stage in THIS CTA's shared memory and reports back.
+    if constexpr (kTgmm) {
+      uint32_t it = 0;
+      uint32_t events = 0;
+      uint32_t own_parity = 0;  // peer of a pair, bit s: parity of the next landing on its own barrier of slot s
+      bool ok = true;
+      for (int tile = first_tile(); tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = decode(tile);
+        const int kb_count = tgmm_block_count<kSeg>(p, t);
+        RowBlocks blocks = first_block(t);
+        const bool tail_stage = kb_count > 0 && tail_needs_clearing(t.rows);
+        for (int kb = kSeg ? 0 : imax(kb_count - 1, 0); kb < kb_count; ++kb) {
+          int r, live;
+          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
+          if (!(kSeg ? block_needs_clearing(live) : tail_stage)) continue;
+          const uint32_t s = (it + kb) % kStages;
+          if (!mbar_wait<kPair>(smem_u32(&bar_tail_go), events & 1u, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          if constexpr (kPair) {
+            // The peer's bytes of such a stage are counted on its own barrier of that slot (see
+            // the producer), which is used for nothing else.
+            if (!leader) {
+              const uint32_t par = (own_parity >> s) & 1u;
+              own_parity ^= 1u << s;
+              if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
+                ok = false;
+                break;
+              }
+            }
+          }
+          ++events;
+          clear_tail_rows<kStageBytes / kBoxBytes>(stage_base + s * kStageBytes, live, lane);
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(smem_u32(&bar_tail_done), 0);
+            } else {
+              mbar_arrive(smem_u32(&bar_tail_done));
+            }
+          }
+        }
+        it += kb_count;
       }
     }
   } else {
