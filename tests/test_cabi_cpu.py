@@ -136,3 +136,12 @@ def test_xla_ffi_shim_compiles_on_its_own():
     assert proc.returncode == 0, proc.stderr
     text = open(src).read()
     assert "ffi::DataType::F32" in text and "RD_DTYPE_F32" in text  # float32 reaches the TF32 kernels
+
+
+def test_probe_program_builds():
+    """The stand-alone hardware probes compile for sm_100a without a GPU."""
+    import os
+
+    from gpu_ragged_dot_b200 import probe
+
+    assert os.path.exists(probe.build_probe())
