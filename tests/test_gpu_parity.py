@@ -200,18 +200,24 @@ def test_256_row_tiles_ragged_boundaries(cta_group, tile_m, trans_rhs):
         _check_tgmm(x, dout, sizes, cfg=cfg, what="pair ragged tgmm")
 
 
-@pytest.mark.parametrize("k", [136, 264, 392, 520, 1032])
-def test_tgmm_512_row_tiles_on_cta_pairs(k):
-    """tgmm with 512 x 256 tiles on CTA pairs (tile_m 256, cta_group 2): k values that end inside
-    the first CTA's rows, the second CTA's rows, the second half and the second tile; group sizes
-    around the 64-row reduction step and the 16-row MMA depth (both CTAs clear their tail rows);
-    empty groups; rows past the last group hold NaN and must not reach any output."""
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("k,n", [(136, 392), (264, 392), (392, 392), (520, 392), (1032, 392),
+                                 (64, 64), (128, 192), (320, 448), (576, 256), (1024, 512)])
+def test_tgmm_256_row_tiles_all_load_paths(k, n, cta_group):
+    """tgmm with 256-row tiles on one CTA and with 512 x 256 tiles on CTA pairs (tile_m 256,
+    cta_group 1 / 2).  k values that end inside the first CTA's rows, the second CTA's rows, the
+    second half and the second tile; k and n that are multiples of 64 (one column-blocked TMA box
+    per operand and stage, also where the box is wider than the tensor) and that are not (one box
+    per 64 columns); group sizes around the 64-row reduction step and the 16-row MMA depth (the
+    fixer warp of either CTA clears the tail rows); empty groups; rows past the last group hold
+    NaN and must not reach any output."""
     sizes = [1, 63, 64, 65, 0, 130, 15, 16, 17, 0, 300, 77]
-    m, n = sum(sizes) + 40, 392
+    m = sum(sizes) + 40
     x, _, dout = _inputs(8, m, k, n, len(sizes))
     x[sum(sizes):] = float("nan")
     dout[sum(sizes):] = float("nan")
-    got = _check_tgmm(x, dout, sizes, cfg=_lib.TileCfg(256, 0, 2, 256), what=f"pair 512-row tgmm k={k}")
+    got = _check_tgmm(x, dout, sizes, cfg=_lib.TileCfg(256, 0, cta_group, 256),
+                      what=f"256-row tgmm k={k} n={n} ctas={cta_group}")
     assert torch.isfinite(got.float()).all()
 
 
