@@ -188,7 +188,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
       cudaSuccess)
     return RD_ERR_LAUNCH;
   cudaLaunchConfig_t lc = {};
-  lc.blockDim = dim3(rd::kGemmThreads, 1, 1);
+  lc.blockDim = dim3(rd::kGemmFixerThreads, 1, 1);
   lc.dynamicSmemBytes = kSmem;
   lc.stream = stream;
   cudaLaunchAttribute attr[1];

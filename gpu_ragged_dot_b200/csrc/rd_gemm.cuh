@@ -5,8 +5,9 @@
 //   tgmm : out[i] = x[rows of group i, :]^T @ dout[rows of group i, :]   (reference :231-281)
 //
 // One persistent, warp-specialised CTA per SM:
-//   warp 0      TMA producer   -- cp.async.bulk.tensor tiles into a kStages-deep smem ring
-//   warp 1      MMA issuer     -- tcgen05.mma (K=16) into one of two TMEM accumulators
+//   warp 0      TMA producer   -- one thread: cp.async.bulk.tensor tiles into a kStages-deep smem ring
+//   warp 1      MMA issuer     -- one thread: tcgen05.mma (K=16) into one of two TMEM accumulators
+//   warp 6      tail fixer     -- tgmm: clears the rows past a group's end in a stage
 //   warps 2..5  epilogue       -- tcgen05.ld, fp32 -> bf16/fp16, staged through swizzled smem and
 //                                 written with TMA stores ([32 rows][64 cols] boxes, clipped at the
 //                                 tensor's edges); a gmm slab that crosses the end of its group
@@ -47,7 +48,9 @@ constexpr int kTileM = 128;  // UMMA M per CTA == output rows per CTA tile
 constexpr int kTileK = 64;   // elements per 128-byte swizzle row == contraction depth per stage
 constexpr int kUmmaK = 16;   // contraction depth of one tcgen05.mma for 16-bit inputs
 constexpr int kBoxBytes = 64 * 128;  // one [64 rows][128 B] TMA box
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;       // TMA warp, MMA warp, four epilogue warps
+constexpr int kGemmFixerWarp = 6;       // ragged_gemm_kernel only: clears tail rows of tgmm stages
+constexpr int kGemmFixerThreads = kGemmThreads + 32;
 constexpr int kOutBoxBytes = 32 * 128;                  // one [32 rows][64 cols] output box
 constexpr int kOutStagingBytes = 4 * 2 * kOutBoxBytes;  // 4 epilogue warps x 2 buffers
 
@@ -278,7 +281,7 @@ constexpr int stage_bytes() {
 // kTgmm == true  : tgmm.  A operand = x^T tile (MN-major), B operand = dout tile (MN-major);
 //                  kBKMajor must be false.
 template <int BN, bool kBKMajor, int kStages, bool kTgmm, int kCtas, bool kSeg = false, bool kFp8 = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmFixerThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
@@ -301,7 +304,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kStages];        // TMA data of this CTA landed
   __shared__ __align__(8) uint64_t bar_empty[kStages];       // MMAs reading the stage retired
-  __shared__ __align__(8) uint64_t bar_peer_ready[kStages];  // leader only: peer's stage is ready
+  __shared__ __align__(8) uint64_t bar_tail_go;    // MMA thread -> fixer warp(s): a stage with tail rows has landed
+  __shared__ __align__(8) uint64_t bar_tail_done;  // fixer warp(s) -> MMA thread (pair: the leader's is used)
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];  // leader only when paired
   __shared__ uint32_t tmem_slot;
@@ -334,8 +338,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
-      mbar_init(smem_u32(&bar_peer_ready[s]), 1);
     }
+    mbar_init(smem_u32(&bar_tail_go), 1);
+    mbar_init(smem_u32(&bar_tail_done), kCtas);  // one arrival per CTA's fixer warp
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_acc_full[a]), 1);
       mbar_init(smem_u32(&bar_acc_empty[a]), 4 * kCtas);  // one arrival per epilogue warp
@@ -431,118 +436,94 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    // In a pair only the leader issues MMAs.  The peer's warp 1 has nothing to do except for
-    // the tgmm stages whose tail rows it must clear in its own shared memory.
-    const uint32_t idesc_full =
-        make_idesc_f16(kFp8 ? 0 : p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
-    // A gmm row tile with at most 64 rows (the short last tile of a group, a small expert) is
-    // multiplied with M = 64: half the tensor-core time for a tile that is mostly padding.
-    // Its accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory.
-    const uint32_t idesc_half = make_idesc_f16(kFp8 ? 0 : p.ab_format, 0, kBKMajor ? 0 : 1, 64, BN);
-    // Stage-0 operand descriptors; later stages / k-steps only add to the 16-byte-unit address.
-    constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;       // A: MN-major (tgmm) or K-major
-    constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;    // B: K-major or MN-major
-    const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
-                                  : make_smem_desc(stage_base, 16, 1024);
-    const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kABytes, 16, 1024)
-                                     : make_smem_desc(stage_base + kABytes, kBoxBytes, 1024);
-    const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
-    const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
-    const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);  // same for A and B (SBO, version, swizzle)
-    uint32_t it = 0;
-    uint32_t local_tile = 0;
-    uint32_t tail_parity = 0;  // bit s: parity of the next tail hand-shake on stage s
-    bool ok = true;
-    for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
-      const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
-                                : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
-      const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
-      const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
-      RowBlocks blocks = first_block(t);
-      const uint32_t idesc = (!kTgmm && !kPair && t.rows <= 64) ? idesc_half : idesc_full;
+    // ONE thread runs the whole loop (in a pair: of the leader CTA): the loop sits on the ring's
+    // critical path and warp-wide steps are expensive there (a __syncwarp costs about 160 clocks
+    // on B200, the MMAs of a stage take 512).  The one warp-wide job, clearing the rows past a
+    // group's end in a tgmm stage, belongs to the fixer warp.
+    if (lane == 0 && leader) {
+      const uint32_t idesc_full =
+          make_idesc_f16(kFp8 ? 0 : p.ab_format, kTgmm ? 1 : 0, kBKMajor ? 0 : 1, kTileM * kCtas, BN);
+      // A gmm row tile with at most 64 rows (the short last tile of a group, a small expert) is
+      // multiplied with M = 64: half the tensor-core time for a tile that is mostly padding.
+      // Its accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory.
+      const uint32_t idesc_half = make_idesc_f16(kFp8 ? 0 : p.ab_format, 0, kBKMajor ? 0 : 1, 64, BN);
+      // Stage-0 operand descriptors; later stages / k-steps only add to the 16-byte-unit address.
+      constexpr uint32_t kAStep = (kTgmm ? 2048u : 32u) >> 4;       // A: MN-major (tgmm) or K-major
+      constexpr uint32_t kBStep = (kBKMajor ? 32u : 2048u) >> 4;    // B: K-major or MN-major
+      const uint64_t adesc0 = kTgmm ? make_smem_desc(stage_base, kBoxBytes, 1024)
+                                    : make_smem_desc(stage_base, 16, 1024);
+      const uint64_t bdesc0 = kBKMajor ? make_smem_desc(stage_base + kABytes, 16, 1024)
+                                       : make_smem_desc(stage_base + kABytes, kBoxBytes, 1024);
+      const uint32_t adesc0_lo = static_cast<uint32_t>(adesc0);
+      const uint32_t bdesc0_lo = static_cast<uint32_t>(bdesc0);
+      const uint32_t desc_hi = static_cast<uint32_t>(adesc0 >> 32);  // same for A and B (SBO, version, swizzle)
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      uint32_t tail_events = 0;  // stages handed to the fixer warp so far
+      bool ok = true;
+      for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
+        const TileCoord t = kTgmm ? decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank)
+                                  : decode_gmm_tile<BN, kCtas>(p, tile, cta_rank);
+        const int kb_count = kTgmm ? tgmm_block_count<kSeg>(p, t) : k_blocks_gmm;
+        const bool tail_stage = kTgmm && kb_count > 0 && tail_needs_clearing(t.rows);
+        RowBlocks blocks = first_block(t);
+        const uint32_t idesc = (!kTgmm && !kPair && t.rows <= 64) ? idesc_half : idesc_full;
 
-      if (kPair && !leader) {
-        // ---- peer CTA: only the tail stage of a tgmm tile needs this warp
-        if (tail_stage) {
-          const uint32_t s = (it + kb_count - 1) % kStages;
-          const uint32_t par = (tail_parity >> s) & 1u;
-          tail_parity ^= 1u << s;
-          if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
-            ok = false;
-            break;
-          }
-          const uint32_t sa = stage_base + s * kStageBytes;
-          const int live = t.rows - (kb_count - 1) * kTileK;
-          clear_tail_rows<(kABytes + kBBytes) / kBoxBytes>(sa, live, lane);
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(smem_u32(&bar_peer_ready[s]), 0);
-          __syncwarp();
-        }
-        it += kb_count;
-        continue;
-      }
-
-      // ---- single CTA, or the leader of a pair
-      const uint32_t acc = local_tile & 1u;
-      const uint32_t acc_ph = (local_tile >> 1) & 1u;
-      if (!mbar_wait<kPair>(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t tmem_d = tmem_base + acc * BN;
-      uint32_t s = it % kStages;
-      uint32_t ph = (it / kStages) & 1u;
-      for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
-        if (!mbar_wait<kPair>(smem_u32(&bar_full[s]), ph, abort_ptr)) {
+        const uint32_t acc = local_tile & 1u;
+        const uint32_t acc_ph = (local_tile >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1u, abort_ptr)) {
           ok = false;
           break;
         }
-        const uint32_t sa = stage_base + s * kStageBytes;
-        // tgmm: contraction depth that is really there in this stage (the group's last rows);
-        // whole 16-deep MMAs past it are skipped.  gmm always issues all four: columns past k
-        // are zero-filled by TMA in both operands.
-        int live = kTileK;
-        if (kTgmm) {
-          int r;
-          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
-        }
-        const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
-        if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
-          // Rows past the end of the group belong to the next group (or to nobody): clear them,
-          // up to the end of the last MMA that is issued, in every box of this stage, so they
-          // add nothing to the reduction.  (In gmm the columns past k are zero-filled by TMA.)
-          clear_tail_rows<(kABytes + kBBytes) / kBoxBytes>(sa, live, lane);
-          __syncwarp();
-          if (kPair) {  // ... and wait until the peer has done the same with its half
-            const uint32_t par = (tail_parity >> s) & 1u;
-            tail_parity ^= 1u << s;
-            if (!mbar_wait<true>(smem_u32(&bar_peer_ready[s]), par, abort_ptr)) {
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        uint32_t s = it % kStages;
+        uint32_t ph = (it / kStages) & 1u;
+        for (int kb = 0; kb < kb_count; ++kb, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0)) {
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          // tgmm: contraction depth that is really there in this stage (the group's last rows);
+          // whole 16-deep MMAs past it are skipped.  gmm always issues all four: columns past k
+          // are zero-filled by TMA in both operands.
+          int live = kTileK;
+          if (kTgmm) {
+            int r;
+            tgmm_block<kSeg>(p, t, blocks, kb, r, live);
+          }
+          const int n_mma = live >= kTileK ? kTileK / kUmmaK : (live + kUmmaK - 1) / kUmmaK;
+          if (kTgmm && (kSeg ? block_needs_clearing(live) : (tail_stage && kb == kb_count - 1))) {
+            // Rows past the end of the group belong to the next group (or to nobody): the fixer
+            // warp (of either CTA in a pair) clears them, up to the end of the last MMA that is
+            // issued, in every box of this stage, so they add nothing to the reduction.  (In gmm
+            // the columns past k are zero-filled by TMA.)
+            mbar_arrive(smem_u32(&bar_tail_go));
+            if constexpr (kPair) mbar_arrive_cluster(smem_u32(&bar_tail_go), 1);
+            if (!mbar_wait<kPair>(smem_u32(&bar_tail_done), tail_events & 1u, abort_ptr)) {
               ok = false;
               break;
             }
+            ++tail_events;
           }
-        }
-        tc_fence_after_sync();
-        if (lane == 0) {
-          // The issue path sits inside the load -> MMA -> free-the-stage loop, so it is kept
-          // short: descriptors are the stage-0 descriptors plus a stage / k-step offset added
-          // to their address field, and only a tgmm tile's last stage looks at n_mma.
+          tc_fence_after_sync();
+          // Descriptors are the stage-0 descriptors plus a stage / k-step offset added to their
+          // address field, and only a tgmm tile's last stage looks at n_mma.
           const uint32_t a_lo = adesc0_lo + s * (kStageBytes >> 4);
           const uint32_t b_lo = bdesc0_lo + s * (kStageBytes >> 4);
           if (kTgmm && n_mma < kTileK / kUmmaK) {
             for (int kk = 0; kk < n_mma; ++kk) {
               umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
-                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
-                              (kb > 0 || kk > 0) ? 1u : 0u);
+                                   make_desc64(b_lo + kk * kBStep, desc_hi), idesc,
+                                   (kb > 0 || kk > 0) ? 1u : 0u);
             }
           } else {
             umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo, desc_hi), make_desc64(b_lo, desc_hi), idesc,
-                            kb > 0 ? 1u : 0u);
+                                 kb > 0 ? 1u : 0u);
 #pragma unroll
             for (int kk = 1; kk < kTileK / kUmmaK; ++kk) {
               umma_ab<kCtas, kFp8>(tmem_d, make_desc64(a_lo + kk * kAStep, desc_hi),
-                              make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
+                                   make_desc64(b_lo + kk * kBStep, desc_hi), idesc, 1u);
             }
           }
           // Frees the smem stage (in both CTAs of a pair) when these MMAs retire.
@@ -552,10 +533,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             umma_commit(smem_u32(&bar_empty[s]));
           }
         }
-        __syncwarp();
-      }
-      if (!ok) break;
-      if (lane == 0) {
+        if (!ok) break;
         const uint32_t bar = smem_u32(&bar_acc_full[acc]);
         if (kb_count > 0) {
           if (kPair) {
@@ -568,7 +546,56 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (kPair) mbar_arrive_cluster(bar, 1);
         }
       }
-      __syncwarp();
+    }
+  } else if (warp == kGemmFixerWarp) {
+    // ------------------------------------------------------------ tail fixer (tgmm)
+    // Walks the tiles like the MMA thread and, for every stage whose last 16-deep MMA reaches past
+    // the end of its group, waits for the MMA thread's go (the stage has landed), clears those
+    // rows in every box of the stage in THIS CTA's shared memory and reports back.
+    if constexpr (kTgmm) {
+      uint32_t it = 0;
+      uint32_t events = 0;
+      uint32_t own_parity = 0;  // peer of a pair, bit s: parity of the next landing on its own barrier of slot s
+      bool ok = true;
+      for (int tile = tile_start; tile < num_tiles && ok; tile += tile_step) {
+        const TileCoord t = decode_tgmm_tile<BN, kCtas>(p, tile, cta_rank);
+        const int kb_count = tgmm_block_count<kSeg>(p, t);
+        RowBlocks blocks = first_block(t);
+        const bool tail_stage = kb_count > 0 && tail_needs_clearing(t.rows);
+        for (int kb = kSeg ? 0 : imax(kb_count - 1, 0); kb < kb_count; ++kb) {
+          int r, live;
+          tgmm_block<kSeg>(p, t, blocks, kb, r, live);
+          if (!(kSeg ? block_needs_clearing(live) : tail_stage)) continue;
+          const uint32_t s = (it + kb) % kStages;
+          if (!mbar_wait<kPair>(smem_u32(&bar_tail_go), events & 1u, abort_ptr)) {
+            ok = false;
+            break;
+          }
+          if constexpr (kPair) {
+            // The peer's bytes of such a stage are counted on its own barrier of that slot (see
+            // the producer), which is used for nothing else.
+            if (!leader) {
+              const uint32_t par = (own_parity >> s) & 1u;
+              own_parity ^= 1u << s;
+              if (!mbar_wait(smem_u32(&bar_full[s]), par, abort_ptr)) {
+                ok = false;
+                break;
+              }
+            }
+          }
+          ++events;
+          clear_tail_rows<(kABytes + kBBytes) / kBoxBytes>(stage_base + s * kStageBytes, live, lane);
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(smem_u32(&bar_tail_done), 0);
+            } else {
+              mbar_arrive(smem_u32(&bar_tail_done));
+            }
+          }
+        }
+        it += kb_count;
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
