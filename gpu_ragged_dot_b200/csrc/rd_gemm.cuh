@@ -23,8 +23,9 @@
 //             broadcast); the peer's loads count their bytes on the LEADER's "full" barrier
 //             (cta_group::2 TMA form), so the leader sees one barrier per stage, and
 //             tcgen05.commit frees the stage in both CTAs.  The one stage per tgmm tile whose
-//             tail rows must be cleared goes through a slower hand-shake (peer clears its
-//             rows, then arrives on the leader's peer_ready barrier).
+//             tail rows must be cleared goes through a slower hand-shake (the peer's bytes
+//             land on its own barrier, either CTA's fixer warp clears its rows and arrives on
+//             the leader's tail_done barrier).
 //
 // Operand layouts (all 128-byte-swizzled, written by TMA, read through UMMA descriptors):
 //   K-major  operand tile [rows][64 k]  : one box, 8-row groups 1024 B apart
@@ -164,7 +165,7 @@ __device__ __forceinline__ bool tail_needs_clearing(int group_rows) {
 
 // tgmm: the 64-row blocks one output block contracts over.  A block never crosses the end of a
 // segment (a group of group_sizes); its rows past the segment's end are cleared or skipped by
-// the MMA warp.  Plain tgmm has one segment per output block, the rows of group t.group.
+// the fixer warp and the MMA thread.  Plain tgmm has one segment per output block, the rows of group t.group.
 struct RowBlocks {
   int q;     // segments opened so far
   int row;   // first row of the next block
@@ -215,7 +216,7 @@ __device__ __forceinline__ bool block_needs_clearing(int live) {
 }
 
 // First row and live rows of block kb of a tile.  Plain tgmm (kSeg false) computes them from the
-// group's row range, as cheaply as can be: this sits in the producer's and the MMA warp's loops.
+// group's row range, as cheaply as can be: this sits in the producer's and the MMA thread's loops.
 template <bool kSeg>
 __device__ __forceinline__ void tgmm_block(const GemmArgs& p, const TileCoord& t, RowBlocks& it, int kb,
                                            int& row, int& live) {
