@@ -342,7 +342,10 @@ def run_single(args):
     torch.cuda.set_device(dev)
     shape = {"mixtral": workloads.MIXTRAL, "decode": workloads.EP_DECODE,
              "deepseek": workloads.DEEPSEEK_V3, "deepseek_quarter": workloads.DEEPSEEK_QUARTER}[args.workload]
-    dt = {"bf16": torch.bfloat16, "f32": torch.float32}[args.dtype]
+    fp8 = args.dtype == "e4m3"
+    if fp8 and args.only != "fwd":
+        raise SystemExit("bench.py: --dtype e4m3 exists for the forward product only (--only fwd)")
+    dt = {"bf16": torch.bfloat16, "f32": torch.float32, "e4m3": torch.bfloat16}[args.dtype]
     peaks = measured_peaks()
     kernels = ["fwd", "dlhs", "drhs"] if args.only is None else [args.only]
     # Allocate only what the selected kernels touch (keeps profiler captures small).
@@ -366,9 +369,14 @@ def run_single(args):
     dA = torch.empty((shape.g, shape.k, shape.n), dtype=dt, device=dev) if "drhs" in kernels else None
     esz = 2 if dt == torch.bfloat16 else 4
     ws = ops._workspace(shape.m, shape.g, dev)
+    if fp8:  # e4m3 operands, weights stored [g, n, k]; the result stays bf16
+        x = x.to(torch.float8_e4m3fn)
+        A = A.transpose(1, 2).contiguous().to(torch.float8_e4m3fn)
 
     def launch(name):
-        if name == "fwd":
+        if name == "fwd" and fp8:
+            ops.gmm_fp8_forward(x, A, gs_fwd, out=y, workspace=ws)
+        elif name == "fwd":
             ops.gmm_forward(x, A, gs_fwd, out=y, workspace=ws)
         elif name == "dlhs":
             ops.gmm_forward(dout, A, gs_bwd, trans_rhs=True, out=dx, workspace=ws)
@@ -414,7 +422,8 @@ def run_single(args):
     traffic = dram_traffic_per_launch() if args.workload == "mixtral" else {}
     gplus_f, gplus_b = int((gs_fwd_np > 0).sum()), int((gs_bwd_np > 0).sum())
     alg_bytes = {
-        "fwd": esz * 1.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
+        "fwd": (1.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n) + 2.0 * shape.m * shape.n) if fp8 else
+               esz * 1.0 * (shape.m * shape.k + gplus_f * shape.k * shape.n + shape.m * shape.n),
         "dlhs": esz * 1.0 * (shape.m * shape.n + gplus_b * shape.k * shape.n + shape.m * shape.k),
         "drhs": esz * 1.0 * (shape.m * shape.k + shape.m * shape.n + shape.g * shape.k * shape.n),
     }
@@ -462,7 +471,8 @@ def run_single(args):
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": args.dtype if args.dtype == "bf16" else "f32 in/out, TF32 products, fp32 accumulate (the bf16 peak is NOT its roof)",
+        "dtype": {"bf16": "bf16", "f32": "f32 in/out, TF32 products, fp32 accumulate (the bf16 peak is NOT its roof)",
+                  "e4m3": "e4m3 in, fp32 accumulate, bf16 out (the bf16 peak is NOT its roof)"}[args.dtype],
         "data": "synthetic",
         "config": (mixtral_config(shape, args.only, shape.m) if args.workload == "mixtral" else {
             "workload": shape.name + ("_fwd_bwd" if args.only is None else "_" + args.only),
@@ -623,6 +633,21 @@ def run_other_workloads(dev, peaks):
     ms8 = _time_ms(lambda: ops.gmm_fp8_forward(x8, A8, gs, out=y, workspace=ws), 30)
     out[s.name + "_fwd_e4m3"] = entry(ms8, 2.0 * s.m * s.k * s.n, 1.0 * (s.m * s.k + gplus * s.k * s.n) + 2.0 * s.m * s.n)
     del x, A, y, x8, A8
+    torch.cuda.empty_cache()
+
+    # the headline shape's forward with e4m3 operands (tensor-bound: kind::f8f6f4 has twice the bf16 rate)
+    s = workloads.MIXTRAL
+    gs_np = workloads.group_sizes_mixtral(0)
+    x, A, _ = workloads.make_inputs(s, dev, with_dout=False)
+    x8, A8 = x.to(f8), A.transpose(1, 2).contiguous().to(f8)
+    del x, A
+    gs = torch.from_numpy(gs_np).to(dev)
+    ws = ops._workspace(s.m, s.g, dev)
+    y = torch.empty((s.m, s.n), dtype=torch.bfloat16, device=dev)
+    ms8 = _time_ms(lambda: ops.gmm_fp8_forward(x8, A8, gs, out=y, workspace=ws), 20)
+    out[s.name + "_fwd_e4m3"] = entry(ms8, 2.0 * s.m * s.k * s.n, 1.0 * (s.m * s.k + s.g * s.k * s.n) + 2.0 * s.m * s.n)
+    out[s.name + "_fwd_e4m3"]["note"] = "tensor-bound; no measured 8-bit peak on this pool (nominal dense 4500 TFLOP/s)"
+    del y, x8, A8
     torch.cuda.empty_cache()
 
     # DeepSeek-V3 shaped: heavy-tailed groups, ~20 % empty
@@ -1066,8 +1091,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"],
-                    help="N=1 profiling runs only: f32 times the TF32 kernels (use with --no-e2e --no-cpu-baseline)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "e4m3"],
+                    help="N=1 profiling runs only: f32 times the TF32 kernels, e4m3 the 8-bit forward "
+                         "(rd_gmm_fp8; with --only fwd); use with --no-e2e --no-cpu-baseline")
     ap.add_argument("--workload", default="mixtral",
                     choices=["mixtral", "decode", "deepseek", "deepseek_quarter", "permute"],
                     help="N=1 only; the headline line is the default (mixtral); the others are for profiling")
