@@ -312,12 +312,20 @@ int launch_gemm2_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
 // 256-row tiles on one CTA (rd_gemm2.cuh) move a third less data per flop than 128-row tiles.
 // They pay off when a tile's second half usually exists: tgmm with k >= 256, and gmm when the
 // groups are long (mean rows per group >= 512; a half without rows is skipped, so the cost of a
-// wrong guess is only a shallower smem ring).
+// wrong guess is only a shallower smem ring).  At exactly 512 rows per group the picture is mixed:
+// 16 ragged groups over m 8192, k 4096, n 14336 are 5-13 % faster on 128-row tiles, the
+// expert-parallel step (64 segments of about 512 rows over 32 weight matrices) 4 % slower.
 bool choose_two_half(bool tgmm, long long m, int k, int g, int bn) {
   if (bn != 256) return false;
   if (tgmm) return k >= 256;
   return g > 0 && m / g >= 512;
 }
+
+// tgmm with 256-row tiles: 512 x 256 tiles on CTA pairs (a quarter less L2 -> SM traffic, a
+// fourth stage) were 0.6-2.4 % faster than one CTA per tile on every compute-bound shape swept
+// (m/g 512 to 2048; k 4096 and 7168; n 1536 to 14336).  Short groups make tgmm output-bound and
+// were not measured: they stay on one CTA.
+bool choose_pair_512(long long m, int k, int g) { return k >= 512 && g > 0 && m / g >= 512; }
 
 // CTA pairs (256 x 256 tiles, B operand split between the two CTAs) pay off where the
 // 256-row granularity wastes nothing: tgmm, whose tile rows are the dense k axis.  For gmm the
@@ -796,10 +804,13 @@ static int tgmm_impl(const void* x, const void* dout, const int32_t* group_sizes
   if (tile_m == 0 && cta_group != 2) tile_m = choose_two_half(true, m, k, g, bn) ? 256 : 128;
   if (tile_m == 0) tile_m = 128;
   if (cta_group == 0) {
-    cta_group = (tile_m == 128 && choose_pair(true, static_cast<long long>((k + 255) / 256) * g *
-                                                        ((n + 255) / 256), bn, sms))
-                    ? 2
-                    : 1;
+    if (tile_m == 256) {
+      cta_group = (seg_count == 1 && choose_pair_512(m, k, g)) ? 2 : 1;
+    } else {
+      cta_group = choose_pair(true, static_cast<long long>((k + 255) / 256) * g * ((n + 255) / 256), bn, sms)
+                      ? 2
+                      : 1;
+    }
   }
   const bool two_half = tile_m == 256;
   const int tile_rows = two_half ? rd::kG2TileRows * cta_group : rd::kTileM * cta_group;

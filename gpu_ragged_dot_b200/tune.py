@@ -28,7 +28,7 @@ import torch
 from . import _lib, ops, tile_table, workloads
 
 # (tile_n, cta_group, tile_m)
-CANDIDATES = [(256, 1, 128), (256, 1, 256), (256, 2, 128), (128, 1, 128), (64, 1, 128)]
+CANDIDATES = [(256, 1, 128), (256, 1, 256), (256, 2, 128), (256, 2, 256), (128, 1, 128), (64, 1, 128)]
 
 
 def _time(fn, reps):
