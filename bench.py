@@ -150,6 +150,30 @@ def physical_gpu_index(local_index: int) -> int:
     return local_index
 
 
+def bind_to_gpu_numa_node(local_index: int) -> str:
+    """Pins this process to the CPUs NVML reports as local to its GPU, so that the pinned host
+    buffers it allocates afterwards (first touch) and the threads that drive the copies sit on the
+    GPU's own NUMA node.  What a deployment does with numactl; returns a note for the JSON line."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_index))
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        local = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus = local & allowed
+        if not cpus:
+            return "not bound: the GPU's local CPUs are outside this process's CPU set"
+        if cpus == allowed:
+            return f"all {len(allowed)} CPUs of this process are local to the GPU"
+        os.sched_setaffinity(0, cpus)
+        return f"bound to the {len(cpus)} CPUs local to the GPU (of {len(allowed)})"
+    except Exception as e:  # no NVML, no permission: run unbound
+        return f"not bound ({type(e).__name__})"
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -847,6 +871,7 @@ def run_expert_parallel(args):
 
     _lib.load()
     rank, world, local = dist_env()
+    numa_note = bind_to_gpu_numa_node(local)
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
@@ -1019,7 +1044,8 @@ def run_expert_parallel(args):
                "api": "ExpertParallelRaggedDot.forward_host + backward_host per rank, pinned host buffers: tokens, "
                       "routing and the cotangent of the rows the rank receives go in, y (the rows received; their "
                       "number is fixed by the inputs and was read once before timing) and dx come out; the weight "
-                      "gradient stays on the device beside the weights it belongs to"}
+                      "gradient stays on the device beside the weights it belongs to",
+               "host_numa": numa_note + " (rank 0)"}
         del layer
         torch.cuda.empty_cache()
     if rank == 0 and results:
