@@ -878,6 +878,7 @@ def test_bounded_wait_expiry_is_reported_and_recoverable(tile_m, monkeypatch):
     next ordinary call on the same workspace is correct.  Nothing traps, faults or hangs."""
     import time
 
+    monkeypatch.delenv("RD_CHECK_STATUS", raising=False)  # the first call must return, not raise
     m, k, n, g = 700, 128, 512, 4
     x, A, _ = _inputs(81, m, k, n, 2)
     gs = torch.tensor([300, 0, 250, 150], dtype=torch.int32)
